@@ -1,0 +1,250 @@
+/*
+ * lmoe.h -- C ABI of the B200 (sm_100a) backend for the quantized indexed
+ * mixture-of-experts path of the "laguna" engine: on-GPU routing, the indexed
+ * Q4_K / Q6_K expert matmuls (decode mat-vec and prefill grouped GEMM), SwiGLU,
+ * weighted combine and the shared expert.
+ *
+ * Every entry point mirrors one function of the reference's `src/ops` dispatch
+ * layer or of `src/moe.rs`; the comment above each declaration names the
+ * reference interface it replaces (path:line inside the reference project).
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers on the current CUDA device unless
+ *     the parameter name ends in `_host`.  Tensors are dense row-major f32
+ *     (activations, weights of the router) or u32 (expert ids), exactly the
+ *     dtypes the reference validates (src/ops/dispatch.rs:812-833).
+ *   - `stream` is a `cudaStream_t` passed as `void *` (NULL = default stream).
+ *     Like the reference (src/ops/dispatch.rs:891-917) every op is
+ *     asynchronous: it is enqueued on the stream and returns.
+ *   - Return value: 0 on success, a negative `lmoe_status` otherwise; the
+ *     message is available from `lmoe_last_error()` (thread-local).  Shape or
+ *     dtype mismatches are reported as errors before anything is launched --
+ *     never as a GPU fault (src/ops/mv_id.rs:137-145).
+ *   - No entry point allocates device memory on the hot path except the
+ *     `*_create` functions.  Scratch is supplied by the caller; its size comes
+ *     from the `*_workspace_bytes` queries.
+ *   - There is no CPU fallback.  Without a CUDA device every compute entry
+ *     point fails with LMOE_ERR_CUDA.
+ */
+#ifndef LMOE_H
+#define LMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t lmoe_status;
+
+enum {
+    LMOE_OK = 0,
+    LMOE_ERR_INVALID = -1,     /* shape / dtype / argument mismatch */
+    LMOE_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for */
+    LMOE_ERR_CUDA = -3,        /* CUDA runtime error (message has the detail) */
+    LMOE_ERR_WORKSPACE = -4,   /* workspace missing, too small or misaligned */
+    LMOE_ERR_DEVICE_FLAG = -5  /* a kernel recorded a bounded-wait timeout or index-guard trip */
+};
+
+/* ggml type ids of the two expert formats (src/gguf.rs:244-276 keeps the GGUF
+ * dtype on the stack; the official checkpoint uses Q4_K gate/up, Q6_K down). */
+enum {
+    LMOE_Q4_K = 12, /* 144-byte super-block, 256 weights (src/ops/mv.metal:55-60) */
+    LMOE_Q6_K = 14  /* 210-byte super-block, 256 weights (src/ops/mv.metal:70-75) */
+};
+
+/* Token count from which the block switches from the indexed mat-vec to the
+ * grouped GEMM: `MM_ID_MIN_SEQ`, src/ops/mod.rs:31. */
+#define LMOE_MM_ID_MIN_SEQ 32
+
+const char *lmoe_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+const char *lmoe_last_error(void);
+
+/* ------------------------------------------------------------------ stack --
+ * `ExpertStack`, src/gguf.rs:247-276: `[n_expert][n_out][k/256]` super-blocks,
+ * expert-major, contiguous, byte-identical to the GGUF tensor data.
+ * `base_off` (bytes, multiple of 16) is the offset of the first block inside
+ * the device allocation, kept for signature compatibility with the reference's
+ * page-floored mmap views (src/gguf.rs:617-658). */
+typedef struct lmoe_expert_stack lmoe_expert_stack;
+
+/* `Weights::expert_stack` (src/gguf.rs:554-607): one upload of the raw
+ * super-blocks into device memory, layout unchanged. `nbytes` must equal
+ * n_expert * n_out * (k/256) * type_size. */
+lmoe_status lmoe_expert_stack_create(int32_t dtype, int64_t n_expert, int64_t n_out, int64_t k,
+                                     const void *bytes_host, size_t nbytes, size_t base_off,
+                                     lmoe_expert_stack **out);
+/* Zero-copy view over super-blocks already resident in device memory (the
+ * counterpart of `expert_stack_mmap`, src/gguf.rs:617-658). The caller keeps
+ * the allocation alive; `device_base + base_off` must be 16-byte aligned. */
+lmoe_status lmoe_expert_stack_wrap(int32_t dtype, int64_t n_expert, int64_t n_out, int64_t k,
+                                   const void *device_base, size_t nbytes, size_t base_off,
+                                   lmoe_expert_stack **out);
+void lmoe_expert_stack_destroy(lmoe_expert_stack *stack);
+/* First super-block on the device (base + base_off). */
+const void *lmoe_expert_stack_device_ptr(const lmoe_expert_stack *stack);
+/* Shape query: any out pointer may be NULL. */
+lmoe_status lmoe_expert_stack_info(const lmoe_expert_stack *stack, int32_t *dtype, int64_t *n_expert,
+                                   int64_t *n_out, int64_t *k, size_t *nbytes);
+
+/* Encode f32 rows into Q4_K / Q6_K super-blocks on the device (a deterministic
+ * encoder used to build synthetic stacks; the reference calls candle's
+ * `QTensor::quantize` for this in its tests, src/ops/dispatch.rs:2234).
+ * `src` holds nblocks*256 floats, `dst` nblocks*type_size bytes. */
+lmoe_status lmoe_quantize(int32_t dtype, const float *src, int64_t nblocks, void *dst, void *stream);
+/* Decode super-blocks to f32 on the device (`QTensor::dequantize`). */
+lmoe_status lmoe_dequantize(int32_t dtype, const void *src, int64_t nblocks, float *dst, void *stream);
+
+/* ---------------------------------------------------------------- routing --
+ * `MoeBlock::route` = `route_logits` + `route_from_logits`, src/moe.rs:62-119:
+ * logits = x . router^T; p = sigmoid(logits); selection = p + bias; ids = the
+ * first top_k of the stable descending order of `selection` (ties -> lower
+ * expert index); weights = p[ids], divided by max(sum, 2^-14) when `norm`,
+ * times `scale` unless scale is 0 or 1.
+ *   router [n_expert, hidden] f32 (GGUF `ffn_gate_inp` orientation),
+ *   bias [n_expert] f32 or NULL, x [t, hidden] f32,
+ *   ids_out [t, top_k] u32, weights_out [t, top_k] f32.
+ * Workspace: lmoe_route_workspace_bytes(t, n_expert). */
+size_t lmoe_route_workspace_bytes(int64_t t, int64_t n_expert);
+lmoe_status lmoe_route(const float *router, const float *bias, const float *x, int64_t t, int64_t hidden,
+                       int64_t n_expert, int64_t top_k, float scale, int32_t norm, uint32_t *ids_out,
+                       float *weights_out, void *workspace, size_t workspace_bytes, void *stream);
+/* `route_from_logits` alone, src/moe.rs:94-119 (logits [t, n_expert] f32). */
+lmoe_status lmoe_route_from_logits(const float *logits, const float *bias, int64_t t, int64_t n_expert,
+                                   int64_t top_k, float scale, int32_t norm, uint32_t *ids_out,
+                                   float *weights_out, void *stream);
+
+/* -------------------------------------------------------- indexed mat-vec --
+ * `ops::mul_mv_id`, src/ops/mv_id.rs:37-45 -> `run_inner`,
+ * src/ops/dispatch.rs:799-918 -> kernel_mul_mv_id_q{4,6}_K_f32_v,
+ * src/ops/mv.metal:181-290, 413-504, 638-717.
+ *   out[t, s, :] = W[ids[t, s]] . x[t, (x_per_row == 1 ? 0 : s), :]
+ *   x [t, x_per_row, k] f32, ids [t_ids, top_k] u32, out [t, top_k, n_out] f32.
+ * Errors (not faults): k != stack k, t_ids != t, x_per_row not in {1, top_k},
+ * k % 256 != 0. An id >= n_expert yields a zero row and sets the device flag
+ * of `lmoe_check_device_flag`. */
+lmoe_status lmoe_mul_mv_id(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
+                           int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k, float *out,
+                           void *stream);
+
+/* `ops::mul_mv`, src/ops/mv_id.rs:54-56 -> `run_plain_mv`,
+ * src/ops/dispatch.rs:964-1057: plain quantized mat-vec (the lm_head bypass).
+ *   weight: raw [n_out, k/256] super-blocks on the device, x [t, k] -> out [t, n_out]. */
+lmoe_status lmoe_mul_mv(const void *weight, int32_t dtype, int64_t n_out, int64_t k, const float *x,
+                        int64_t t, float *out, void *stream);
+
+/* ------------------------------------------------------ grouped GEMM path --
+ * `Map0Scratch`, src/ops/dispatch.rs:547-549, 752-757: `tpe` (n_expert u32 at
+ * byte 0) followed by `ids_map` (n_expert * t i32 at byte n_expert*4): for each
+ * expert the flat `token*top_k + slot` ids routed to it, tokens ascending. */
+size_t lmoe_map0_scratch_bytes(int64_t n_expert, int64_t t);
+/* `ops::mm_id::prepare_map0`, src/ops/mm_id.rs:27-29 -> `prepare_mm_id_map0`,
+ * src/ops/dispatch.rs:927-956 -> kernel_mul_mm_id_map0, src/ops/mm_id.metal:207-269.
+ * Experts must be distinct within a token (src/ops/dispatch.rs:2341-2346). */
+lmoe_status lmoe_prepare_map0(const uint32_t *ids, int64_t t, int64_t top_k, int64_t n_expert,
+                              void *scratch, size_t scratch_bytes, void *stream);
+/* `ops::mm_id::supported`, src/ops/mm_id.rs:48-50. Returns 1 or 0. */
+int32_t lmoe_mm_id_supported(int32_t dtype, int64_t top_k);
+/* Workspace of one grouped-GEMM projection (staged f16 activations). */
+size_t lmoe_mm_id_workspace_bytes(int64_t t, int64_t top_k, int64_t x_per_row, int64_t k);
+/* `ops::mm_id::mul_mm_id_shared`, src/ops/mm_id.rs:32-39 -> `run_mm_shared`,
+ * src/ops/dispatch.rs:789-797 -> kernel_mul_mm_id_q{4,6}_K_f32_t,
+ * src/ops/mm_id.metal:492-647.  Same shapes and errors as lmoe_mul_mv_id.  The
+ * scratch geometry (`map_n_expert`, `map_t`, `map_top_k`: what prepare_map0 was
+ * called with) is re-validated against this projection, src/ops/dispatch.rs:903-909.
+ * Operands are staged as f16 tiles with f32 accumulation, like the reference's
+ * default variant (`MmVariant::Tensor`, src/ops/mod.rs:205-215). */
+lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *stack, const float *x, int64_t t,
+                                  int64_t x_per_row, int64_t k, const uint32_t *ids, int64_t t_ids,
+                                  int64_t top_k, const void *map0_scratch, int64_t map_n_expert,
+                                  int64_t map_t, int64_t map_top_k, float *out, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+/* `ops::mm_id::mul_mm_id`, src/ops/mm_id.rs:16-18: self-contained (runs its own
+ * map0 pass). Workspace: lmoe_mm_id_workspace_bytes(...) + lmoe_map0_scratch_bytes(...). */
+lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
+                           int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k, float *out,
+                           void *workspace, size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------- glue --
+ * `ops::silu_mul`, src/ops/silu_mul.rs:14 -> kernel_moe_silu_mul,
+ * src/ops/silu_mul.metal:57-72: out[i] = (g / (1 + exp(-g))) * u, the two
+ * roundings kept separate. n <= INT32_MAX. */
+lmoe_status lmoe_silu_mul(const float *gate, const float *up, int64_t n, float *out, void *stream);
+/* `ops::combine`, src/ops/combine.rs:16 -> `run_combine`, src/ops/dispatch.rs:1366-1506
+ * -> kernel_moe_combine{,_rescale}, src/ops/combine.metal:70-133:
+ *   out[s, c] = sum_k down[s, k, c] * (col_l2[s, k] * 2^-15) * w[s, k]
+ * (col_l2 may be NULL: plain weighted sum). Fixed summation order: k strided
+ * over next_pow2(top_k/2) lanes, lanes folded by a butterfly. Errors:
+ * next_pow2(top_k/2) > 32; seq*top_k*n_out > INT32_MAX (src/ops/dispatch.rs:294-305). */
+lmoe_status lmoe_combine(const float *down, const float *col_l2, const float *weights, int64_t seq,
+                         int64_t top_k, int64_t n_out, float *out, void *stream);
+
+/* ------------------------------------------------------------ whole block --
+ * `MoeBlock`, src/moe.rs:28-79, with `FusedExperts` (src/moe.rs:194-324) and
+ * `SharedExpert` (src/moe.rs:327-345) behind it.  The layer borrows the stacks
+ * and the router/bias device buffers; they must outlive it. Shared stacks are
+ * `[1, n_out, k]` stacks or all NULL (no shared expert). */
+typedef struct lmoe_layer lmoe_layer;
+
+lmoe_status lmoe_layer_create(int64_t hidden, int64_t expert_ff, int64_t n_expert, int64_t top_k,
+                              float scale, int32_t norm, const float *router, const float *bias,
+                              const lmoe_expert_stack *gate, const lmoe_expert_stack *up,
+                              const lmoe_expert_stack *down, const lmoe_expert_stack *shared_gate,
+                              const lmoe_expert_stack *shared_up, const lmoe_expert_stack *shared_down,
+                              lmoe_layer **out);
+void lmoe_layer_destroy(lmoe_layer *layer);
+
+/* Bytes of scratch `lmoe_moe_forward*` needs for up to `max_tokens` tokens. */
+size_t lmoe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens);
+
+/* `MoeBlock::forward` on the decode path (t < LMOE_MM_ID_MIN_SEQ in the
+ * reference; any t <= 64 here), src/moe.rs:73-78 with the mv_id branch of
+ * src/moe.rs:221-323 fused: route, stream each DISTINCT selected expert and the
+ * shared expert once, SwiGLU and the weighted combine in the same kernels.
+ *   x [t, hidden] f32 -> out [t, hidden] f32; ids_out [t, top_k] / weights_out
+ * [t, top_k] receive the routing decision when non-NULL. */
+lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                    uint32_t *ids_out, float *weights_out, void *workspace,
+                                    size_t workspace_bytes, void *stream);
+
+/* `MoeBlock::forward` on the prefill path (the mm_id branch of src/moe.rs:236-323):
+ * route, sort token-slots by expert, grouped GEMM on tensor cores with f16
+ * operand tiles dequantized in shared memory and f32 accumulation, SwiGLU in
+ * the gate/up epilogue, routing weight in the down epilogue, fixed-order
+ * combine plus the shared expert. */
+lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                     uint32_t *ids_out, float *weights_out, void *workspace,
+                                     size_t workspace_bytes, void *stream);
+
+/* `MoeBlock::forward` with HOST buffers: copies x to the device, runs the decode
+ * or prefill path (t >= LMOE_MM_ID_MIN_SEQ -> prefill, src/moe.rs:236-240),
+ * copies the result back and synchronises the stream. `x_host` / `out_host`
+ * should be pinned for full copy bandwidth. */
+lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                  uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
+/* Expert-parallel pieces (experts [first, first + n_local) of the layer are
+ * resident on this GPU; the reference has no multi-GPU path, this is new):
+ * run the routed experts of pre-routed, pre-dispatched rows.
+ *   x [rows, hidden] f32, local_ids [rows] u32 (expert id relative to the
+ *   layer's first expert), row_weights [rows] f32 -> out [rows, hidden] f32
+ *   = row_weights[r] * FFN_{local_ids[r]}(x[r]). */
+lmoe_status lmoe_experts_forward_rows(const lmoe_layer *layer, const float *x, const uint32_t *local_ids,
+                                      const float *row_weights, int64_t rows, float *out, void *workspace,
+                                      size_t workspace_bytes, void *stream);
+/* The shared expert alone: out [t, hidden] = FFN_shared(x [t, hidden]). */
+lmoe_status lmoe_shared_forward(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                void *workspace, size_t workspace_bytes, void *stream);
+
+/* Reads (and clears) the device error word kept in the first bytes of a
+ * workspace after the stream has been synchronised by the caller: 0 = clean.
+ * Non-zero: LMOE_ERR_DEVICE_FLAG with the cause in lmoe_last_error(). */
+lmoe_status lmoe_check_device_flag(void *workspace, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LMOE_H */

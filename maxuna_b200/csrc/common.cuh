@@ -1,0 +1,81 @@
+// Shared declarations of the sm_100a MoE library: error plumbing, handle
+// structs, launch prototypes of every kernel file.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lmoe.h"
+
+#define QK_K 256
+#define Q4K_BYTES 144
+#define Q6K_BYTES 210
+
+// ---- error plumbing (thread-local message, status code) --------------------
+lmoe_status lmoe_fail(lmoe_status code, const char *fmt, ...);
+void lmoe_clear_error();
+
+#define LMOE_CUDA(expr)                                                                            \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess)                                                                    \
+            return lmoe_fail(LMOE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));      \
+    } while (0)
+
+#define LMOE_LAUNCH_CHECK(name)                                                                    \
+    do {                                                                                           \
+        cudaError_t e__ = cudaGetLastError();                                                      \
+        if (e__ != cudaSuccess)                                                                    \
+            return lmoe_fail(LMOE_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---- handles ----------------------------------------------------------------
+struct lmoe_expert_stack {
+    int32_t dtype;
+    int64_t n_expert, n_out, k;
+    const uint8_t *base; // device allocation (or caller's buffer for wrapped stacks)
+    size_t base_off;     // first super-block = base + base_off
+    size_t nbytes;       // bytes of super-blocks
+    bool owned;
+    int device;
+    const uint8_t *blocks() const { return base + base_off; }
+    int type_size() const { return dtype == LMOE_Q4_K ? Q4K_BYTES : Q6K_BYTES; }
+    int64_t row_bytes() const { return k / QK_K * type_size(); }
+    int64_t expert_bytes() const { return n_out * row_bytes(); }
+};
+
+struct lmoe_layer {
+    int64_t hidden, expert_ff, n_expert, top_k;
+    float scale;
+    int32_t norm;
+    const float *router, *bias;
+    const lmoe_expert_stack *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+};
+
+static inline int lmoe_type_size(int32_t dtype) {
+    return dtype == LMOE_Q4_K ? Q4K_BYTES : dtype == LMOE_Q6_K ? Q6K_BYTES : 0;
+}
+
+static inline size_t lmoe_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- kernel launchers (one per .cu file) -----------------------------------
+// route.cu
+cudaError_t launch_route_logits(const float *router, const float *x, int t, int hidden, int n_expert,
+                                float *logits, cudaStream_t s);
+cudaError_t launch_route_select(const float *logits, const float *bias, int t, int n_expert, int top_k,
+                                float scale, int norm, uint32_t *ids, float *weights, cudaStream_t s);
+// mv_id.cu
+cudaError_t launch_mul_mv_id(int dtype, const uint8_t *w, int64_t expert_bytes, int n_expert, int n_out, int k,
+                             const float *x, int t, int x_per_row, const uint32_t *ids, int top_k, float *out,
+                             cudaStream_t s);
+// glue.cu
+cudaError_t launch_silu_mul(const float *g, const float *u, int64_t n, float *out, cudaStream_t s);
+cudaError_t launch_combine(const float *down, const float *col_l2, const float *w, int seq, int top_k,
+                           int n_out, float *out, cudaStream_t s);
+cudaError_t launch_add_inplace(float *out, const float *b, int64_t n, cudaStream_t s);
+cudaError_t launch_map0(const uint32_t *ids, int t, int top_k, int n_expert, uint32_t *tpe, int32_t *ids_map,
+                        cudaStream_t s);
+// codec.cu
+cudaError_t launch_quantize(int dtype, const float *src, int64_t nblocks, uint8_t *dst, cudaStream_t s);
+cudaError_t launch_dequantize(int dtype, const uint8_t *src, int64_t nblocks, float *dst, cudaStream_t s);

@@ -1,0 +1,122 @@
+// Stand-alone routing kernels: router logits (bit-specified f32 reduction) and
+// the sigmoid / bias / ordered top-k / normalise step.
+// Reference: `route_logits` and `route_from_logits`, src/moe.rs:84-119.
+#include "common.cuh"
+#include "route_math.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 8;
+
+// grid (ceil(n_expert / ROUTE_WARPS), ceil(t / TT)); one warp per expert row,
+// TT tokens per pass so the router row is read once per token tile.
+template <int TT>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_logits_kernel(const float *__restrict__ router, const float *__restrict__ x, int t, int hidden,
+                    int n_expert, float *__restrict__ logits) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = blockIdx.x * ROUTE_WARPS + warp;
+    const int t0 = blockIdx.y * TT;
+    if (e >= n_expert) return;
+    const float *w = router + (size_t)e * hidden;
+    float acc[TT][4];
+#pragma unroll
+    for (int i = 0; i < TT; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+    if ((hidden & 3) == 0) {
+        const int full = hidden / 128; // passes where every lane has a full float4
+#pragma unroll 4
+        for (int j = 0; j < full; j++) {
+            const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + 128 * j + 4 * lane));
+#pragma unroll
+            for (int i = 0; i < TT; i++) {
+                if (t0 + i < t) {
+                    const float4 xv =
+                        __ldg(reinterpret_cast<const float4 *>(x + (size_t)(t0 + i) * hidden + 128 * j + 4 * lane));
+                    acc[i][0] = __fmaf_rn(xv.x, wv.x, acc[i][0]);
+                    acc[i][1] = __fmaf_rn(xv.y, wv.y, acc[i][1]);
+                    acc[i][2] = __fmaf_rn(xv.z, wv.z, acc[i][2]);
+                    acc[i][3] = __fmaf_rn(xv.w, wv.w, acc[i][3]);
+                }
+            }
+        }
+        const int base = 128 * full + 4 * lane; // ragged last pass (hidden % 128 != 0)
+        if (base < hidden) {
+            const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + base));
+#pragma unroll
+            for (int i = 0; i < TT; i++) {
+                if (t0 + i < t) {
+                    const float4 xv = __ldg(reinterpret_cast<const float4 *>(x + (size_t)(t0 + i) * hidden + base));
+                    acc[i][0] = __fmaf_rn(xv.x, wv.x, acc[i][0]);
+                    acc[i][1] = __fmaf_rn(xv.y, wv.y, acc[i][1]);
+                    acc[i][2] = __fmaf_rn(xv.z, wv.z, acc[i][2]);
+                    acc[i][3] = __fmaf_rn(xv.w, wv.w, acc[i][3]);
+                }
+            }
+        }
+    } else {
+        for (int j = 0; 128 * j < hidden; j++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int idx = 128 * j + 4 * lane + c;
+                if (idx < hidden) {
+                    const float wv = w[idx];
+#pragma unroll
+                    for (int i = 0; i < TT; i++)
+                        if (t0 + i < t) acc[i][c] = __fmaf_rn(x[(size_t)(t0 + i) * hidden + idx], wv, acc[i][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TT; i++) {
+        const float v = lmoe_router_fold(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        if (lane == 0 && t0 + i < t) logits[(size_t)(t0 + i) * n_expert + e] = v;
+    }
+}
+
+// One warp per token; scores staged in shared memory (2 * n_expert floats per warp).
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_select_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int t, int n_expert,
+                    int top_k, float scale, int norm, uint32_t *__restrict__ ids, float *__restrict__ weights) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int token = blockIdx.x * ROUTE_WARPS + warp;
+    if (token >= t) return;
+    float *probs = smem + (size_t)warp * 2 * n_expert;
+    float *sel = probs + n_expert;
+    for (int e = lane; e < n_expert; e += 32) {
+        const float p = lmoe_sigmoid_fixed(logits[(size_t)token * n_expert + e]);
+        probs[e] = p;
+        sel[e] = bias ? __fadd_rn(p, bias[e]) : p;
+    }
+    __syncwarp();
+    lmoe_warp_select(sel, probs, n_expert, top_k, scale, norm, ids + (size_t)token * top_k,
+                     weights + (size_t)token * top_k, lane);
+}
+
+} // namespace
+
+cudaError_t launch_route_logits(const float *router, const float *x, int t, int hidden, int n_expert,
+                                float *logits, cudaStream_t s) {
+    if (t == 0) return cudaSuccess;
+    const unsigned gx = (unsigned)((n_expert + ROUTE_WARPS - 1) / ROUTE_WARPS);
+    if (t <= 2) {
+        route_logits_kernel<1><<<dim3(gx, t), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
+    } else if (t <= 64) {
+        route_logits_kernel<4><<<dim3(gx, (t + 3) / 4), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
+    } else {
+        route_logits_kernel<8><<<dim3(gx, (t + 7) / 8), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_route_select(const float *logits, const float *bias, int t, int n_expert, int top_k,
+                                float scale, int norm, uint32_t *ids, float *weights, cudaStream_t s) {
+    if (t == 0) return cudaSuccess;
+    const size_t smem = (size_t)ROUTE_WARPS * 2 * n_expert * sizeof(float);
+    const unsigned grid = (unsigned)((t + ROUTE_WARPS - 1) / ROUTE_WARPS);
+    route_select_kernel<<<grid, ROUTE_WARPS * 32, smem, s>>>(logits, bias, t, n_expert, top_k, scale, norm, ids,
+                                                             weights);
+    return cudaGetLastError();
+}

@@ -183,7 +183,8 @@ class HostLayer:
                  gate_dtype=Q4_K, down_dtype=Q6_K):
         self.hidden, self.expert_ff, self.n_expert, self.top_k = hidden, expert_ff, n_expert, top_k
         self.scale, self.norm = scale, norm
-        self.router, self.bias = _f32(router), _f32(bias)
+        self.router = _f32(router)
+        self.bias = None if bias is None else _f32(bias)
         self.gate, self.up, self.down = _u8(gate).reshape(-1), _u8(up).reshape(-1), _u8(down).reshape(-1)
         self.sh_gate = None if sh_gate is None else _u8(sh_gate).reshape(-1)
         self.sh_up = None if sh_up is None else _u8(sh_up).reshape(-1)

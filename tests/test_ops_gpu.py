@@ -1,0 +1,231 @@
+"""Op-level parity on the GPU, through the C ABI, against the CPU oracle.
+
+The cases follow the reference's on-device kernel tests: mul_mv_id
+(src/ops/mv_id.rs:100-203), combine / silu_mul (src/ops/combine.rs:76-124,
+src/ops/silu_mul.rs:58-99), routing (src/moe.rs:405-500), with the reference's
+bound of rel-L2 < 1e-3 against the dequantize-then-dot oracle and bit-exact
+expert ids.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DTYPES = [(12, "Q4K"), (14, "Q6K")]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _stack(orc, dev, dt, n_expert, n_out, k, seed):
+    from maxuna_b200.gguf import ExpertStack
+
+    w = orc.pseudo_random(n_expert * n_out * k, seed, -1.0, 1.0)
+    raw = orc.quantize(dt, w)
+    return ExpertStack.from_bytes(raw, dt, n_expert, n_out, k, device=dev), raw
+
+
+def _run_mv(orc, dev, dt, n_expert, n_out, k, t, top_k, xpr, ids, seed, base_off=0):
+    from maxuna_b200 import ops
+    from maxuna_b200.gguf import ExpertStack
+
+    w = orc.pseudo_random(n_expert * n_out * k, seed, -1.0, 1.0)
+    raw = orc.quantize(dt, w)
+    stack = ExpertStack.from_bytes(raw, dt, n_expert, n_out, k, device=dev, base_off=base_off)
+    x = orc.pseudo_random(t * xpr * k, seed ^ 0xABCD, -1.0, 1.0).reshape(t, xpr, k)
+    got = ops.mul_mv_id(stack, torch.from_numpy(x).to(dev), torch.from_numpy(ids.astype(np.int32)).to(dev))
+    assert tuple(got.shape) == (t, top_k, n_out)
+    want = orc.mul_id(dt, raw, n_expert, n_out, k, x, ids)
+    return got.cpu().numpy(), want
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_mv_shared_row_gate_up(orc, dev, dt, name):
+    ids = orc.random_ids(3, 2, 4, 0x11)
+    got, want = _run_mv(orc, dev, dt, 4, 8, 256, 3, 2, 1, ids, 0x100)
+    assert orc.rel_l2(got, want) < 1e-3
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_mv_per_slot_row_down(orc, dev, dt, name):
+    ids = orc.random_ids(5, 4, 4, 0x22)
+    got, want = _run_mv(orc, dev, dt, 4, 8, 256, 5, 4, 4, ids, 0x200)
+    assert orc.rel_l2(got, want) < 1e-3
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_mv_repeated_expert_ids(orc, dev, dt, name):
+    ids = np.ones((4, 3), np.uint32)
+    got, want = _run_mv(orc, dev, dt, 4, 8, 256, 4, 3, 1, ids, 0x300)
+    assert orc.rel_l2(got, want) < 1e-3
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_mv_ragged_n_out_and_two_blocks(orc, dev, dt, name):
+    # n_out = 100 (ragged last row group), k = 512 = two super-blocks per row
+    for xpr, seed, iseed in ((1, 0x100, 0x11), (4, 0x200, 0x22)):
+        ids = orc.random_ids(5, 4, 8, iseed)
+        got, want = _run_mv(orc, dev, dt, 8, 100, 512, 5, 4, xpr, ids, seed)
+        assert orc.rel_l2(got, want) < 1e-3
+
+
+def test_mv_base_off_bitwise(orc, dev):
+    ids = orc.random_ids(3, 2, 4, 0x44)
+    a, _ = _run_mv(orc, dev, 12, 4, 8, 256, 3, 2, 1, ids, 0x0FF5E7, base_off=0)
+    b, _ = _run_mv(orc, dev, 12, 4, 8, 256, 3, 2, 1, ids, 0x0FF5E7, base_off=96)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_mv_shape_mismatch_errors(orc, dev):
+    from maxuna_b200 import LmoeError, ops
+
+    stack, _ = _stack(orc, dev, 12, 4, 8, 256, 1)
+    x = torch.zeros(1, 1, 128, device=dev)
+    ids = torch.zeros(1, 2, dtype=torch.int32, device=dev)
+    with pytest.raises(LmoeError):
+        ops.mul_mv_id(stack, x, ids)
+    with pytest.raises(LmoeError):
+        ops.mul_mv_id(stack, torch.zeros(2, 1, 256, device=dev), ids)  # ids t != x t
+    with pytest.raises(LmoeError):
+        ops.mul_mv_id(stack, torch.zeros(1, 1, 256, device=dev, dtype=torch.float16), ids)
+    torch.cuda.synchronize()  # the context must still be healthy
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_plain_mv(orc, dev, dt, name):
+    from maxuna_b200 import ops
+
+    n_out, k, t = 100, 768, 3
+    raw = orc.quantize(dt, orc.pseudo_random(n_out * k, 7, -1.0, 1.0))
+    x = orc.pseudo_random(t * k, 8, -1.0, 1.0).reshape(t, k)
+    buf = torch.zeros(raw.size + 128, dtype=torch.uint8, device=dev)
+    buf[: raw.size] = torch.from_numpy(raw).to(dev)
+    got = ops.mul_mv(buf, dt, n_out, k, torch.from_numpy(x).to(dev)).cpu().numpy()
+    assert orc.rel_l2(got, orc.mul_mv(dt, raw, n_out, k, x)) < 1e-3
+
+
+@pytest.mark.parametrize("dt,name", DTYPES)
+def test_device_codec_matches_oracle(orc, dev, dt, name):
+    from maxuna_b200.gguf import ExpertStack
+
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((3, 4, 512)) * 0.02).astype(np.float32)
+    st = ExpertStack.quantize(torch.from_numpy(w).to(dev), dt)
+    raw = st.raw()
+    # device decode == oracle decode of the same bytes, bit for bit
+    deq_dev = st.dequantize().cpu().numpy().ravel()
+    deq_cpu = orc.dequantize(dt, raw)
+    np.testing.assert_allclose(deq_dev, deq_cpu, rtol=1e-6, atol=1e-9)
+    # and the device encoder produces valid blocks close to the input
+    assert orc.rel_l2(deq_cpu, w) < (0.08 if dt == 12 else 0.02)
+    # golden blocks (gguf-py decode) through the device decoder
+    z = np.load(os.path.join(GOLD, "kquant_decode.npz"))
+    key = "q4k" if dt == 12 else "q6k"
+    blocks = z[key + "_blocks"]
+    g = ExpertStack.from_bytes(blocks.reshape(-1), dt, 1, blocks.shape[0], 256, device=dev)
+    np.testing.assert_allclose(g.dequantize().cpu().numpy().reshape(-1, 256), z[key + "_decoded"], rtol=2e-6, atol=1e-9)
+
+
+def test_routing_known_answers(orc, dev):
+    from maxuna_b200 import ops
+
+    for c in json.load(open(os.path.join(GOLD, "routing_kat.json"))):
+        logits = torch.tensor([c["logits"]], dtype=torch.float32, device=dev)
+        bias = torch.tensor(c["bias"], dtype=torch.float32, device=dev)
+        ids, w = ops.route_from_logits(logits, bias, c["top_k"], c["scale"], c["norm"])
+        assert ids[0].tolist() == c["ids"], c["name"]
+        want = np.array(c["weights"])
+        assert np.all(np.abs(w[0].cpu().numpy() - want) <= c["atol"] + c["rtol"] * np.abs(want)), c["name"]
+    # router matmul == direct logits with an identity router (src/moe.rs:486-500)
+    x = torch.tensor([[2.0, -2.0, 0.0, 1.0, -1.0, 3.0, 0.5, -0.5]], device=dev)
+    ids, w = ops.route(torch.eye(8, device=dev), None, x, 3)
+    ids2, w2 = ops.route_from_logits(x, None, 3)
+    assert torch.equal(ids, ids2) and torch.equal(w, w2)
+
+
+@pytest.mark.parametrize("t", [1, 2, 3, 16, 33, 257])
+def test_routing_bit_exact_vs_oracle(orc, dev, t):
+    from maxuna_b200 import ops
+
+    rng = np.random.default_rng(100 + t)
+    router = (rng.standard_normal((256, 3072)) * 0.02).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, 256).astype(np.float32)
+    x = rng.standard_normal((t, 3072)).astype(np.float32)
+    ids, w = ops.route(torch.from_numpy(router).to(dev), torch.from_numpy(bias).to(dev), torch.from_numpy(x).to(dev), 10)
+    ids_o, w_o = orc.route(router, bias, x, 10)
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), w_o.view(np.uint32))  # weights bit-exact too
+
+
+def test_routing_odd_hidden_and_ties(orc, dev):
+    from maxuna_b200 import ops
+
+    rng = np.random.default_rng(9)
+    for hidden, ne in ((200, 16), (7, 8)):
+        router = rng.standard_normal((ne, hidden)).astype(np.float32)
+        x = rng.standard_normal((5, hidden)).astype(np.float32)
+        ids, w = ops.route(torch.from_numpy(router).to(dev), None, torch.from_numpy(x).to(dev), 3)
+        ids_o, w_o = orc.route(router, None, x, 3)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+    # all-equal scores: lowest indices first, in order
+    ids, _ = ops.route_from_logits(torch.zeros(4, 256, device=dev), None, 10)
+    assert ids.cpu().numpy().tolist() == [list(range(10))] * 4
+
+
+@pytest.mark.parametrize("seq", [1, 8, 512])
+def test_combine_and_silu_mul(orc, dev, seq):
+    from maxuna_b200 import ops
+
+    rng = np.random.default_rng(seq)
+    top_k, n_out = 10, 96
+    mag = lambda shape: (10.0 ** rng.uniform(-6, 4, shape) * rng.choice([-1.0, 1.0], shape)).astype(np.float32)
+    down, w = mag((seq, top_k, n_out)), rng.uniform(0, 1, (seq, top_k)).astype(np.float32)
+    l2 = (10.0 ** rng.uniform(-6, 4, (seq, top_k, 1))).astype(np.float32)
+    td = lambda a: torch.from_numpy(a).to(dev)
+    # fixed summation order => bitwise equal to the oracle's restatement of that order
+    assert np.array_equal(ops.combine(td(down), None, td(w)).cpu().numpy().view(np.uint32),
+                          orc.combine(down, None, w).view(np.uint32))
+    assert np.array_equal(ops.combine(td(down), td(l2), td(w)).cpu().numpy().view(np.uint32),
+                          orc.combine(down, l2, w).view(np.uint32))
+    g = rng.standard_normal((seq, top_k, 64)).astype(np.float32) * 4
+    u = rng.standard_normal((seq, top_k, 64)).astype(np.float32)
+    np.testing.assert_allclose(ops.silu_mul(td(g), td(u)).cpu().numpy(), orc.silu_mul(g, u), rtol=2e-6, atol=1e-7)
+
+
+def test_map0_matches_oracle(orc, dev):
+    from maxuna_b200 import ops
+
+    for t, top_k, ne, seed in ((40, 4, 6, 0x43), (512, 10, 256, 0x52), (1000, 10, 256, 0x53), (1, 2, 4, 1)):
+        ids = orc.distinct_ids(t, top_k, ne, seed)
+        s = ops.prepare_map0(ne, torch.from_numpy(ids.astype(np.int32)).to(dev))
+        tpe, m = orc.map0(ids, ne)
+        assert np.array_equal(s.tpe().cpu().numpy().astype(np.uint32), tpe)
+        got = s.ids_map().cpu().numpy()
+        for e in range(ne):
+            assert np.array_equal(got[e, : tpe[e]], m[e, : tpe[e]])
+
+
+def _tiny_block(dev, seed=3, hidden=256, ff=256, ne=8, top_k=3, shared=True):
+    from maxuna_b200.moe import MoeBlock
+
+    return MoeBlock.random(hidden, ff, ne, top_k, seed=seed, device=dev, shared=shared, weight_std=0.25)
+
+
+def test_unfused_block_vs_oracle(orc, dev):
+    blk = _tiny_block(dev)
+    host = blk.host_layer(orc)
+    x = np.random.default_rng(4).uniform(-1, 1, (5, blk.hidden)).astype(np.float32)
+    want, ids_o, w_o = host.forward(x)
+    xd = torch.from_numpy(x).to(dev)
+    ids, w = blk.route(xd)
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+    got = blk.forward_unfused(xd).cpu().numpy()
+    assert orc.rel_l2(got, want) < 1e-3
