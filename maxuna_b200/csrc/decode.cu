@@ -1,0 +1,808 @@
+// Fused MoE block for decode batches (t <= 16 tokens per launch): routing, the
+// gate/up mat-vecs with SwiGLU, the down mat-vec, the weighted combine and the
+// shared expert in ONE persistent kernel.
+//
+// Reference semantics: `MoeBlock::forward`, src/moe.rs:73-78, with the mv_id
+// branch of `FusedExperts::forward`, src/moe.rs:221-323 (kernels
+// kernel_mul_mv_id_q4_K/q6_K_f32_v, src/ops/mv.metal:181-290, 413-504),
+// `silu_mul` (src/ops/silu_mul.metal:57-72), `combine`
+// (src/ops/combine.metal:70-97) and `SharedExpert::forward`, src/moe.rs:342-344.
+//
+// Structure (the path is HBM-bound: 70.5 MB per token at the production shape)
+//   * grid = every SM x 2 CTAs, launched cooperatively so all CTAs are resident;
+//     CTA = 1 producer warp + 4 consumer warps.
+//   * The producer streams raw super-blocks global -> shared with 1-D bulk
+//     copies (cp.async.bulk + mbarrier) through a 3-stage ring: each DISTINCT
+//     selected expert (and the shared expert) is read from HBM exactly once per
+//     call, however many tokens selected it.
+//   * Consumers decode 4/6-bit fields into f16 bit patterns in registers
+//     (the integers are placed in the f16 subnormal range, which is exact) and
+//     use mma.sync m16n8k16 with the weights as the A operand (16 rows) and the
+//     activations as B: each activation is carried as an f16 hi/lo pair in two
+//     MMA columns, so products are exact and accumulation is f32.  Sub-block
+//     scales are applied to the f32 accumulator fragments; the Q4_K "min" term
+//     and the Q6_K "-32" offset are one extra MMA per super-block against
+//     per-sub-block activation sums.
+//   * Work units (8 gate+8 up rows, or 16 down rows, of one expert) are split
+//     contiguously over CTAs; the K dimension of a unit is split over the four
+//     consumer warps and reduced in shared memory in a fixed order.
+//   * Phases are separated by bounded grid barriers; the producer runs ahead of
+//     them (weights do not depend on them), which keeps HBM busy across phases.
+//   * The down projection writes weighted partial rows; the CTA that delivers
+//     the last partial of a (token, 16-row tile) sums the K+1 partials in slot
+//     order, so the result is deterministic without float atomics.
+#include "fused.cuh"
+#include "kquant.cuh"
+#include "route_math.cuh"
+
+namespace {
+
+constexpr int CW = 4;                      // consumer warps
+constexpr int DEC_THREADS = 32 * (CW + 1); // + producer warp
+constexpr int NSTAGE = 3;
+constexpr int NTOK = 2;         // tokens per pass over an expert's weights
+constexpr int NCOL = 2 * NTOK;  // MMA columns in use: (token, hi/lo)
+constexpr int DEC_MAX_T = 16;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+struct DecodeParams {
+    const float *x;
+    float *out;
+    uint32_t *ids_out;
+    float *w_out;
+    const float *router, *bias;
+    const uint8_t *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+    int t, hidden, ff, n_expert, top_k;
+    float scale;
+    int norm, has_shared;
+    uint32_t *ctrl;   // [0..3] flag, [4] grid barrier, [5] exit count, [16..] tile counters [t][hidden/16]
+    float *logits;    // [t][n_expert]
+    __half *act_hl;   // [t*(top_k+1)][2][ff], k permuted within groups of 8
+    float *ypart;     // [t*(top_k+1)][hidden]
+};
+
+// Shared-memory layout (bytes), computed identically on host and device.
+struct DecLayout {
+    int stage_bytes, xs, ss;
+    int o_ring, o_xc, o_s, o_red, o_bar, o_ids, o_w, o_cnt, o_off, o_plist, o_act, o_ppre, total;
+    __host__ __device__ DecLayout(int hidden, int ff, int n_expert, int t, int top_k) {
+        const int row4 = hidden / QK_K * Q4K_BYTES, row6 = ff / QK_K * Q6K_BYTES;
+        int sb = 16 * row4 > 16 * row6 ? 16 * row4 : 16 * row6;
+        stage_bytes = (sb + 127) / 128 * 128;
+        const int kmax = hidden > ff ? hidden : ff;
+        xs = kmax + 32; // halfs per column (+64 B so two columns land in different bank halves)
+        int nsb = hidden / 32 > ff / 16 ? hidden / 32 : ff / 16;
+        ss = (nsb + 15) / 16 * 16;
+        const int tk = t * top_k;
+        int o = 0;
+        o_ring = o; o += NSTAGE * stage_bytes;
+        o_xc = o;
+        int xc_bytes = NCOL * xs * 2;
+        const int sel_bytes = CW * 2 * n_expert * 4; // routing scratch aliases the activation cache
+        if (sel_bytes > xc_bytes) xc_bytes = sel_bytes;
+        o += (xc_bytes + 15) / 16 * 16;
+        o_s = o; o += NCOL * ss * 2;
+        o_red = o; o += 2 * CW * 16 * NCOL * 4;
+        o_bar = o; o += 64;
+        o_ids = o; o += tk * 4;
+        o_w = o; o += tk * 4;
+        o_cnt = o; o += n_expert * 4;
+        o_off = o; o += (n_expert + 2) / 2 * 2 * 2;
+        o_plist = o; o += (tk + 1) / 2 * 2 * 2;
+        o_act = o; o += (tk + 2) / 2 * 2 * 2;
+        o_ppre = o; o += (tk + 2) / 2 * 2 * 2;
+        total = (o + 15) / 16 * 16;
+    }
+};
+
+// ---- PTX helpers -------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after SPIN_LIMIT polls, records the fact and carries on
+// (results are then invalid, but every loop in the kernel stays finite).
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *ctrl, uint32_t where) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return;
+    if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
+        ctrl[1] = where;
+        ctrl[2] = blockIdx.x;
+    }
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t ld_acquire(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Grid-wide barrier among the consumer threads of all CTAs (thread 0 of each
+// CTA arrives).  `target` = arrivals expected so far in this launch.
+__device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, int tid) {
+    __threadfence();
+    bar_sync(1, CW * 32);
+    if (tid == 0) {
+        atomicAdd(&ctrl[4], 1u);
+        uint32_t i = 0;
+        while (ld_acquire(&ctrl[4]) < target) {
+            __nanosleep(32);
+            if (++i > SPIN_LIMIT) {
+                if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
+                    ctrl[1] = 0x100u + target;
+                    ctrl[2] = blockIdx.x;
+                }
+                break;
+            }
+        }
+        __threadfence();
+    }
+    bar_sync(1, CW * 32);
+}
+
+// Position of element i of an aligned group of 8 activations: [x0 x2 x1 x3 x4 x6 x5 x7]
+// (bits 0 and 1 swapped), which puts each lane's MMA B fragment in consecutive bytes.
+__device__ __forceinline__ int perm8(int i) { return (i & ~3) | ((i & 1) << 1) | ((i >> 1) & 1); }
+
+// One work unit: a row tile of one expert for one pass of <= NTOK tokens.
+struct Unit {
+    int shared;  // 1 = shared expert
+    int expert;  // routed: expert id
+    int qpass;   // pass index (unique per (expert, pass) within shared / routed)
+    int tile;
+    int n_tok;
+    int tok[NTOK], pair[NTOK];
+};
+
+struct Tables {
+    const uint32_t *ids; // [t*K]
+    const float *w;
+    const uint16_t *off, *plist, *act, *ppre;
+    int n_active, routed_passes, shared_passes;
+};
+
+__device__ __forceinline__ void unit_range(int n_units, int &u0, int &u1) {
+    u0 = (int)((long long)blockIdx.x * n_units / gridDim.x);
+    u1 = (int)((long long)(blockIdx.x + 1) * n_units / gridDim.x);
+}
+
+// Resolve routed pass index -> (active index, pass within expert).
+__device__ __forceinline__ int find_active(const uint16_t *ppre, int n_active, int q) {
+    int lo = 0, hi = n_active - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (ppre[mid] <= q) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ Unit make_unit(const DecodeParams &P, const Tables &T, int shared, int u, int tiles) {
+    Unit U;
+    U.shared = shared;
+    U.qpass = u / tiles;
+    U.tile = u - U.qpass * tiles;
+    if (shared) {
+        U.expert = 0;
+        U.n_tok = min(NTOK, P.t - U.qpass * NTOK);
+        for (int i = 0; i < NTOK; i++) {
+            U.tok[i] = min(U.qpass * NTOK + i, P.t - 1);
+            U.pair[i] = U.tok[i] * (P.top_k + 1) + P.top_k;
+        }
+    } else {
+        const int a = find_active(T.ppre, T.n_active, U.qpass);
+        U.expert = T.act[a];
+        const int r = U.qpass - T.ppre[a];
+        const int o = T.off[U.expert], n = T.off[U.expert + 1] - o;
+        U.n_tok = min(NTOK, n - r * NTOK);
+        for (int i = 0; i < NTOK; i++) {
+            const int p = T.plist[o + min(r * NTOK + i, n - 1)];
+            U.tok[i] = p / P.top_k;
+            U.pair[i] = U.tok[i] * (P.top_k + 1) + (p - U.tok[i] * P.top_k);
+        }
+    }
+    return U;
+}
+
+// ---- activation cache staging --------------------------------------------------
+// Phase 1: x rows (f32, global) -> f16 hi/lo columns, permuted; 32-wide sums S.
+__device__ __forceinline__ void stage_x(const DecodeParams &P, const Unit &U, __half *xc, __half *sh, int xs,
+                                        int ss, int tid) {
+    const int groups = P.hidden / 8;
+    for (int i = tid; i < U.n_tok * groups; i += CW * 32) {
+        const int tk = i / groups, g8 = i - tk * groups;
+        const float *src = P.x + (size_t)U.tok[tk] * P.hidden + g8 * 8;
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(src + 4));
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        __align__(16) __half hi[8], lo[8];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const __half h = __float2half_rn(v[j]);
+            hi[perm8(j)] = h;
+            lo[perm8(j)] = __float2half_rn(v[j] - __half2float(h));
+            sum += v[j];
+        }
+        *reinterpret_cast<uint4 *>(xc + (2 * tk) * xs + g8 * 8) = *reinterpret_cast<const uint4 *>(hi);
+        *reinterpret_cast<uint4 *>(xc + (2 * tk + 1) * xs + g8 * 8) = *reinterpret_cast<const uint4 *>(lo);
+        // 32-wide sub-block sum = 4 consecutive groups = 4 consecutive lanes (groups % 4 == 0)
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((g8 & 3) == 0) {
+            const __half h = __float2half_rn(sum);
+            sh[(2 * tk) * ss + (g8 >> 2)] = h;
+            sh[(2 * tk + 1) * ss + (g8 >> 2)] = __float2half_rn(sum - __half2float(h));
+        }
+    }
+}
+
+// Phase 2: SwiGLU activations (f16 hi/lo, already permuted, global/L2) -> cache; 16-wide sums.
+__device__ __forceinline__ void stage_act(const DecodeParams &P, const Unit &U, __half *xc, __half *sh, int xs,
+                                          int ss, int tid) {
+    const int groups = P.ff / 8;
+    for (int i = tid; i < U.n_tok * groups; i += CW * 32) {
+        const int tk = i / groups, g8 = i - tk * groups;
+        const __half *src = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + g8 * 8;
+        const uint4 hi = __ldcg(reinterpret_cast<const uint4 *>(src));
+        const uint4 lo = __ldcg(reinterpret_cast<const uint4 *>(src + P.ff));
+        *reinterpret_cast<uint4 *>(xc + (2 * tk) * xs + g8 * 8) = hi;
+        *reinterpret_cast<uint4 *>(xc + (2 * tk + 1) * xs + g8 * 8) = lo;
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&hi);
+        const __half2 *l2 = reinterpret_cast<const __half2 *>(&lo);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 a = __half22float2(h2[j]), b = __half22float2(l2[j]);
+            sum += (a.x + b.x) + (a.y + b.y);
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if ((g8 & 1) == 0) {
+            const __half h = __float2half_rn(sum);
+            sh[(2 * tk) * ss + (g8 >> 1)] = h;
+            sh[(2 * tk + 1) * ss + (g8 >> 1)] = __float2half_rn(sum - __half2float(h));
+        }
+    }
+}
+
+// ---- per-unit math ---------------------------------------------------------------
+// 16 Q4_K rows (8 gate + 8 up) x the blocks of this warp.  acc: rows g / g+8, columns 2t, 2t+1.
+__device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
+                                         const __half *xcol, const __half *scol, bool colv, float (&acc)[4]) {
+    const uint8_t *rg = stage + g * row_bytes;
+    const uint8_t *rG = rg + 8 * row_bytes;
+    for (int b = warp; b < nb; b += CW) {
+        const uint8_t *bg = rg + b * Q4K_BYTES, *bG = rG + b * Q4K_BYTES;
+        const uint4 hg = *reinterpret_cast<const uint4 *>(bg);
+        const uint4 hG = *reinterpret_cast<const uint4 *>(bG);
+        const float dg = lmoe_h2f((uint16_t)(hg.x & 0xffff)) * 16777216.f;
+        const float mg = lmoe_h2f((uint16_t)(hg.x >> 16)) * 16777216.f;
+        const float dG = lmoe_h2f((uint16_t)(hG.x & 0xffff)) * 16777216.f;
+        const float mG = lmoe_h2f((uint16_t)(hG.x >> 16)) * 16777216.f;
+        uint32_t scg[2], mng[2], scG[2], mnG[2];
+        q4k_unpack_scales(hg.y, hg.z, hg.w, scg[0], scg[1], mng[0], mng[1]);
+        q4k_unpack_scales(hG.y, hG.z, hG.w, scG[0], scG[1], mnG[0], mnG[1]);
+        // min term: one MMA, A = the 8 six-bit mins of each row, B = 32-wide activation sums
+        float cm[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+            const uint32_t ma = __byte_perm(t < 2 ? mng[0] : mng[1], 0u, sel);
+            const uint32_t mA = __byte_perm(t < 2 ? mnG[0] : mnG[1], 0u, sel);
+            const uint32_t sb = colv ? *reinterpret_cast<const uint32_t *>(scol + 8 * b + 2 * t) : 0u;
+            mma16816(cm, ma, mA, 0u, 0u, sb, 0u);
+        }
+        float ab[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint2 wg = *reinterpret_cast<const uint2 *>(bg + 16 + 32 * j + 8 * t);
+            const uint2 wG = *reinterpret_cast<const uint2 *>(bG + 16 + 32 * j + 8 * t);
+            uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = make_uint4(0u, 0u, 0u, 0u);
+            if (colv) {
+                xl = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 8 * t);
+                xh = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
+            }
+            float fl[4] = {0.f, 0.f, 0.f, 0.f}, fh[4] = {0.f, 0.f, 0.f, 0.f};
+            mma16816(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, (wg.x >> 8) & 0x000F000Fu, (wG.x >> 8) & 0x000F000Fu,
+                     xl.x, xl.y);
+            mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, (wg.y >> 8) & 0x000F000Fu, (wG.y >> 8) & 0x000F000Fu,
+                     xl.z, xl.w);
+            mma16816(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, (wg.x >> 8) & 0x00F000F0u, (wG.x >> 8) & 0x00F000F0u,
+                     xh.x, xh.y);
+            mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, (wg.y >> 8) & 0x00F000F0u, (wG.y >> 8) & 0x00F000F0u,
+                     xh.z, xh.w);
+            const uint32_t wsg = scg[j >> 1] >> (16 * (j & 1)), wsG = scG[j >> 1] >> (16 * (j & 1));
+            const float s0g = (float)(wsg & 0xff), s1g = (float)((wsg >> 8) & 0xff) * 0.0625f;
+            const float s0G = (float)(wsG & 0xff), s1G = (float)((wsG >> 8) & 0xff) * 0.0625f;
+            ab[0] += s0g * fl[0] + s1g * fh[0];
+            ab[1] += s0g * fl[1] + s1g * fh[1];
+            ab[2] += s0G * fl[2] + s1G * fh[2];
+            ab[3] += s0G * fl[3] + s1G * fh[3];
+        }
+        acc[0] += dg * ab[0] - mg * cm[0];
+        acc[1] += dg * ab[1] - mg * cm[1];
+        acc[2] += dG * ab[2] - mG * cm[2];
+        acc[3] += dG * ab[3] - mG * cm[3];
+    }
+}
+
+__device__ __forceinline__ uint32_t lds32_a2(const uint8_t *p) {
+    // p is 2-byte aligned; both neighbouring words are inside the staged tile
+    if (reinterpret_cast<uintptr_t>(p) & 2) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t *>(p - 2);
+        const uint32_t hi = *reinterpret_cast<const uint32_t *>(p + 2);
+        return __byte_perm(lo, hi, 0x5432);
+    }
+    return *reinterpret_cast<const uint32_t *>(p);
+}
+
+__device__ __forceinline__ uint32_t sc_pair_half2(const int8_t *p) {
+    const __half2 h = __floats2half2_rn((float)p[0], (float)p[1]);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// 16 Q6_K rows x the blocks of this warp.
+__device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
+                                         const __half *xcol, const __half *scol, bool colv, float (&acc)[4]) {
+    const uint8_t *rg = stage + g * row_bytes;
+    const uint8_t *rG = rg + 8 * row_bytes;
+    for (int b = warp; b < nb; b += CW) {
+        const uint8_t *bg = rg + b * Q6K_BYTES, *bG = rG + b * Q6K_BYTES;
+        const int8_t *scg = reinterpret_cast<const int8_t *>(bg + 192);
+        const int8_t *scG = reinterpret_cast<const int8_t *>(bG + 192);
+        const float dg = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bg + 208));
+        const float dG = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bG + 208));
+        // "-32" offset: one MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
+        float co[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            uint32_t s0 = 0u, s1 = 0u;
+            if (colv) {
+                s0 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t);
+                s1 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t + 8);
+            }
+            mma16816(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
+                     sc_pair_half2(scG + 2 * t + 8), s0, s1);
+        }
+        float ab[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int l0 = 16 * c + 4 * t;
+                const uint32_t qa_g = lds32_a2(bg + 64 * n + l0), qb_g = lds32_a2(bg + 64 * n + 32 + l0);
+                const uint32_t qh_g = lds32_a2(bg + 128 + 32 * n + l0);
+                const uint32_t qa_G = lds32_a2(bG + 64 * n + l0), qb_G = lds32_a2(bG + 64 * n + 32 + l0);
+                const uint32_t qh_G = lds32_a2(bG + 128 + 32 * n + l0);
+                const __half *xp = xcol + 256 * b + 128 * n + 16 * c + 4 * t;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    // group i: q1 (ql lo | qh 0-1), q2 (ql+32 lo | qh 2-3), q3 (ql hi | qh 4-5), q4 (ql+32 hi | qh 6-7)
+                    const uint32_t qg = (i & 1) ? qb_g : qa_g, qG = (i & 1) ? qb_G : qa_G;
+                    const uint32_t hg = (i & 1) ? (qh_g << 2) : (qh_g << 4), hG = (i & 1) ? (qh_G << 2) : (qh_G << 4);
+                    const uint32_t hg8 = (i & 1) ? (qh_g >> 6) : (qh_g >> 4), hG8 = (i & 1) ? (qh_G >> 6) : (qh_G >> 4);
+                    const uint32_t ml = (i & 2) ? 0x00F000F0u : 0x000F000Fu, mh = (i & 2) ? 0x03000300u : 0x00300030u;
+                    const uint32_t a0 = (qg & ml) | (hg & mh), a1 = (qG & ml) | (hG & mh);
+                    const uint32_t a2 = ((qg >> 8) & ml) | (hg8 & mh), a3 = ((qG >> 8) & ml) | (hG8 & mh);
+                    uint2 xv = make_uint2(0u, 0u);
+                    if (colv) xv = *reinterpret_cast<const uint2 *>(xp + 32 * i);
+                    float f[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma16816(f, a0, a1, a2, a3, xv.x, xv.y);
+                    const float pw = (i & 2) ? 0.0625f : 1.0f;
+                    const float sg = (float)scg[8 * n + 2 * i + c] * pw, sG = (float)scG[8 * n + 2 * i + c] * pw;
+                    ab[0] += sg * f[0];
+                    ab[1] += sg * f[1];
+                    ab[2] += sG * f[2];
+                    ab[3] += sG * f[3];
+                }
+            }
+        }
+        acc[0] += dg * (ab[0] * 16777216.f - 32.f * co[0]);
+        acc[1] += dg * (ab[1] * 16777216.f - 32.f * co[1]);
+        acc[2] += dG * (ab[2] * 16777216.f - 32.f * co[2]);
+        acc[3] += dG * (ab[3] * 16777216.f - 32.f * co[3]);
+    }
+}
+
+// ---- the kernel ---------------------------------------------------------------------
+__global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid_constant__ DecodeParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const DecLayout L(P.hidden, P.ff, P.n_expert, P.t, P.top_k);
+    uint8_t *ring = smem + L.o_ring;
+    __half *xc = reinterpret_cast<__half *>(smem + L.o_xc);
+    __half *sh = reinterpret_cast<__half *>(smem + L.o_s);
+    float *red = reinterpret_cast<float *>(smem + L.o_red);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.o_bar);
+    uint64_t *empty = full + NSTAGE;
+    uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + L.o_ids);
+    float *w_s = reinterpret_cast<float *>(smem + L.o_w);
+    uint32_t *cnt_s = reinterpret_cast<uint32_t *>(smem + L.o_cnt);
+    uint16_t *off_s = reinterpret_cast<uint16_t *>(smem + L.o_off);
+    uint16_t *plist_s = reinterpret_cast<uint16_t *>(smem + L.o_plist);
+    uint16_t *act_s = reinterpret_cast<uint16_t *>(smem + L.o_act);
+    uint16_t *ppre_s = reinterpret_cast<uint16_t *>(smem + L.o_ppre);
+    __shared__ int s_n_active, s_routed_passes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x;
+    const int K = P.top_k, E = P.n_expert;
+    const int nb4 = P.hidden / QK_K, nb6 = P.ff / QK_K;
+    const int row4 = nb4 * Q4K_BYTES, row6 = nb6 * Q6K_BYTES;
+    const int tiles1 = P.ff / 8, tiles2 = P.hidden / 16;
+    const int shared_passes = P.has_shared ? (P.t + NTOK - 1) / NTOK : 0;
+    const size_t gexp = (size_t)P.ff * row4, dexp = (size_t)P.hidden * row6;
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == CW) {
+        // ===================== producer warp (lane 0 issues) =====================
+        uint32_t n = 0;
+        auto fill = [&](const uint8_t *src0, const uint8_t *src1, uint32_t bytes_each) {
+            const int s = n % NSTAGE;
+            const uint32_t r = n / NSTAGE;
+            mbar_wait(&empty[s], (r & 1) ^ 1, P.ctrl, 0x10);
+            uint8_t *dst = ring + (size_t)s * L.stage_bytes;
+            mbar_expect_tx(&full[s], src1 ? 2 * bytes_each : bytes_each);
+            bulk_g2s(dst, src0, bytes_each, &full[s]);
+            if (src1) bulk_g2s(dst + bytes_each, src1, bytes_each, &full[s]);
+            n++;
+        };
+        int u0, u1, u = 0;
+        // phase 1, shared expert: known before routing.  Only as many fills as the ring
+        // holds may be issued before the routing tables exist (consumers drain the ring
+        // only after they have built them).
+        unit_range(shared_passes * tiles1, u0, u1);
+        if (lane == 0) {
+            for (u = u0; u < u1 && u < u0 + NSTAGE; u++) {
+                const int tile = u % tiles1;
+                fill(P.sh_gate + (size_t)tile * 8 * row4, P.sh_up + (size_t)tile * 8 * row4, 8 * row4);
+            }
+        }
+        __syncwarp();
+        bar_sync(2, DEC_THREADS); // routing tables are ready
+        if (lane == 0) {
+            for (; u < u1; u++) {
+                const int tile = u % tiles1;
+                fill(P.sh_gate + (size_t)tile * 8 * row4, P.sh_up + (size_t)tile * 8 * row4, 8 * row4);
+            }
+            const int n_active = s_n_active, routed_passes = s_routed_passes;
+            unit_range(routed_passes * tiles1, u0, u1);
+            for (u = u0; u < u1; u++) {
+                const int q = u / tiles1, tile = u - q * tiles1;
+                const int e = act_s[find_active(ppre_s, n_active, q)];
+                fill(P.gate + e * gexp + (size_t)tile * 8 * row4, P.up + e * gexp + (size_t)tile * 8 * row4, 8 * row4);
+            }
+            // phase 2 (weights do not depend on the grid barrier: keep streaming)
+            unit_range(shared_passes * tiles2, u0, u1);
+            for (u = u0; u < u1; u++) fill(P.sh_down + (size_t)(u % tiles2) * 16 * row6, nullptr, 16 * row6);
+            unit_range(routed_passes * tiles2, u0, u1);
+            for (u = u0; u < u1; u++) {
+                const int q = u / tiles2, tile = u - q * tiles2;
+                const int e = act_s[find_active(ppre_s, n_active, q)];
+                fill(P.down + e * dexp + (size_t)tile * 16 * row6, nullptr, 16 * row6);
+            }
+        }
+        return;
+    }
+
+    // ========================= consumer warps =========================
+    const int g = lane >> 2, t4 = lane & 3;
+
+    // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
+    {
+        const int ntt = (P.t + 3) / 4;
+        const int H = P.hidden;
+        for (int q = blockIdx.x * CW + warp; q < E * ntt; q += G * CW) {
+            const int e = q / ntt, t0 = (q - e * ntt) * 4;
+            const float *wr = P.router + (size_t)e * H;
+            float a[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.f;
+#pragma unroll 4
+            for (int base = 4 * lane; base < H; base += 128) {
+                const float4 wv = __ldg(reinterpret_cast<const float4 *>(wr + base));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (t0 + i < P.t) {
+                        const float4 xv = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)(t0 + i) * H + base));
+                        a[i][0] = __fmaf_rn(xv.x, wv.x, a[i][0]);
+                        a[i][1] = __fmaf_rn(xv.y, wv.y, a[i][1]);
+                        a[i][2] = __fmaf_rn(xv.z, wv.z, a[i][2]);
+                        a[i][3] = __fmaf_rn(xv.w, wv.w, a[i][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float v = lmoe_router_fold(a[i][0], a[i][1], a[i][2], a[i][3]);
+                if (lane == 0 && t0 + i < P.t) P.logits[(size_t)(t0 + i) * E + e] = v;
+            }
+        }
+    }
+    grid_barrier(P.ctrl, (uint32_t)G, tid);
+
+    // ---- phase 0b: selection, redundantly in every CTA (scratch aliases the activation cache) ----
+    {
+        float *probs = reinterpret_cast<float *>(xc) + (size_t)warp * 2 * E;
+        float *sel = probs + E;
+        for (int tok = warp; tok < P.t; tok += CW) {
+            for (int e = lane; e < E; e += 32) {
+                const float p = lmoe_sigmoid_fixed(__ldcg(P.logits + (size_t)tok * E + e));
+                probs[e] = p;
+                sel[e] = P.bias ? __fadd_rn(p, __ldg(P.bias + e)) : p;
+            }
+            __syncwarp();
+            lmoe_warp_select(sel, probs, E, K, P.scale, P.norm, ids_s + tok * K, w_s + tok * K, lane);
+            __syncwarp();
+        }
+        for (int e = tid; e < E; e += CW * 32) cnt_s[e] = 0;
+    }
+    bar_sync(1, CW * 32);
+    if (blockIdx.x == 0) {
+        for (int i = tid; i < P.t * K; i += CW * 32) {
+            if (P.ids_out) P.ids_out[i] = ids_s[i];
+            if (P.w_out) P.w_out[i] = w_s[i];
+        }
+    }
+    // ---- phase 0c: per-expert token lists ----
+    for (int i = tid; i < P.t * K; i += CW * 32) atomicAdd(&cnt_s[ids_s[i]], 1u);
+    bar_sync(1, CW * 32);
+    if (warp == 0) {
+        // exclusive scans over experts: list offsets, active index, pass prefix
+        const int per = (E + 31) / 32;
+        const int e0 = lane * per, e1 = min(E, e0 + per);
+        int c_sum = 0, a_sum = 0, p_sum = 0;
+        for (int e = e0; e < e1; e++) {
+            const int c = (int)cnt_s[e];
+            c_sum += c;
+            a_sum += c > 0;
+            p_sum += (c + NTOK - 1) / NTOK;
+        }
+        int c_pre = c_sum, a_pre = a_sum, p_pre = p_sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int c2 = __shfl_up_sync(0xffffffffu, c_pre, o), a2 = __shfl_up_sync(0xffffffffu, a_pre, o);
+            const int p2 = __shfl_up_sync(0xffffffffu, p_pre, o);
+            if (lane >= o) { c_pre += c2; a_pre += a2; p_pre += p2; }
+        }
+        const int c_tot = __shfl_sync(0xffffffffu, c_pre, 31), a_tot = __shfl_sync(0xffffffffu, a_pre, 31);
+        const int p_tot = __shfl_sync(0xffffffffu, p_pre, 31);
+        c_pre -= c_sum; a_pre -= a_sum; p_pre -= p_sum;
+        for (int e = e0; e < e1; e++) {
+            const int c = (int)cnt_s[e];
+            off_s[e] = (uint16_t)c_pre;
+            if (c > 0) {
+                act_s[a_pre] = (uint16_t)e;
+                ppre_s[a_pre] = (uint16_t)p_pre;
+                a_pre++;
+                p_pre += (c + NTOK - 1) / NTOK;
+            }
+            c_pre += c;
+        }
+        if (lane == 31) {
+            off_s[E] = (uint16_t)c_tot;
+            ppre_s[a_tot] = (uint16_t)p_tot;
+            s_n_active = a_tot;
+            s_routed_passes = p_tot;
+        }
+    }
+    bar_sync(1, CW * 32);
+    for (int e = tid; e < E; e += CW * 32) cnt_s[e] = 0;
+    bar_sync(1, CW * 32);
+    for (int i = tid; i < P.t * K; i += CW * 32) {
+        const uint32_t e = ids_s[i];
+        const uint32_t pos = atomicAdd(&cnt_s[e], 1u);
+        plist_s[off_s[e] + pos] = (uint16_t)i;
+    }
+    __threadfence_block();
+    bar_sync(1, CW * 32);
+    bar_sync(2, DEC_THREADS); // release the producer: the routing tables are complete
+
+    Tables T{ids_s, w_s, off_s, plist_s, act_s, ppre_s, s_n_active, s_routed_passes, shared_passes};
+
+    uint32_t n = 0; // ring fill counter, same sequence as the producer's
+    int xkey = -1;
+    int redbuf = 0;
+
+    // ---- phases 1 and 2 ----
+    for (int phase = 1; phase <= 2; phase++) {
+        const int tiles = phase == 1 ? tiles1 : tiles2;
+        for (int kind = 0; kind < 2; kind++) { // shared units first, then routed
+            const int shared = kind == 0;
+            int u0, u1;
+            unit_range((shared ? shared_passes : T.routed_passes) * tiles, u0, u1);
+            for (int u = u0; u < u1; u++) {
+                const Unit U = make_unit(P, T, shared, u, tiles);
+                const int key = (phase << 24) | (shared << 23) | U.qpass;
+                if (key != xkey) {
+                    bar_sync(1, CW * 32); // everyone is done with the previous contents
+                    if (phase == 1) stage_x(P, U, xc, sh, L.xs, L.ss, tid);
+                    else stage_act(P, U, xc, sh, L.xs, L.ss, tid);
+                    xkey = key;
+                    bar_sync(1, CW * 32);
+                }
+                const int s = n % NSTAGE;
+                mbar_wait(&full[s], (n / NSTAGE) & 1, P.ctrl, 0x20 + phase);
+                const uint8_t *stage = ring + (size_t)s * L.stage_bytes;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const bool colv = g < 2 * U.n_tok;
+                if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + g * L.xs, sh + g * L.ss, colv, acc);
+                else unit_q6k(stage, row6, nb6, warp, g, t4, xc + g * L.xs, sh + g * L.ss, colv, acc);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                n++;
+                // K-split partials -> shared memory
+                float *rb = red + redbuf * (CW * 16 * NCOL);
+                if (t4 < NTOK) {
+                    float *r0 = rb + (warp * 16 + g) * NCOL + 2 * t4;
+                    r0[0] = acc[0]; r0[1] = acc[1];
+                    r0[8 * NCOL] = acc[2]; r0[8 * NCOL + 1] = acc[3];
+                }
+                bar_sync(1, CW * 32);
+                if (warp == 0) {
+                    if (phase == 1) {
+                        // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
+                        const int tk = lane >> 3, r = lane & 7;
+                        if (tk < U.n_tok) {
+                            float gv = 0.f, uv = 0.f;
+#pragma unroll
+                            for (int w = 0; w < CW; w++) {
+                                gv += rb[(w * 16 + r) * NCOL + 2 * tk];
+                                gv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
+                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk];
+                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk + 1];
+                            }
+                            const float sv = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+                            const float av = __fmul_rn(sv, uv);
+                            const __half h = __float2half_rn(av);
+                            __half *dst = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + U.tile * 8 + perm8(r);
+                            dst[0] = h;
+                            dst[P.ff] = __float2half_rn(av - __half2float(h));
+                        }
+                    } else {
+                        // weighted partial rows, then the last arriver of each (token, tile) combines
+                        const int tk = lane >> 4, r = lane & 15;
+                        const bool valid = tk < U.n_tok;
+                        const int row = U.tile * 16 + r;
+                        if (valid) {
+                            float yv = 0.f;
+#pragma unroll
+                            for (int w = 0; w < CW; w++) {
+                                yv += rb[(w * 16 + r) * NCOL + 2 * tk];
+                                yv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
+                            }
+                            const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
+                            if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
+                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + row, yv);
+                            __threadfence();
+                        }
+                        __syncwarp();
+                        uint32_t old = 0;
+                        if (valid && r == 0) old = atomicAdd(&P.ctrl[16 + U.tok[tk] * tiles2 + U.tile], 1u);
+                        old = __shfl_sync(0xffffffffu, old, lane & 16);
+                        if (valid && old == (uint32_t)(K + P.has_shared - 1)) {
+                            __threadfence();
+                            const float *yp = P.ypart + (size_t)U.tok[tk] * (K + 1) * P.hidden + row;
+                            float sum = 0.f;
+                            for (int sl = 0; sl < K + P.has_shared; sl++) sum = __fadd_rn(sum, __ldcg(yp + (size_t)sl * P.hidden));
+                            P.out[(size_t)U.tok[tk] * P.hidden + row] = sum;
+                        }
+                    }
+                }
+                redbuf ^= 1;
+            }
+        }
+        if (phase == 1) grid_barrier(P.ctrl, (uint32_t)(2 * G), tid);
+    }
+
+    // ---- exit: the last CTA leaves the control words zeroed for the next call ----
+    bar_sync(1, CW * 32);
+    if (tid == 0) {
+        __threadfence();
+        const uint32_t old = atomicAdd(&P.ctrl[5], 1u);
+        if (old == (uint32_t)(G - 1)) {
+            for (int i = 0; i < P.t * tiles2; i++) P.ctrl[16 + i] = 0u;
+            P.ctrl[4] = 0u;
+            P.ctrl[5] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+} // namespace
+
+// ---- host side ------------------------------------------------------------------------
+size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k) {
+    size_t o = 65536; // control words
+    o += lmoe_align_up((size_t)t * n_expert * 4, 256);
+    o += lmoe_align_up((size_t)t * (top_k + 1) * 2 * ff * 2, 256);
+    o += lmoe_align_up((size_t)t * (top_k + 1) * hidden * 4, 256);
+    return o;
+}
+
+int decode_max_tokens() { return DEC_MAX_T; }
+
+lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
+                              float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    const int H = (int)Ly->hidden, F = (int)Ly->expert_ff, E = (int)Ly->n_expert, K = (int)Ly->top_k;
+    if (Ly->gate->dtype != LMOE_Q4_K || Ly->down->dtype != LMOE_Q6_K)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the fused decode kernel is built for Q4_K gate/up and Q6_K down stacks");
+    if (t < 1 || t > DEC_MAX_T) return lmoe_fail(LMOE_ERR_INVALID, "decode launch takes 1..%d tokens, got %d", DEC_MAX_T, t);
+    if (H % 128 || F % 16 || 16 + t * (H / 16) > 16384)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode needs hidden %% 128 == 0, expert_ff %% 16 == 0 and t*hidden/16 <= 16368");
+    if (t * K > 65535) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "t*top_k too large");
+    const DecLayout L(H, F, E, t, K);
+    int dev = 0, sms = 0, max_smem = 0;
+    LMOE_CUDA(cudaGetDevice(&dev));
+    LMOE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    LMOE_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (L.total > max_smem)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode needs %d bytes of shared memory per CTA, device allows %d",
+                         L.total, max_smem);
+    if (workspace_bytes < decode_workspace_bytes(t, H, F, E, K) || !workspace)
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "decode workspace needs %zu bytes, got %zu",
+                         decode_workspace_bytes(t, H, F, E, K), workspace_bytes);
+    LMOE_CUDA(cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+    int occ = 0;
+    LMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, moe_decode_kernel, DEC_THREADS, L.total));
+    if (occ < 1) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode kernel does not fit on an SM");
+    if (occ > 2) occ = 2;
+
+    DecodeParams P;
+    P.x = x; P.out = out; P.ids_out = ids_out; P.w_out = w_out;
+    P.router = Ly->router; P.bias = Ly->bias;
+    P.gate = Ly->gate->blocks(); P.up = Ly->up->blocks(); P.down = Ly->down->blocks();
+    P.has_shared = Ly->sh_gate != nullptr;
+    P.sh_gate = P.has_shared ? Ly->sh_gate->blocks() : nullptr;
+    P.sh_up = P.has_shared ? Ly->sh_up->blocks() : nullptr;
+    P.sh_down = P.has_shared ? Ly->sh_down->blocks() : nullptr;
+    P.t = t; P.hidden = H; P.ff = F; P.n_expert = E; P.top_k = K;
+    P.scale = Ly->scale; P.norm = Ly->norm;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    P.ctrl = reinterpret_cast<uint32_t *>(ws);
+    size_t o = 65536;
+    P.logits = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * E * 4, 256);
+    P.act_hl = reinterpret_cast<__half *>(ws + o); o += lmoe_align_up((size_t)t * (K + 1) * 2 * F * 2, 256);
+    P.ypart = reinterpret_cast<float *>(ws + o);
+    void *args[] = {&P};
+    LMOE_CUDA(cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(occ * sms), dim3(DEC_THREADS), args,
+                                          (size_t)L.total, stream));
+    return LMOE_OK;
+}

@@ -1,23 +1,102 @@
 // Whole-block entry points (`MoeBlock::forward`, src/moe.rs:73-78).
 #include "fused.cuh"
 
-#define NOT_YET(name) return lmoe_fail(LMOE_ERR_UNSUPPORTED, name " is not built yet")
+// decode.cu
+size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k);
+int decode_max_tokens();
+lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
+                              float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// prefill.cu
+size_t prefill_workspace_bytes(const lmoe_layer *Ly, int64_t t);
+lmoe_status launch_moe_prefill(const lmoe_layer *Ly, const float *x, int64_t t, float *out, uint32_t *ids_out,
+                               float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 
-extern "C" size_t lmoe_layer_workspace_bytes(const lmoe_layer *, int64_t) { return 256; }
-extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *, const float *, int64_t, float *, uint32_t *,
-                                               float *, void *, size_t, void *) { NOT_YET("moe_forward_decode"); }
-extern "C" lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *, const float *, int64_t, float *, uint32_t *,
-                                                float *, void *, size_t, void *) { NOT_YET("moe_forward_prefill"); }
-extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *, const float *, int64_t, float *, uint32_t *,
-                                             float *, void *, size_t, void *) { NOT_YET("moe_forward_host"); }
-extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *, const float *, const uint32_t *, const float *,
-                                                 int64_t, float *, void *, size_t, void *) { NOT_YET("experts_forward_rows"); }
-extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *, const float *, int64_t, float *, void *, size_t,
-                                           void *) { NOT_YET("shared_forward"); }
-extern "C" int32_t lmoe_mm_id_supported(int32_t, int64_t) { return 0; }
-extern "C" size_t lmoe_mm_id_workspace_bytes(int64_t, int64_t, int64_t, int64_t) { return 0; }
-extern "C" lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *, const float *, int64_t, int64_t, int64_t,
-                                             const uint32_t *, int64_t, int64_t, const void *, int64_t, int64_t,
-                                             int64_t, float *, void *, size_t, void *) { NOT_YET("mul_mm_id_shared"); }
-extern "C" lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *, const float *, int64_t, int64_t, int64_t,
-                                      const uint32_t *, int64_t, int64_t, float *, void *, size_t, void *) { NOT_YET("mul_mm_id"); }
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" size_t lmoe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens) {
+    if (!layer || max_tokens < 0) return 0;
+    const int tdec = (int)(max_tokens < decode_max_tokens() ? (max_tokens < 1 ? 1 : max_tokens) : decode_max_tokens());
+    size_t dec = decode_workspace_bytes(tdec, (int)layer->hidden, (int)layer->expert_ff, (int)layer->n_expert,
+                                        (int)layer->top_k);
+    size_t pre = prefill_workspace_bytes(layer, max_tokens);
+    // host-buffer calls stage x and out behind the kernel scratch
+    size_t host = 2 * lmoe_align_up((size_t)max_tokens * layer->hidden * 4, 256) +
+                  2 * lmoe_align_up((size_t)max_tokens * layer->top_k * 4, 256);
+    return lmoe_align_up(dec > pre ? dec : pre, 256) + host;
+}
+
+static lmoe_status forward_check(const lmoe_layer *layer, const float *x, int64_t t, float *out) {
+    if (!layer) return lmoe_fail(LMOE_ERR_INVALID, "layer is NULL");
+    if (!x || !out) return lmoe_fail(LMOE_ERR_INVALID, "x/out is NULL");
+    if (t < 0 || t > (1 << 22)) return lmoe_fail(LMOE_ERR_INVALID, "t (%lld) out of range", (long long)t);
+    if (!aligned16(x) || !aligned16(out)) return lmoe_fail(LMOE_ERR_INVALID, "x and out must be 16-byte aligned");
+    return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                               uint32_t *ids_out, float *weights_out, void *workspace,
+                                               size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, x, t, out);
+    if (st) return st;
+    if (t > 64) return lmoe_fail(LMOE_ERR_INVALID, "the decode path takes at most 64 tokens, got %lld", (long long)t);
+    const int step = decode_max_tokens();
+    for (int64_t t0 = 0; t0 < t; t0 += step) {
+        const int n = (int)(t - t0 < step ? t - t0 : step);
+        st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
+                               ids_out ? ids_out + t0 * layer->top_k : nullptr,
+                               weights_out ? weights_out + t0 * layer->top_k : nullptr, workspace, workspace_bytes,
+                               (cudaStream_t)stream);
+        if (st) return st;
+    }
+    return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                                uint32_t *ids_out, float *weights_out, void *workspace,
+                                                size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, x, t, out);
+    if (st) return st;
+    if (t == 0) return LMOE_OK;
+    return launch_moe_prefill(layer, x, t, out, ids_out, weights_out, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                             uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                             size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!layer) return lmoe_fail(LMOE_ERR_INVALID, "layer is NULL");
+    if (!x_host || !out_host) return lmoe_fail(LMOE_ERR_INVALID, "x_host/out_host is NULL");
+    if (t < 0 || t > (1 << 22)) return lmoe_fail(LMOE_ERR_INVALID, "t (%lld) out of range", (long long)t);
+    if (t == 0) return LMOE_OK;
+    const size_t need = lmoe_layer_workspace_bytes(layer, t);
+    if (!workspace || workspace_bytes < need)
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes for %lld tokens, got %zu", need, (long long)t,
+                         workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t xb = lmoe_align_up((size_t)t * layer->hidden * 4, 256);
+    const size_t ib = lmoe_align_up((size_t)t * layer->top_k * 4, 256);
+    const size_t kernel_ws = need - 2 * xb - 2 * ib;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    float *xd = reinterpret_cast<float *>(ws + kernel_ws);
+    float *od = reinterpret_cast<float *>(ws + kernel_ws + xb);
+    uint32_t *idd = reinterpret_cast<uint32_t *>(ws + kernel_ws + 2 * xb);
+    float *wd = reinterpret_cast<float *>(ws + kernel_ws + 2 * xb + ib);
+    LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
+    lmoe_status st;
+    // `use_mm`, src/moe.rs:236-240
+    if (t >= LMOE_MM_ID_MIN_SEQ)
+        st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
+                                      workspace, kernel_ws, stream);
+    else
+        st = lmoe_moe_forward_decode(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
+                                     workspace, kernel_ws, stream);
+    if (st) return st;
+    LMOE_CUDA(cudaMemcpyAsync(out_host, od, (size_t)t * layer->hidden * 4, cudaMemcpyDeviceToHost, s));
+    if (ids_out_host) LMOE_CUDA(cudaMemcpyAsync(ids_out_host, idd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
+    if (weights_out_host)
+        LMOE_CUDA(cudaMemcpyAsync(weights_out_host, wd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
+    LMOE_CUDA(cudaStreamSynchronize(s));
+    return LMOE_OK;
+}
