@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE hot path on B200.
+
+Metric (BASELINE.json): MoE-layer decode tok/s, with achieved HBM GB/s against the
+measured peak.  Workload at N=1 = BASELINE config 2: one MoE FFN layer (hidden
+3072, 256 routed experts + 1 shared, top-10, Q4_K gate/up, Q6_K down), decode
+batch sweep B = 1/2/4/8/16 with independent N(0,1) hidden states.  One "step" is
+one pass over the sweep (31 tokens, five launches of the fused decode kernel).
+Every launch uses a different layer copy out of `--layers` (default 8, 12.6 GB
+of weights, far beyond the 126 MB L2) and a different hidden-state batch, so
+weights come from HBM, not from cache.
+
+  value     device-resident inputs, CUDA-event timed, whole job (all ranks)
+  e2e       same sweep through the C-ABI host-buffer call (pinned host x in,
+            host result out, copies inside the timed region)
+  roofline  decode kernel: algorithmic bytes / event-timed launch duration
+  cpu_baseline  the CPU restatement of the reference's CPU path (int8-activation
+            k-quant dot products), all host threads, bounded sample
+
+`--impl reference` times that CPU restatement alone (the reference is Rust +
+Metal and cannot be built or run here).
+With N>1 (torchrun) every rank runs an independent replica of the sweep (decode
+at batch <= 16 does not shard; weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, F, E, K = 3072, 1024, 256, 10
+SWEEP = (1, 2, 4, 8, 16)
+EXPERT_BYTES = 2 * F * (H // 256) * 144 + H * (F // 256) * 210  # 6 119 424
+ROUTER_BYTES = E * H * 4
+NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+           "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+           "clocks_event_reasons.sw_power_cap")
+
+
+def algorithmic_bytes(n_distinct: int, batch: int) -> int:
+    """Bytes one decode launch must move: each distinct routed expert once, the shared
+    expert, the router, the bias, activations in and out."""
+    return n_distinct * EXPERT_BYTES + EXPERT_BYTES + ROUTER_BYTES + E * 4 + batch * (H * 4 + H * 4)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={NVSMI_Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_host_layer(orc, seed=0):
+    """Config-1/2 layer on the host for the CPU arm: N(0,0.02) weights through the oracle's encoder."""
+    rng = np.random.default_rng(seed)
+
+    def stack(dt, ne, n_out, k):
+        out = np.empty(ne * n_out * (k // 256) * orc.TYPE_SIZE[dt], np.uint8)
+        per = n_out * (k // 256) * orc.TYPE_SIZE[dt]
+        for e in range(ne):
+            w = (rng.standard_normal(n_out * k, dtype=np.float32) * np.float32(0.02))
+            out[e * per:(e + 1) * per] = orc.quantize(dt, w)
+        return out
+
+    return orc.HostLayer(H, F, E, K, router=(rng.standard_normal((E, H)) * 0.02).astype(np.float32),
+                         bias=rng.uniform(-0.1, 0.1, E).astype(np.float32),
+                         gate=stack(orc.Q4_K, E, F, H), up=stack(orc.Q4_K, E, F, H), down=stack(orc.Q6_K, E, H, F),
+                         sh_gate=stack(orc.Q4_K, 1, F, H), sh_up=stack(orc.Q4_K, 1, F, H),
+                         sh_down=stack(orc.Q6_K, 1, H, F))
+
+
+def cpu_time_sweep(host, xs, batches, budget_s):
+    """Time the int8-activation CPU path over `batches`; stops early past the budget.
+    Returns (tokens, seconds)."""
+    tok, t0 = 0, time.perf_counter()
+    for b in batches:
+        host.forward_q8(xs[b])
+        tok += b
+        if time.perf_counter() - t0 > budget_s:
+            break
+    return tok, time.perf_counter() - t0
+
+
+def run_reference(args, rank, world):
+    """`--impl reference`: the CPU restatement of the reference's CPU path, rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+
+    orc.build()
+    host = build_host_layer(orc, seed=0)
+    rng = np.random.default_rng(1)
+    xs = {b: rng.standard_normal((b, H)).astype(np.float32) for b in SWEEP}
+    # bounded sample: size each step so steps+warmup end in about two minutes
+    tok, sec = cpu_time_sweep(host, xs, (1,), 1e9)
+    per_tok = sec / tok
+    total = args.steps + args.warmup
+    max_tok_per_step = max(1, int(120.0 / total / per_tok))
+    batches = []
+    for b in SWEEP:
+        if sum(batches) + b <= max_tok_per_step:
+            batches.append(b)
+    if not batches:
+        batches = [1]
+    for _ in range(args.warmup):
+        cpu_time_sweep(host, xs, batches, 1e9)
+    t0 = time.perf_counter()
+    toks = 0
+    for _ in range(args.steps):
+        n, _ = cpu_time_sweep(host, xs, batches, 1e9)
+        toks += n
+    sec = time.perf_counter() - t0
+    val = toks / sec
+    cores = orc.num_threads()
+    sample = f"decode batches {batches} of the sweep per step ({sum(batches)} tokens), one layer"
+    print(json.dumps({
+        "impl": "reference", "metric": "moe_layer_decode_tok_per_s", "value": val, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8xq4/q6 -> f32", "data": "synthetic",
+        "config": {"workload": "config2: single MoE layer decode sweep B=1/2/4/8/16", "hidden": H, "expert_ff": F,
+                   "n_expert": E, "top_k": K, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's CPU k-quant path (the reference itself is Rust + Metal: not buildable here)",
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--layers", type=int, default=8, help="layer copies rotated through (working set >> L2)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from maxuna_b200 import _native
+    from maxuna_b200.moe import MoeBlock
+
+    _native.lib()
+    layers = [MoeBlock.random(H, F, E, K, seed=100 * rank + i, device=dev) for i in range(args.layers)]
+    n_x = 64
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    xs = {b: [torch.randn(b, H, generator=gen, device=dev) for _ in range(n_x)] for b in SWEEP}
+    outs = {b: torch.empty(b, H, device=dev) for b in SWEEP}
+    ws = [ly.workspace(max(SWEEP)) for ly in layers]
+    n_launch = args.steps * len(SWEEP)
+    ids_log = torch.zeros(n_launch, max(SWEEP) * K, dtype=torch.int32, device=dev)
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch(i, b, log_row=None):
+        ly = layers[i % args.layers]
+        x = xs[b][i % n_x]
+        idp = None if log_row is None else ids_log[log_row].data_ptr()
+        _native.check(lib.lmoe_moe_forward_decode(ly.handle, x.data_ptr(), b, outs[b].data_ptr(), idp, None,
+                                                  ws[i % args.layers].data_ptr(), ws[i % args.layers].numel(), stream))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up ----
+    i = 0
+    for _ in range(args.warmup):
+        for b in SWEEP:
+            launch(i, b)
+            i += 1
+    barrier()
+
+    # ---- timed region: K sweeps, device-resident inputs ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    row = 0
+    for _ in range(args.steps):
+        for b in SWEEP:
+            launch(i, b, row)
+            i += 1
+            row += 1
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+
+    # ---- per-batch timing (same rotation), for the sweep table and the roofline ----
+    per_b = {}
+    for b in SWEEP:
+        n = max(50, args.steps // 2)
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(n):
+            launch(i, b)
+            i += 1
+        a1.record()
+        torch.cuda.synchronize()
+        per_b[b] = a0.elapsed_time(a1) / n * 1e-3  # seconds per launch
+
+    # distinct experts per launch from the logged routing decisions
+    ids_host = ids_log.cpu().numpy()
+    distinct = {b: [] for b in SWEEP}
+    for r in range(n_launch):
+        b = SWEEP[r % len(SWEEP)]
+        distinct[b].append(len(np.unique(ids_host[r, : b * K])))
+    mean_u = {b: float(np.mean(distinct[b])) for b in SWEEP}
+    bytes_sweep = sum(algorithmic_bytes(1, b) - EXPERT_BYTES + mean_u[b] * EXPERT_BYTES for b in SWEEP)
+    launch_s = sum(per_b[b] for b in SWEEP)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak_gbs, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak_gbs, peak_src = 6650.0, "fallback"
+    achieved = bytes_sweep / launch_s / 1e9
+    sweep_tab = []
+    for b in SWEEP:
+        by = algorithmic_bytes(1, b) - EXPERT_BYTES + mean_u[b] * EXPERT_BYTES
+        sweep_tab.append({"batch": b, "us_per_launch": per_b[b] * 1e6, "tok_per_s": b / per_b[b],
+                          "distinct_experts": mean_u[b], "gb_per_s": by / per_b[b] / 1e9,
+                          "frac_of_peak": by / per_b[b] / 1e9 / peak_gbs})
+
+    # ---- end to end: host buffers through the C ABI ----
+    xh = {b: [x.cpu().pin_memory() for x in xs[b][:8]] for b in SWEEP}
+    oh = {b: torch.empty(b, H).pin_memory() for b in SWEEP}
+    e2e_steps = max(20, args.steps // 10)
+
+    def host_call(j, b):
+        ly = layers[j % args.layers]
+        _native.check(lib.lmoe_moe_forward_host(ly.handle, xh[b][j % 8].data_ptr(), b, oh[b].data_ptr(), None, None,
+                                                ws[j % args.layers].data_ptr(), ws[j % args.layers].numel(), stream))
+
+    j = 0
+    for _ in range(3):
+        for b in SWEEP:
+            host_call(j, b)
+            j += 1
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for b in SWEEP:
+            host_call(j, b)
+            j += 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+
+    # ---- max over ranks ----
+    tokens_per_step = sum(SWEEP)
+    if world > 1:
+        tt = torch.tensor([ms, e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(tt[0]), float(tt[1])
+    value = world * tokens_per_step * args.steps / (ms * 1e-3)
+    e2e_val = world * tokens_per_step * e2e_steps / e2e_s
+
+    # ---- CPU baseline (rank 0, N=1 only, bounded sample) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as orc
+
+        host = layers[0].host_layer(orc)
+        xs_cpu = {b: xs[b][0].cpu().numpy() for b in SWEEP}
+        cpu_time_sweep(host, xs_cpu, (1,), 1e9)
+        tok, sec = cpu_time_sweep(host, xs_cpu, SWEEP + SWEEP + SWEEP, 20.0)
+        cpu = {"value": tok / sec, "unit": "tok/s", "cores": orc.num_threads(), "kind": "port",
+               "sample": f"{tok} tokens of the decode sweep on layer 0 (int8-activation k-quant dots, OpenMP)"}
+
+    if rank == 0:
+        line = {
+            "metric": "moe_layer_decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K x f16(hi+lo) -> f32",
+            "data": "synthetic",
+            "config": {"workload": "config2: single MoE layer decode sweep B=1/2/4/8/16 (31 tokens per step)",
+                       "hidden": H, "expert_ff": F, "n_expert": E, "top_k": K, "shared_expert": True,
+                       "layers_rotated": args.layers,
+                       "l2": f"inputs larger than L2: {args.layers} layer copies ({args.layers * 1.573:.1f} GB), "
+                             "a different copy and hidden-state batch every launch",
+                       "parallelism": "replicas" if world > 1 else "single GPU"},
+            "gpu_launches": args.steps * len(SWEEP),
+            "e2e": {"value": e2e_val, "unit": "tok/s",
+                    "h2d_bytes_per_step": tokens_per_step * H * 4, "d2h_bytes_per_step": tokens_per_step * H * 4,
+                    "steps": e2e_steps},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": achieved / peak_gbs, "traffic": None, "peak_source": peak_src,
+                         "kernel": "moe_decode_kernel", "algorithmic_bytes_per_sweep": bytes_sweep},
+            "sweep": sweep_tab,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -631,7 +631,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         const uint32_t pos = atomicAdd(&cnt_s[e], 1u);
         plist_s[off_s[e] + pos] = (uint16_t)i;
     }
-    __threadfence_block();
+    bar_sync(1, CW * 32);
+    // every CTA must see the same list order (passes are cut from it): sort each short list
+    for (int e = tid; e < E; e += CW * 32) {
+        const int o = off_s[e], c = off_s[e + 1] - o;
+        for (int i = 1; i < c; i++) {
+            const uint16_t v = plist_s[o + i];
+            int j = i - 1;
+            while (j >= 0 && plist_s[o + j] > v) { plist_s[o + j + 1] = plist_s[o + j]; j--; }
+            plist_s[o + j + 1] = v;
+        }
+    }
     bar_sync(1, CW * 32);
     bar_sync(2, DEC_THREADS); // release the producer: the routing tables are complete
 

@@ -61,7 +61,10 @@ class ExpertStack:
     def __del__(self):
         h = getattr(self, "_h", None)
         if h:
-            _native.lib().lmoe_expert_stack_destroy(h)
+            try:
+                _native.lib().lmoe_expert_stack_destroy(h)
+            except Exception:  # interpreter shutdown: the library is already gone
+                pass
             self._h = None
 
     # ---- construction -----------------------------------------------------

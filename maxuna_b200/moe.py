@@ -112,7 +112,10 @@ class MoeBlock:
     def __del__(self):
         h = getattr(self, "_h", None)
         if h:
-            lib().lmoe_layer_destroy(h)
+            try:
+                lib().lmoe_layer_destroy(h)
+            except Exception:  # interpreter shutdown: the library is already gone
+                pass
             self._h = None
 
     @property
