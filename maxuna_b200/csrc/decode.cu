@@ -28,9 +28,9 @@
 //     consumer warps and reduced in shared memory in a fixed order.
 //   * Phases are separated by bounded grid barriers; the producer runs ahead of
 //     them (weights do not depend on them), which keeps HBM busy across phases.
-//   * The down projection writes weighted partial rows; the CTA that delivers
-//     the last partial of a (token, 16-row tile) sums the K+1 partials in slot
-//     order, so the result is deterministic without float atomics.
+//   * The down projection writes weighted partial rows; a last phase sums the
+//     K+1 partials of every output element in slot order, so the result is
+//     deterministic without float atomics.
 #include "fused.cuh"
 #include "kquant.cuh"
 #include "route_math.cuh"
@@ -55,7 +55,7 @@ struct DecodeParams {
     int t, hidden, ff, n_expert, top_k;
     float scale;
     int norm, has_shared;
-    uint32_t *ctrl;   // [0..3] flag, [4] grid barrier, [5] exit count, [16..] tile counters [t][hidden/16]
+    uint32_t *ctrl;   // [0..3] flag, [4] grid barrier, [5] exit count, [8192..] optional timing stamps
     float *logits;    // [t][n_expert]
     __half *act_hl;   // [t*(top_k+1)][2][ff], k permuted within groups of 8
     float *ypart;     // [t*(top_k+1)][hidden]
@@ -298,6 +298,19 @@ __device__ __forceinline__ void stage_act(const DecodeParams &P, const Unit &U, 
 }
 
 // ---- per-unit math ---------------------------------------------------------------
+// d = a*b (fresh accumulator: C is the zero register, no moves needed)
+__device__ __forceinline__ void mma16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+// byte i (0..3) of `w` as an exact float: 0x4B0000bb is 2^23 + bb
+template <int I>
+__device__ __forceinline__ float byte_to_float(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + I)) - 8388608.0f;
+}
+
 // 16 Q4_K rows (8 gate + 8 up) x the blocks of this warp.  acc: rows g / g+8, columns 2t, 2t+1.
 __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
                                          const __half *xcol, const __half *scol, bool colv, float (&acc)[4]) {
@@ -315,15 +328,16 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
         q4k_unpack_scales(hg.y, hg.z, hg.w, scg[0], scg[1], mng[0], mng[1]);
         q4k_unpack_scales(hG.y, hG.z, hG.w, scG[0], scG[1], mnG[0], mnG[1]);
         // min term: one MMA, A = the 8 six-bit mins of each row, B = 32-wide activation sums
-        float cm[4] = {0.f, 0.f, 0.f, 0.f};
+        float cm[4];
         {
             const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
             const uint32_t ma = __byte_perm(t < 2 ? mng[0] : mng[1], 0u, sel);
             const uint32_t mA = __byte_perm(t < 2 ? mnG[0] : mnG[1], 0u, sel);
             const uint32_t sb = colv ? *reinterpret_cast<const uint32_t *>(scol + 8 * b + 2 * t) : 0u;
-            mma16816(cm, ma, mA, 0u, 0u, sb, 0u);
+            mma16816_z(cm, ma, mA, 0u, 0u, sb, 0u);
         }
-        float ab[4] = {0.f, 0.f, 0.f, 0.f};
+        // low-nibble and high-nibble sub-blocks accumulate apart (they differ by a factor 16)
+        float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint2 wg = *reinterpret_cast<const uint2 *>(bg + 16 + 32 * j + 8 * t);
@@ -333,27 +347,27 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
                 xl = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 8 * t);
                 xh = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
             }
-            float fl[4] = {0.f, 0.f, 0.f, 0.f}, fh[4] = {0.f, 0.f, 0.f, 0.f};
-            mma16816(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, (wg.x >> 8) & 0x000F000Fu, (wG.x >> 8) & 0x000F000Fu,
-                     xl.x, xl.y);
-            mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, (wg.y >> 8) & 0x000F000Fu, (wG.y >> 8) & 0x000F000Fu,
-                     xl.z, xl.w);
-            mma16816(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, (wg.x >> 8) & 0x00F000F0u, (wG.x >> 8) & 0x00F000F0u,
-                     xh.x, xh.y);
-            mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, (wg.y >> 8) & 0x00F000F0u, (wG.y >> 8) & 0x00F000F0u,
-                     xh.z, xh.w);
-            const uint32_t wsg = scg[j >> 1] >> (16 * (j & 1)), wsG = scG[j >> 1] >> (16 * (j & 1));
-            const float s0g = (float)(wsg & 0xff), s1g = (float)((wsg >> 8) & 0xff) * 0.0625f;
-            const float s0G = (float)(wsG & 0xff), s1G = (float)((wsG >> 8) & 0xff) * 0.0625f;
-            ab[0] += s0g * fl[0] + s1g * fh[0];
-            ab[1] += s0g * fl[1] + s1g * fh[1];
-            ab[2] += s0G * fl[2] + s1G * fh[2];
-            ab[3] += s0G * fl[3] + s1G * fh[3];
+            const uint32_t sg8 = wg.x >> 8, sG8 = wG.x >> 8, tg8 = wg.y >> 8, tG8 = wG.y >> 8;
+            float fl[4], fh[4];
+            mma16816_z(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, sg8 & 0x000F000Fu, sG8 & 0x000F000Fu, xl.x, xl.y);
+            mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, tg8 & 0x000F000Fu, tG8 & 0x000F000Fu, xl.z, xl.w);
+            mma16816_z(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, sg8 & 0x00F000F0u, sG8 & 0x00F000F0u, xh.x, xh.y);
+            mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, tg8 & 0x00F000F0u, tG8 & 0x00F000F0u, xh.z, xh.w);
+            float s0g, s1g, s0G, s1G;
+            if (j & 1) {
+                s0g = byte_to_float<2>(scg[j >> 1]); s1g = byte_to_float<3>(scg[j >> 1]);
+                s0G = byte_to_float<2>(scG[j >> 1]); s1G = byte_to_float<3>(scG[j >> 1]);
+            } else {
+                s0g = byte_to_float<0>(scg[j >> 1]); s1g = byte_to_float<1>(scg[j >> 1]);
+                s0G = byte_to_float<0>(scG[j >> 1]); s1G = byte_to_float<1>(scG[j >> 1]);
+            }
+            al[0] += s0g * fl[0]; al[1] += s0g * fl[1]; al[2] += s0G * fl[2]; al[3] += s0G * fl[3];
+            ah[0] += s1g * fh[0]; ah[1] += s1g * fh[1]; ah[2] += s1G * fh[2]; ah[3] += s1G * fh[3];
         }
-        acc[0] += dg * ab[0] - mg * cm[0];
-        acc[1] += dg * ab[1] - mg * cm[1];
-        acc[2] += dG * ab[2] - mG * cm[2];
-        acc[3] += dG * ab[3] - mG * cm[3];
+        acc[0] += dg * (al[0] + 0.0625f * ah[0]) - mg * cm[0];
+        acc[1] += dg * (al[1] + 0.0625f * ah[1]) - mg * cm[1];
+        acc[2] += dG * (al[2] + 0.0625f * ah[2]) - mG * cm[2];
+        acc[3] += dG * (al[3] + 0.0625f * ah[3]) - mG * cm[3];
     }
 }
 
@@ -384,19 +398,22 @@ __device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, in
         const float dg = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bg + 208));
         const float dG = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bG + 208));
         // "-32" offset: one MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
-        float co[4] = {0.f, 0.f, 0.f, 0.f};
+        float co[4];
         {
             uint32_t s0 = 0u, s1 = 0u;
             if (colv) {
                 s0 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t);
                 s1 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t + 8);
             }
-            mma16816(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
-                     sc_pair_half2(scG + 2 * t + 8), s0, s1);
+            mma16816_z(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
+                       sc_pair_half2(scG + 2 * t + 8), s0, s1);
         }
-        float ab[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+        float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
         for (int n = 0; n < 2; n++) {
+            // the eight scales of this half, biased to unsigned so a byte permute turns them into floats
+            const uint32_t swg0 = lds32_a2(bg + 192 + 8 * n) ^ 0x80808080u, swg1 = lds32_a2(bg + 196 + 8 * n) ^ 0x80808080u;
+            const uint32_t swG0 = lds32_a2(bG + 192 + 8 * n) ^ 0x80808080u, swG1 = lds32_a2(bG + 196 + 8 * n) ^ 0x80808080u;
 #pragma unroll
             for (int c = 0; c < 2; c++) {
                 const int l0 = 16 * c + 4 * t;
@@ -416,23 +433,39 @@ __device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, in
                     const uint32_t a2 = ((qg >> 8) & ml) | (hg8 & mh), a3 = ((qG >> 8) & ml) | (hG8 & mh);
                     uint2 xv = make_uint2(0u, 0u);
                     if (colv) xv = *reinterpret_cast<const uint2 *>(xp + 32 * i);
-                    float f[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma16816(f, a0, a1, a2, a3, xv.x, xv.y);
-                    const float pw = (i & 2) ? 0.0625f : 1.0f;
-                    const float sg = (float)scg[8 * n + 2 * i + c] * pw, sG = (float)scG[8 * n + 2 * i + c] * pw;
-                    ab[0] += sg * f[0];
-                    ab[1] += sg * f[1];
-                    ab[2] += sG * f[2];
-                    ab[3] += sG * f[3];
+                    float f[4];
+                    mma16816_z(f, a0, a1, a2, a3, xv.x, xv.y);
+                    // scale index within the half: 2*i + c
+                    float sg, sG;
+                    if (i < 2) {
+                        sg = (c ? byte_to_float<1>(swg0 >> (16 * i)) : byte_to_float<0>(swg0 >> (16 * i))) - 128.f;
+                        sG = (c ? byte_to_float<1>(swG0 >> (16 * i)) : byte_to_float<0>(swG0 >> (16 * i))) - 128.f;
+                        al[0] += sg * f[0]; al[1] += sg * f[1]; al[2] += sG * f[2]; al[3] += sG * f[3];
+                    } else {
+                        sg = (c ? byte_to_float<1>(swg1 >> (16 * (i - 2))) : byte_to_float<0>(swg1 >> (16 * (i - 2)))) - 128.f;
+                        sG = (c ? byte_to_float<1>(swG1 >> (16 * (i - 2))) : byte_to_float<0>(swG1 >> (16 * (i - 2)))) - 128.f;
+                        ah[0] += sg * f[0]; ah[1] += sg * f[1]; ah[2] += sG * f[2]; ah[3] += sG * f[3];
+                    }
                 }
             }
         }
-        acc[0] += dg * (ab[0] * 16777216.f - 32.f * co[0]);
-        acc[1] += dg * (ab[1] * 16777216.f - 32.f * co[1]);
-        acc[2] += dG * (ab[2] * 16777216.f - 32.f * co[2]);
-        acc[3] += dG * (ab[3] * 16777216.f - 32.f * co[3]);
+        acc[0] += dg * ((al[0] + 0.0625f * ah[0]) * 16777216.f - 32.f * co[0]);
+        acc[1] += dg * ((al[1] + 0.0625f * ah[1]) * 16777216.f - 32.f * co[1]);
+        acc[2] += dG * ((al[2] + 0.0625f * ah[2]) * 16777216.f - 32.f * co[2]);
+        acc[3] += dG * ((al[3] + 0.0625f * ah[3]) * 16777216.f - 32.f * co[3]);
     }
 }
+
+#ifdef LMOE_DECODE_TIMING
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
+    return v;
+}
+#define STAMP(i) do { if (tid == 0) reinterpret_cast<unsigned long long *>(P.ctrl + 8192)[blockIdx.x * 16 + (i)] = gtime(); } while (0)
+#else
+#define STAMP(i) do { } while (0)
+#endif
 
 // ---- the kernel ---------------------------------------------------------------------
 __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid_constant__ DecodeParams P) {
@@ -525,8 +558,48 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     // ========================= consumer warps =========================
     const int g = lane >> 2, t4 = lane & 3;
 
+    STAMP(0);
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
-    {
+    if (P.hidden == 128 * 24) {
+        // router row held in registers (all its loads in flight at once); hidden states of
+        // two tokens at a time staged as f32 in the (not yet used) activation cache
+        constexpr int HB = 24;
+        const int H = P.hidden;
+        float *xs32 = reinterpret_cast<float *>(xc);
+        for (int er = 0; er * G * CW < E; er++) {
+            const int e = blockIdx.x + G * (warp + CW * er);
+            const bool have = e < E;
+            float4 wv[HB];
+            if (have) {
+                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
+#pragma unroll
+                for (int j = 0; j < HB; j++) wv[j] = __ldg(wr + 32 * j);
+            }
+            for (int t0 = 0; t0 < P.t; t0 += 2) {
+                const int nt = min(2, P.t - t0);
+                bar_sync(1, CW * 32);
+                for (int i = tid; i < nt * (H / 4); i += CW * 32)
+                    reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
+                bar_sync(1, CW * 32);
+                if (have) {
+                    for (int i = 0; i < nt; i++) {
+                        const float4 *xr = reinterpret_cast<const float4 *>(xs32 + i * H) + lane;
+                        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                        for (int j = 0; j < HB; j++) {
+                            const float4 xv = xr[32 * j];
+                            a0 = __fmaf_rn(xv.x, wv[j].x, a0);
+                            a1 = __fmaf_rn(xv.y, wv[j].y, a1);
+                            a2 = __fmaf_rn(xv.z, wv[j].z, a2);
+                            a3 = __fmaf_rn(xv.w, wv[j].w, a3);
+                        }
+                        const float v = lmoe_router_fold(a0, a1, a2, a3);
+                        if (lane == 0) P.logits[(size_t)(t0 + i) * E + e] = v;
+                    }
+                }
+            }
+        }
+    } else {
         const int ntt = (P.t + 3) / 4;
         const int H = P.hidden;
         for (int q = blockIdx.x * CW + warp; q < E * ntt; q += G * CW) {
@@ -556,24 +629,20 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
         }
     }
+    STAMP(1);
     grid_barrier(P.ctrl, (uint32_t)G, tid);
+    STAMP(2);
 
-    // ---- phase 0b: selection, redundantly in every CTA (scratch aliases the activation cache) ----
+    // ---- phase 0b: selection, redundantly in every CTA ----
     {
-        float *probs = reinterpret_cast<float *>(xc) + (size_t)warp * 2 * E;
-        float *sel = probs + E;
         for (int tok = warp; tok < P.t; tok += CW) {
-            for (int e = lane; e < E; e += 32) {
-                const float p = lmoe_sigmoid_fixed(__ldcg(P.logits + (size_t)tok * E + e));
-                probs[e] = p;
-                sel[e] = P.bias ? __fadd_rn(p, __ldg(P.bias + e)) : p;
-            }
-            __syncwarp();
-            lmoe_warp_select(sel, probs, E, K, P.scale, P.norm, ids_s + tok * K, w_s + tok * K, lane);
-            __syncwarp();
+            const float *lrow = P.logits + (size_t)tok * E;
+            lmoe_warp_select_regs([&](int e) { return __ldcg(lrow + e); }, P.bias, E, K, P.scale, P.norm,
+                                  ids_s + tok * K, w_s + tok * K, lane);
         }
         for (int e = tid; e < E; e += CW * 32) cnt_s[e] = 0;
     }
+    STAMP(8);
     bar_sync(1, CW * 32);
     if (blockIdx.x == 0) {
         for (int i = tid; i < P.t * K; i += CW * 32) {
@@ -643,8 +712,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         }
     }
     bar_sync(1, CW * 32);
+    STAMP(9);
     bar_sync(2, DEC_THREADS); // release the producer: the routing tables are complete
 
+    STAMP(3);
     Tables T{ids_s, w_s, off_s, plist_s, act_s, ppre_s, s_n_active, s_routed_passes, shared_passes};
 
     uint32_t n = 0; // ring fill counter, same sequence as the producer's
@@ -686,7 +757,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                     r0[8 * NCOL] = acc[2]; r0[8 * NCOL + 1] = acc[3];
                 }
                 bar_sync(1, CW * 32);
-                if (warp == 0) {
+                if (warp == (int)(n & (CW - 1))) { // the epilogue rotates over the warps
                     if (phase == 1) {
                         // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
                         const int tk = lane >> 3, r = lane & 7;
@@ -707,11 +778,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                             dst[P.ff] = __float2half_rn(av - __half2float(h));
                         }
                     } else {
-                        // weighted partial rows, then the last arriver of each (token, tile) combines
+                        // weighted partial row of this (pair, tile); summed over slots in phase 3
                         const int tk = lane >> 4, r = lane & 15;
-                        const bool valid = tk < U.n_tok;
-                        const int row = U.tile * 16 + r;
-                        if (valid) {
+                        if (tk < U.n_tok) {
                             float yv = 0.f;
 #pragma unroll
                             for (int w = 0; w < CW; w++) {
@@ -720,26 +789,36 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                             }
                             const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
                             if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
-                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + row, yv);
-                            __threadfence();
-                        }
-                        __syncwarp();
-                        uint32_t old = 0;
-                        if (valid && r == 0) old = atomicAdd(&P.ctrl[16 + U.tok[tk] * tiles2 + U.tile], 1u);
-                        old = __shfl_sync(0xffffffffu, old, lane & 16);
-                        if (valid && old == (uint32_t)(K + P.has_shared - 1)) {
-                            __threadfence();
-                            const float *yp = P.ypart + (size_t)U.tok[tk] * (K + 1) * P.hidden + row;
-                            float sum = 0.f;
-                            for (int sl = 0; sl < K + P.has_shared; sl++) sum = __fadd_rn(sum, __ldcg(yp + (size_t)sl * P.hidden));
-                            P.out[(size_t)U.tok[tk] * P.hidden + row] = sum;
+                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + U.tile * 16 + r, yv);
                         }
                     }
                 }
                 redbuf ^= 1;
             }
         }
-        if (phase == 1) grid_barrier(P.ctrl, (uint32_t)(2 * G), tid);
+        STAMP(phase == 1 ? 4 : 6);
+        grid_barrier(P.ctrl, (uint32_t)((phase + 1) * G), tid);
+        STAMP(phase == 1 ? 5 : 7);
+    }
+
+    // ---- phase 3: out[t, :] = sum over slots (then the shared expert) of the weighted partial rows,
+    //      in slot order (`combine`, src/ops/combine.metal:70-97, plus `routed + shared`, src/moe.rs:77) ----
+    {
+        const int nslot = K + P.has_shared;
+        const int h4 = P.hidden / 4;
+        for (int i = blockIdx.x * (CW * 32) + tid; i < P.t * h4; i += G * CW * 32) {
+            const int tok = i / h4, c = i - tok * h4;
+            const float4 *yp = reinterpret_cast<const float4 *>(P.ypart + (size_t)tok * (K + 1) * P.hidden) + c;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sl = 0; sl < nslot; sl++) {
+                const float4 v = __ldcg(yp + (size_t)sl * h4);
+                sum.x = __fadd_rn(sum.x, v.x);
+                sum.y = __fadd_rn(sum.y, v.y);
+                sum.z = __fadd_rn(sum.z, v.z);
+                sum.w = __fadd_rn(sum.w, v.w);
+            }
+            reinterpret_cast<float4 *>(P.out + (size_t)tok * P.hidden)[c] = sum;
+        }
     }
 
     // ---- exit: the last CTA leaves the control words zeroed for the next call ----
@@ -748,7 +827,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         __threadfence();
         const uint32_t old = atomicAdd(&P.ctrl[5], 1u);
         if (old == (uint32_t)(G - 1)) {
-            for (int i = 0; i < P.t * tiles2; i++) P.ctrl[16 + i] = 0u;
             P.ctrl[4] = 0u;
             P.ctrl[5] = 0u;
             __threadfence();
@@ -779,21 +857,29 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode needs hidden %% 128 == 0, expert_ff %% 16 == 0 and t*hidden/16 <= 16368");
     if (t * K > 65535) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "t*top_k too large");
     const DecLayout L(H, F, E, t, K);
-    int dev = 0, sms = 0, max_smem = 0;
+    // device facts and the kernel's shared-memory opt-in are looked up once per (device, size)
+    static thread_local int c_dev = -1, c_sms = 0, c_max_smem = 0, c_total = -1, c_occ = 0;
+    int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));
-    LMOE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    LMOE_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    if (L.total > max_smem)
+    if (dev != c_dev) {
+        LMOE_CUDA(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
+        LMOE_CUDA(cudaDeviceGetAttribute(&c_max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        c_dev = dev;
+        c_total = -1;
+    }
+    if (L.total > c_max_smem)
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode needs %d bytes of shared memory per CTA, device allows %d",
-                         L.total, max_smem);
+                         L.total, c_max_smem);
     if (workspace_bytes < decode_workspace_bytes(t, H, F, E, K) || !workspace)
         return lmoe_fail(LMOE_ERR_WORKSPACE, "decode workspace needs %zu bytes, got %zu",
                          decode_workspace_bytes(t, H, F, E, K), workspace_bytes);
-    LMOE_CUDA(cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
-    int occ = 0;
-    LMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, moe_decode_kernel, DEC_THREADS, L.total));
-    if (occ < 1) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode kernel does not fit on an SM");
-    if (occ > 2) occ = 2;
+    if (L.total != c_total) {
+        LMOE_CUDA(cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+        LMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&c_occ, moe_decode_kernel, DEC_THREADS, L.total));
+        c_total = L.total;
+    }
+    if (c_occ < 1) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode kernel does not fit on an SM");
+    const int occ = c_occ > 2 ? 2 : c_occ, sms = c_sms;
 
     DecodeParams P;
     P.x = x; P.out = out; P.ids_out = ids_out; P.w_out = w_out;

@@ -88,3 +88,63 @@ __device__ __forceinline__ void lmoe_warp_select(float *sel, const float *probs,
     if (scale != 0.0f && scale != 1.0f) my_w = __fmul_rn(my_w, scale);
     if (lane < top_k) w_row[lane] = my_w;
 }
+
+// Register-resident variant of the selection for n_expert <= 512: each lane keeps
+// experts lane, lane+32, ... ; every round is two warp-wide integer reductions
+// (maximum of an order-preserving key, then the lowest expert index holding it).
+// `logit_of(e)` supplies the pre-sigmoid logit.  Same result as lmoe_warp_select.
+template <typename LogitFn>
+__device__ __forceinline__ void lmoe_warp_select_regs(LogitFn logit_of, const float *__restrict__ bias,
+                                                      int n_expert, int top_k, float scale, int norm,
+                                                      uint32_t *ids_row, float *w_row, int lane) {
+    constexpr int EPL = 16;
+    float p[EPL];
+    uint32_t key[EPL];
+    float lg[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+        const int e = lane + 32 * i;
+        lg[i] = e < n_expert ? logit_of(e) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+        const int e = lane + 32 * i;
+        key[i] = 0u;
+        p[i] = 0.0f;
+        if (e < n_expert) {
+            p[i] = lmoe_sigmoid_fixed(lg[i]);
+            float sv = bias ? __fadd_rn(p[i], __ldg(bias + e)) : p[i];
+            sv = __fadd_rn(sv, 0.0f); // -0 -> +0 so the integer order equals the float order
+            const uint32_t u = __float_as_uint(sv);
+            key[i] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+            if (key[i] == 0u) key[i] = 1u; // 0 marks "taken / absent"
+        }
+    }
+    float my_w = 0.0f;
+    for (int k = 0; k < top_k; k++) {
+        uint32_t best = 0u;
+#pragma unroll
+        for (int i = 0; i < EPL; i++) best = key[i] > best ? key[i] : best;
+        const uint32_t m = __reduce_max_sync(0xffffffffu, best);
+        uint32_t cand = 0xffffffffu;
+#pragma unroll
+        for (int i = EPL - 1; i >= 0; i--)
+            if (key[i] == m) cand = (uint32_t)(lane + 32 * i);
+        const uint32_t idx = __reduce_min_sync(0xffffffffu, cand);
+        float pw = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPL; i++)
+            if ((uint32_t)(lane + 32 * i) == idx) { pw = p[i]; key[i] = 0u; }
+        pw = __shfl_sync(0xffffffffu, pw, idx & 31);
+        if (lane == k) my_w = pw;
+        if (lane == 0) ids_row[k] = idx;
+    }
+    if (norm) {
+        float sum = 0.0f;
+        for (int k = 0; k < top_k; k++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_w, k));
+        sum = sum < 6.103515625e-5f ? 6.103515625e-5f : sum;
+        my_w = __fdiv_rn(my_w, sum);
+    }
+    if (scale != 0.0f && scale != 1.0f) my_w = __fmul_rn(my_w, scale);
+    if (lane < top_k) w_row[lane] = my_w;
+}
