@@ -147,8 +147,9 @@ lmoe_status lmoe_prepare_map0(const uint32_t *ids, int64_t t, int64_t top_k, int
                               void *scratch, size_t scratch_bytes, void *stream);
 /* `ops::mm_id::supported`, src/ops/mm_id.rs:48-50. Returns 1 or 0. */
 int32_t lmoe_mm_id_supported(int32_t dtype, int64_t top_k);
-/* Workspace of one grouped-GEMM projection (staged f16 activations). */
-size_t lmoe_mm_id_workspace_bytes(int64_t t, int64_t top_k, int64_t x_per_row, int64_t k);
+/* Workspace of one grouped-GEMM projection over `stack` (staged f16 activations,
+ * tile list, device flag). */
+size_t lmoe_mm_id_workspace_bytes(const lmoe_expert_stack *stack, int64_t t, int64_t top_k, int64_t x_per_row);
 /* `ops::mm_id::mul_mm_id_shared`, src/ops/mm_id.rs:32-39 -> `run_mm_shared`,
  * src/ops/dispatch.rs:789-797 -> kernel_mul_mm_id_q{4,6}_K_f32_t,
  * src/ops/mm_id.metal:492-647.  Same shapes and errors as lmoe_mul_mv_id.  The
@@ -162,7 +163,7 @@ lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *stack, const float *x
                                   int64_t map_t, int64_t map_top_k, float *out, void *workspace,
                                   size_t workspace_bytes, void *stream);
 /* `ops::mm_id::mul_mm_id`, src/ops/mm_id.rs:16-18: self-contained (runs its own
- * map0 pass). Workspace: lmoe_mm_id_workspace_bytes(...) + lmoe_map0_scratch_bytes(...). */
+ * map0 pass). Workspace: lmoe_mm_id_workspace_bytes(...) + lmoe_map0_scratch_bytes(n_expert, t). */
 lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
                            int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k, float *out,
                            void *workspace, size_t workspace_bytes, void *stream);
@@ -235,6 +236,8 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
 lmoe_status lmoe_experts_forward_rows(const lmoe_layer *layer, const float *x, const uint32_t *local_ids,
                                       const float *row_weights, int64_t rows, float *out, void *workspace,
                                       size_t workspace_bytes, void *stream);
+/* Bytes of scratch `lmoe_experts_forward_rows` / `lmoe_shared_forward` need for `rows` rows. */
+size_t lmoe_rows_workspace_bytes(const lmoe_layer *layer, int64_t rows);
 /* The shared expert alone: out [t, hidden] = FFN_shared(x [t, hidden]). */
 lmoe_status lmoe_shared_forward(const lmoe_layer *layer, const float *x, int64_t t, float *out,
                                 void *workspace, size_t workspace_bytes, void *stream);

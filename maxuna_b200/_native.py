@@ -34,7 +34,7 @@ PROTOTYPES = {
     "lmoe_map0_scratch_bytes": (c_sz, [c_i64, c_i64]),
     "lmoe_prepare_map0": (c_i32, [c_vp, c_i64, c_i64, c_i64, c_vp, c_sz, c_vp]),
     "lmoe_mm_id_supported": (c_i32, [c_i32, c_i64]),
-    "lmoe_mm_id_workspace_bytes": (c_sz, [c_i64, c_i64, c_i64, c_i64]),
+    "lmoe_mm_id_workspace_bytes": (c_sz, [c_vp, c_i64, c_i64, c_i64]),
     "lmoe_mul_mm_id_shared": (c_i32, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_i64, c_i64, c_vp, c_i64, c_i64,
                                       c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_mul_mm_id": (c_i32, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
@@ -48,6 +48,7 @@ PROTOTYPES = {
     "lmoe_moe_forward_prefill": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_host": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_forward_rows": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_rows_workspace_bytes": (c_sz, [c_vp, c_i64]),
     "lmoe_shared_forward": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_check_device_flag": (c_i32, [c_vp, c_vp]),
 }

@@ -1,0 +1,536 @@
+// Grouped (indexed) quantized GEMM on the 5th-generation tensor cores: for every
+// expert e, the rows routed to e times W[e]^T, scattered back to [t, top_k, n_out].
+//
+// Reference: `ops::mul_mm_id{,_shared}`, src/ops/mm_id.rs:16-39 ->
+// kernel_mul_mm_id_q{4,6}_K_f32_t, src/ops/mm_id.metal:492-647 (f16 operand
+// tiles, f32 accumulation); per-expert lists from map0, src/ops/mm_id.metal:207-269.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0        raw loader : cp.async.bulk of the tile's quantized super-blocks
+//   warps 1-4     dequant    : raw Q4_K/Q6_K -> f16 A tile (128 rows x 64 k) written in the
+//                              tensor core's K-major 128-byte-swizzled layout
+//   warps 5-8     B loader   : cp.async gathers of the routed rows' f16 activations
+//                              (256 rows x 64 k) into the same swizzled layout
+//   warp 9        MMA        : one thread issues tcgen05.mma (M=128, N<=256, K=16),
+//                              accumulators in TMEM (two buffers of 256 columns)
+//   warps 10-13   epilogue   : tcgen05.ld, optional row scale, scatter to the output rows
+// The weight tile is the A operand (M = 128 output features) and the routed
+// rows are the N dimension, so ragged per-expert row counts cost only a
+// rounding to 16.  Every wait is bounded; a wait that runs out records a flag
+// and the kernel drains and exits.
+#include "fused.cuh"
+#include "kquant.cuh"
+
+namespace {
+
+constexpr int MM_M = 128;      // weight rows per tile
+constexpr int MM_N = 256;      // routed rows per tile
+constexpr int MM_K = 64;       // k per pipeline stage (one 128-byte swizzle row of f16)
+constexpr int MM_THREADS = 14 * 32;
+constexpr int A_STAGE_BYTES = MM_M * MM_K * 2; // 16 KB
+constexpr int B_STAGE_BYTES = MM_N * MM_K * 2; // 32 KB
+constexpr uint32_t MM_SPIN = 1u << 24;
+
+struct MmParams {
+    const uint8_t *w;        // stack blocks
+    int64_t expert_bytes;
+    int dtype, n_expert, n_out, k;
+    const __half *xh;        // f16 activations [src_rows, k]
+    int x_per_row, top_k, t; // source row of flat id f: x_per_row == 1 ? f / top_k : f
+    const uint32_t *tpe;     // [n_expert] rows per expert
+    const int32_t *ids_map;  // [n_expert, map_stride] flat ids
+    int map_stride;
+    const int32_t *tiles;    // [n_tiles][4] = expert, first list index, valid rows, m0
+    const int32_t *n_tiles;  // device scalar
+    const float *row_scale;  // per flat id, or NULL
+    float *out;              // [t*top_k, n_out] f32
+    uint32_t *flag;          // device flag words
+    int n_stage, raw_slots, raw_slot_bytes;
+};
+
+// ---- PTX helpers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint64_t *b, uint32_t c) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(c));
+}
+__device__ __forceinline__ void mb_arrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void mb_expect_tx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mb_try(uint64_t *b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and records the flag) when the limit runs out.
+__device__ __forceinline__ bool mb_wait(uint64_t *b, uint32_t parity, uint32_t *flag, uint32_t where) {
+    for (uint32_t i = 0; i < MM_SPIN; i++)
+        if (mb_try(b, parity)) return true;
+    if (atomicCAS(flag, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
+        flag[1] = 0x1000u + where;
+        flag[2] = blockIdx.x;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)),
+                 "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc),
+        "r"(accum) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte-swizzled operand tile: rows of 64 f16 (128 B); groups of 8 rows are
+// 1024 B apart; the 16-byte chunk c of row r sits at chunk position c ^ (r % 8).
+__device__ __forceinline__ uint32_t swz_off(int r, int chunk) {
+    return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
+}
+// Shared-memory matrix descriptor of such a tile (start address advanced by 32 B per K=16 step).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    const uint64_t lo = (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16);           // LBO (unused) = 16 B
+    const uint64_t hi = (uint64_t)(1024 >> 4) | ((uint64_t)1 << 14) | ((uint64_t)2 << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
+    return lo | (hi << 32);
+}
+
+// ---- dequantisation into the swizzled A tile ------------------------------------
+// (1024 + a | 1024 + b) - off, times scale, minus bias: exact integers in f16, one rounding in the fma
+__device__ __forceinline__ uint32_t h2_sub_fma(uint32_t v, uint32_t off, __half2 s, __half2 m) {
+    const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&v), *reinterpret_cast<const __half2 *>(&off));
+    const __half2 r = __hfma2(q, s, m);
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// One row, 64 weights of a Q4_K super-block (sub-block pair j) -> 8 chunks of 8 halfs.
+// Within a chunk the order is [0 2 1 3 4 6 5 7]; the activation rows use the same order.
+__device__ __forceinline__ void dequant_q4k_row64(const uint8_t *blk, int j, uint8_t *a_stage, int r) {
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = lmoe_h2f((uint16_t)(dm & 0xffff)), dmin = lmoe_h2f((uint16_t)(dm >> 16));
+    int sc0, mn0, sc1, mn1;
+    q4k_scale_min(blk + 4, 2 * j, sc0, mn0);
+    q4k_scale_min(blk + 4, 2 * j + 1, sc1, mn1);
+    const __half2 s_lo = __float2half2_rn(d * (float)sc0), m_lo = __float2half2_rn(-dmin * (float)mn0);
+    const __half2 s_hi = __float2half2_rn(d * (float)sc1), m_hi = __float2half2_rn(-dmin * (float)mn1);
+    const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j);
+    const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * j);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t v = w[2 * c + h], v8 = v >> 8;
+            lo[2 * h] = h2_sub_fma((v & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            lo[2 * h + 1] = h2_sub_fma((v8 & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            hi[2 * h] = h2_sub_fma((v & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+            hi[2 * h + 1] = h2_sub_fma((v8 & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+        }
+        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c + 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+__device__ __forceinline__ uint32_t ld32_a2(const uint8_t *p) {
+    const uint16_t *q = reinterpret_cast<const uint16_t *>(p);
+    return (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+}
+
+// One row, 64 weights of a Q6_K super-block: quarter js (k = 64*js .. 64*js+63), i.e. the
+// groups i = 2*(js&1) and i+1 of half n = js>>1 (group i: 4 bits from ql, 2 bits (2i, 2i+1) from qh).
+__device__ __forceinline__ void dequant_q6k_row64(const uint8_t *blk, int js, uint8_t *a_stage, int r) {
+    const int n = js >> 1, hi_nib = js & 1; // groups 0,1 use the low nibbles of ql, groups 2,3 the high nibbles
+    const float d = lmoe_h2f(*reinterpret_cast<const uint16_t *>(blk + 208));
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192) + 8 * n + 4 * hi_nib;
+    const uint8_t *ql = blk + 64 * n, *qh = blk + 128 + 32 * n;
+    // low nibble: 6-bit q lands in mantissa bits 0-5 (1024 + q); high nibble: bits 4-9 (1024 + 16 q)
+    const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
+    const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u; // 1024 + 16*32 | 1024 + 32
+    const float pw = hi_nib ? 0.0625f : 1.0f;
+    const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+    for (int gi = 0; gi < 2; gi++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) { // 8 l-values per chunk
+            const __half2 s = __float2half2_rn(d * (float)sc[2 * gi + (c >> 1)] * pw);
+            uint32_t o[4];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int l = 8 * c + 4 * h;
+                const uint32_t q = ld32_a2(ql + 32 * gi + l), hh = ld32_a2(qh + l);
+                const uint32_t h02 = gi ? (hh << 2) : (hh << 4); // bytes 0, 2 of the word
+                const uint32_t h13 = gi ? (hh >> 6) : (hh >> 4); // bytes 1, 3
+                const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
+                const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
+                o[2 * h] = h2_sub_fma(v02, off, s, zero);
+                o[2 * h + 1] = h2_sub_fma(v13, off, s, zero);
+            }
+            *reinterpret_cast<uint4 *>(a_stage + swz_off(r, 4 * gi + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// ---- tile list -----------------------------------------------------------------------
+// tiles[i] = {expert, first list index, valid rows, first weight row}; m tiles vary fastest so
+// CTAs running side by side share the same activation rows in L2.
+__global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__restrict__ tpe, int n_expert, int n_out,
+                                                          int32_t *__restrict__ tiles, int32_t *__restrict__ n_tiles,
+                                                          int max_tiles) {
+    __shared__ int pre[513];
+    const int m_tiles = (n_out + MM_M - 1) / MM_M;
+    const int e = threadIdx.x;
+    const int cnt = e < n_expert ? (int)((tpe[e] + MM_N - 1) / MM_N) * m_tiles : 0;
+    pre[e + 1] = cnt;
+    if (e == 0) pre[0] = 0;
+    __syncthreads();
+    if (e == 0)
+        for (int i = 1; i <= 512; i++) pre[i] += pre[i - 1];
+    __syncthreads();
+    if (e < n_expert) {
+        int o = pre[e];
+        const int rows = (int)tpe[e];
+        for (int n0 = 0; n0 < rows; n0 += MM_N)
+            for (int m = 0; m < m_tiles; m++, o++) {
+                if (o >= max_tiles) break;
+                tiles[4 * o + 0] = e;
+                tiles[4 * o + 1] = n0;
+                tiles[4 * o + 2] = min(MM_N, rows - n0);
+                tiles[4 * o + 3] = m * MM_M;
+            }
+    }
+    if (e == 0) *n_tiles = min(pre[512], max_tiles);
+}
+
+// f32 rows -> f16 rows, each aligned group of 8 stored as [0 2 1 3 4 6 5 7]
+// (the order in which the dequantiser emits a chunk of weights).
+__global__ void to_half_perm_kernel(const float *__restrict__ x, int64_t n8, __half *__restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const float4 a = reinterpret_cast<const float4 *>(x)[2 * i], b = reinterpret_cast<const float4 *>(x)[2 * i + 1];
+    __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.z), __floats2half2_rn(a.y, a.w), __floats2half2_rn(b.x, b.z),
+                                  __floats2half2_rn(b.y, b.w)};
+    reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(h);
+}
+
+struct MmSmem {
+    int o_raw, o_a, o_b, o_bar, o_tmem, total;
+    __host__ __device__ MmSmem(int n_stage, int raw_slots, int raw_slot_bytes) {
+        int o = 0;
+        o_a = o; o += n_stage * A_STAGE_BYTES;
+        o_b = o; o += n_stage * B_STAGE_BYTES;
+        o_raw = o; o += raw_slots * ((raw_slot_bytes + 127) / 128 * 128);
+        o_bar = o; o += 8 * (3 * 8 + 2 * 4 + 4);
+        o_tmem = o; o += 16;
+        total = o + 1024; // slack to align the base to 1024 B
+    }
+};
+
+// ---- the grouped GEMM kernel -------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_constant__ MmParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const MmSmem L(P.n_stage, P.raw_slots, P.raw_slot_bytes);
+    uint8_t *a_st = smem + L.o_a, *b_st = smem + L.o_b, *raw = smem + L.o_raw;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.o_bar);
+    uint64_t *a_full = bars, *b_full = bars + 8, *ab_empty = bars + 16, *raw_full = bars + 24, *raw_empty = bars + 28;
+    uint64_t *acc_full = bars + 32, *acc_empty = bars + 34;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L.o_tmem);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = P.n_stage;
+    const int n_tiles = *P.n_tiles;
+    const int k_stages = P.k / MM_K;
+    const int ts = DT == LMOE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+    const int row_bytes = P.k / QK_K * ts;
+    const int raw_slot_stride = (P.raw_slot_bytes + 127) / 128 * 128;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) {
+            mb_init(&a_full[s], 4);
+            mb_init(&b_full[s], 128);
+            mb_init(&ab_empty[s], 1);
+        }
+        for (int s = 0; s < P.raw_slots; s++) {
+            mb_init(&raw_full[s], 1);
+            mb_init(&raw_empty[s], 4);
+        }
+        for (int s = 0; s < 2; s++) {
+            mb_init(&acc_full[s], 1);
+            mb_init(&acc_empty[s], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================= raw loader =================
+        uint32_t rg = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int e = P.tiles[4 * tile], m0 = P.tiles[4 * tile + 3];
+            const int vrows = min(MM_M, P.n_out - m0);
+            const uint8_t *wt = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
+            if (DT == LMOE_Q4_K) {
+                for (int sb = 0; sb < P.k / QK_K && ok; sb++, rg++) {
+                    const int slot = rg % P.raw_slots;
+                    ok = mb_wait(&raw_empty[slot], ((rg / P.raw_slots) & 1) ^ 1, P.flag, 1);
+                    if (lane == 0) mb_expect_tx(&raw_full[slot], (uint32_t)vrows * Q4K_BYTES);
+                    __syncwarp();
+                    uint8_t *dst = raw + (size_t)slot * raw_slot_stride;
+                    for (int r = lane; r < vrows; r += 32)
+                        bulk_g2s(dst + r * Q4K_BYTES, wt + (size_t)r * row_bytes + (size_t)sb * Q4K_BYTES, Q4K_BYTES,
+                                 &raw_full[slot]);
+                }
+            } else {
+                const int slot = rg % P.raw_slots;
+                ok = mb_wait(&raw_empty[slot], ((rg / P.raw_slots) & 1) ^ 1, P.flag, 1);
+                if (lane == 0) {
+                    const uint32_t bytes = (uint32_t)vrows * row_bytes;
+                    mb_expect_tx(&raw_full[slot], bytes);
+                    bulk_g2s(raw + (size_t)slot * raw_slot_stride, wt, bytes, &raw_full[slot]);
+                }
+                __syncwarp();
+                rg++;
+            }
+        }
+    } else if (warp <= 4) {
+        // ================= dequant: thread = weight row =================
+        const int r = (warp - 1) * 32 + lane;
+        uint32_t g = 0, rg = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int m0 = P.tiles[4 * tile + 3];
+            const bool rvalid = m0 + r < P.n_out;
+            for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                const int s = g % NS;
+                const int slot = rg % P.raw_slots;
+                const bool first = DT == LMOE_Q4_K ? (ks & 3) == 0 : ks == 0;
+                const bool last = DT == LMOE_Q4_K ? (ks & 3) == 3 : ks == k_stages - 1;
+                if (first) ok = mb_wait(&raw_full[slot], (rg / P.raw_slots) & 1, P.flag, 2);
+                ok = ok && mb_wait(&ab_empty[s], ((g / NS) & 1) ^ 1, P.flag, 3);
+                uint8_t *ast = a_st + (size_t)s * A_STAGE_BYTES;
+                const uint8_t *rs = raw + (size_t)slot * raw_slot_stride;
+                if (rvalid) {
+                    if (DT == LMOE_Q4_K) dequant_q4k_row64(rs + r * Q4K_BYTES, ks & 3, ast, r);
+                    else dequant_q6k_row64(rs + (size_t)r * row_bytes + (ks >> 2) * Q6K_BYTES, ks & 3, ast, r);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mb_arrive(&a_full[s]);
+                    if (last) mb_arrive(&raw_empty[slot]);
+                }
+                if (last) rg++;
+            }
+        }
+    } else if (warp <= 8) {
+        // ================= B loader: gathered f16 activation rows =================
+        const int bt = (warp - 5) * 32 + lane;
+        const int c = bt & 7, r0 = bt >> 3; // this thread copies chunk c of rows r0, r0+16, ...
+        uint32_t g = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int e = P.tiles[4 * tile], l0 = P.tiles[4 * tile + 1], nv = P.tiles[4 * tile + 2];
+            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            const __half *src[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int rr = r0 + 16 * i;
+                const int fid = rr < nv ? list[rr] : 0;
+                const int srow = P.x_per_row == 1 ? fid / P.top_k : fid;
+                src[i] = P.xh + (size_t)srow * P.k + c * 8;
+            }
+            for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                const int s = g % NS;
+                ok = mb_wait(&ab_empty[s], ((g / NS) & 1) ^ 1, P.flag, 4);
+                uint8_t *bst = b_st + (size_t)s * B_STAGE_BYTES;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int rr = r0 + 16 * i;
+                    if (rr < nv) cp_async16(bst + swz_off(rr, c), src[i] + ks * MM_K);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                // the previous stage's copies have landed: make them visible to the tensor core, then signal
+                if (g > 0) {
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    fence_async_smem();
+                    mb_arrive(&b_full[(g - 1) % NS]);
+                }
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (g > 0) {
+            fence_async_smem();
+            mb_arrive(&b_full[(g - 1) % NS]);
+        }
+    } else if (warp == 9) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+                const int nv = P.tiles[4 * tile + 2];
+                const int npad = (nv + 15) & ~15;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
+                const uint32_t buf = it & 1;
+                ok = mb_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, P.flag, 5);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % NS;
+                    ok = mb_wait(&a_full[s], (g / NS) & 1, P.flag, 6) && mb_wait(&b_full[s], (g / NS) & 1, P.flag, 7);
+                    tc_fence_after();
+                    const uint64_t ad = umma_desc(s32(a_st + (size_t)s * A_STAGE_BYTES));
+                    const uint64_t bd = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < MM_K / 16; kk++)
+                        tc_mma_f16(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                    tc_commit(&ab_empty[s]); // frees the stage when these MMAs have read it
+                }
+                tc_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================= epilogue: TMEM -> registers -> scattered rows =================
+        const int q = warp & 3; // TMEM lane quadrant this warp may read
+        const int m = 32 * q + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+            const int e = P.tiles[4 * tile], l0 = P.tiles[4 * tile + 1], nv = P.tiles[4 * tile + 2], m0 = P.tiles[4 * tile + 3];
+            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            const uint32_t buf = it & 1;
+            ok = mb_wait(&acc_full[buf], (it >> 1) & 1, P.flag, 8);
+            tc_fence_after();
+            const bool mvalid = m0 + m < P.n_out;
+            for (int cb = 0; cb < nv; cb += 32) {
+                uint32_t v[32];
+                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * 256 + cb, v);
+                const int my = cb + lane;
+                const int myfid = my < nv ? list[my] : 0;
+                const float mysc = (P.row_scale && my < nv) ? P.row_scale[myfid] : 1.0f;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                    const float sc = __shfl_sync(0xffffffffu, mysc, j);
+                    if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + m0 + m] = __uint_as_float(v[j]) * sc;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mb_arrive(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+} // namespace
+
+// ---- host side ---------------------------------------------------------------------------
+static int mm_m_tiles(int64_t n_out) { return (int)((n_out + MM_M - 1) / MM_M); }
+
+int64_t mm_max_tiles(int64_t rows, int64_t n_expert, int64_t n_out) {
+    return ((rows + MM_N - 1) / MM_N + n_expert) * mm_m_tiles(n_out);
+}
+
+// Pipeline shape for a stack; false when the tile does not fit in shared memory.
+static bool mm_shape(int dtype, int64_t k, int &n_stage, int &raw_slots, int &raw_slot_bytes) {
+    if (dtype == LMOE_Q4_K) {
+        n_stage = 3; raw_slots = 2; raw_slot_bytes = MM_M * Q4K_BYTES;
+    } else {
+        n_stage = 2; raw_slots = 1; raw_slot_bytes = (int)(MM_M * (k / QK_K) * Q6K_BYTES);
+    }
+    return MmSmem(n_stage, raw_slots, raw_slot_bytes).total <= 227 * 1024;
+}
+
+bool mm_id_kernel_available(int dtype, int64_t n_out, int64_t k) {
+    int a, b, c;
+    if (dtype != LMOE_Q4_K && dtype != LMOE_Q6_K) return false;
+    if (k <= 0 || k % QK_K) return false;
+    if (dtype == LMOE_Q6_K && (n_out & 1)) return false; // whole-tile bulk copies need 16-byte multiples
+    return mm_shape(dtype, k, a, b, c);
+}
+
+size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out) {
+    return lmoe_align_up((size_t)mm_max_tiles(rows, n_expert, n_out) * 16 + 256, 256);
+}
+
+cudaError_t launch_to_half_perm(const float *x, int64_t n, __half *out, cudaStream_t s) {
+    const int64_t n8 = n / 8;
+    if (n8 == 0) return cudaSuccess;
+    to_half_perm_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(x, n8, out);
+    return cudaGetLastError();
+}
+
+// One grouped projection. `xh`: f16 rows (permuted groups of 8); `tiles_ws`: mm_tiles_bytes() scratch
+// whose last 256 bytes hold the tile count; `flag`: 4 device words (zero = clean).
+lmoe_status launch_mm_id(const lmoe_expert_stack *st, const __half *xh, int x_per_row, int top_k, int64_t t,
+                         const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
+                         const float *row_scale, float *out, void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
+    MmParams P;
+    if (!mm_shape(st->dtype, st->k, P.n_stage, P.raw_slots, P.raw_slot_bytes))
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM tile for k=%lld does not fit in shared memory", (long long)st->k);
+    if (st->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
+    const int64_t max_tiles = mm_max_tiles(list_rows, st->n_expert, st->n_out);
+    int32_t *tiles = static_cast<int32_t *>(tiles_ws);
+    int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 16, 256));
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)st->n_expert, (int)st->n_out, tiles, n_tiles, (int)max_tiles);
+    LMOE_LAUNCH_CHECK("build_tiles_kernel");
+    P.w = st->blocks(); P.expert_bytes = st->expert_bytes();
+    P.dtype = st->dtype; P.n_expert = (int)st->n_expert; P.n_out = (int)st->n_out; P.k = (int)st->k;
+    P.xh = xh; P.x_per_row = x_per_row; P.top_k = top_k; P.t = (int)t;
+    P.tpe = tpe; P.ids_map = ids_map; P.map_stride = (int)map_stride;
+    P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.flag = flag;
+    const MmSmem L(P.n_stage, P.raw_slots, P.raw_slot_bytes);
+    static thread_local int c_dev = -1, c_sms = 0;
+    int dev = 0;
+    LMOE_CUDA(cudaGetDevice(&dev));
+    if (dev != c_dev) {
+        LMOE_CUDA(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
+        LMOE_CUDA(cudaFuncSetAttribute(mm_id_kernel<LMOE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        LMOE_CUDA(cudaFuncSetAttribute(mm_id_kernel<LMOE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        c_dev = dev;
+    }
+    if (st->dtype == LMOE_Q4_K) mm_id_kernel<LMOE_Q4_K><<<c_sms, MM_THREADS, L.total, stream>>>(P);
+    else mm_id_kernel<LMOE_Q6_K><<<c_sms, MM_THREADS, L.total, stream>>>(P);
+    LMOE_LAUNCH_CHECK("mm_id_kernel");
+    return LMOE_OK;
+}

@@ -1,19 +1,319 @@
-// Prefill path: expert-sorted grouped GEMM (placeholder until the tensor-core kernel lands).
+// Prefill path: routing, per-expert row lists, grouped tensor-core GEMMs for
+// gate / up / down, SwiGLU with the f16 range guard, fixed-order combine, shared expert.
+// Reference: the mm_id branch of `FusedExperts::forward`, src/moe.rs:236-323, and
+// `MoeBlock::forward`, src/moe.rs:73-78.
 #include "fused.cuh"
 
-#define NOT_YET(name) return lmoe_fail(LMOE_ERR_UNSUPPORTED, name " is not built yet")
+// mm_id.cu
+int64_t mm_max_tiles(int64_t rows, int64_t n_expert, int64_t n_out);
+bool mm_id_kernel_available(int dtype, int64_t n_out, int64_t k);
+size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out);
+cudaError_t launch_to_half_perm(const float *x, int64_t n, __half *out, cudaStream_t s);
+lmoe_status launch_mm_id(const lmoe_expert_stack *st, const __half *xh, int x_per_row, int top_k, int64_t t,
+                         const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
+                         const float *row_scale, float *out, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
 
-size_t prefill_workspace_bytes(const lmoe_layer *, int64_t) { return 65536; }
-lmoe_status launch_moe_prefill(const lmoe_layer *, const float *, int64_t, float *, uint32_t *, float *, void *, size_t,
-                               cudaStream_t) { NOT_YET("moe_forward_prefill"); }
-extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *, const float *, const uint32_t *, const float *,
-                                                 int64_t, float *, void *, size_t, void *) { NOT_YET("experts_forward_rows"); }
-extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *, const float *, int64_t, float *, void *, size_t,
-                                           void *) { NOT_YET("shared_forward"); }
-extern "C" int32_t lmoe_mm_id_supported(int32_t, int64_t) { return 0; }
-extern "C" size_t lmoe_mm_id_workspace_bytes(int64_t, int64_t, int64_t, int64_t) { return 0; }
-extern "C" lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *, const float *, int64_t, int64_t, int64_t,
-                                             const uint32_t *, int64_t, int64_t, const void *, int64_t, int64_t,
-                                             int64_t, float *, void *, size_t, void *) { NOT_YET("mul_mm_id_shared"); }
-extern "C" lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *, const float *, int64_t, int64_t, int64_t,
-                                      const uint32_t *, int64_t, int64_t, float *, void *, size_t, void *) { NOT_YET("mul_mm_id"); }
+namespace {
+
+// One warp per row: act = silu(g) * u; l2 = clamp(||act||, 1e-8, 1e30); the f16 operand of the
+// down projection is act * 32768 / l2 (src/moe.rs:292-302) stored with groups of 8 permuted
+// [0 2 1 3 4 6 5 7]; scale[row] = l2 * 2^-15 * weight[row] undoes it in the down epilogue
+// together with the routing weight (src/ops/combine.metal:102-133).
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restrict__ g, const float *__restrict__ u,
+                                                          const float *__restrict__ w, int64_t rows, int ff,
+                                                          __half *__restrict__ act, float *__restrict__ scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float *gr = g + row * ff, *ur = u + row * ff;
+    float ss = 0.f;
+    for (int i = lane * 8; i < ff; i += 256) {
+        const float4 g0 = *reinterpret_cast<const float4 *>(gr + i), g1 = *reinterpret_cast<const float4 *>(gr + i + 4);
+        const float4 u0 = *reinterpret_cast<const float4 *>(ur + i), u1 = *reinterpret_cast<const float4 *>(ur + i + 4);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float a = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, expf(-gv[j]))), uv[j]);
+            ss += a * a;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float l2 = fminf(fmaxf(sqrtf(ss), 1e-8f), 1e30f);
+    const float k = 32768.0f / l2;
+    for (int i = lane * 8; i < ff; i += 256) {
+        const float4 g0 = *reinterpret_cast<const float4 *>(gr + i), g1 = *reinterpret_cast<const float4 *>(gr + i + 4);
+        const float4 u0 = *reinterpret_cast<const float4 *>(ur + i), u1 = *reinterpret_cast<const float4 *>(ur + i + 4);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) a[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, expf(-gv[j]))), uv[j]) * k;
+        __align__(16) __half2 h[4] = {__floats2half2_rn(a[0], a[2]), __floats2half2_rn(a[1], a[3]),
+                                      __floats2half2_rn(a[4], a[6]), __floats2half2_rn(a[5], a[7])};
+        *reinterpret_cast<uint4 *>(act + row * ff + i) = *reinterpret_cast<const uint4 *>(h);
+    }
+    if (lane == 0) scale[row] = l2 * 0x1p-15f * (w ? w[row] : 1.0f);
+}
+
+// out[t, c] = sum over slots (in slot order) of y[t, s, c], then + shared[t, c].
+__global__ void sum_slots_kernel(const float *__restrict__ y, const float *__restrict__ shared, int64_t t, int top_k,
+                                 int n4, float *__restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= t * n4) return;
+    const int64_t tok = i / n4, c = i - tok * n4;
+    const float4 *yp = reinterpret_cast<const float4 *>(y) + tok * top_k * n4 + c;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top_k; k++) {
+        const float4 v = yp[(int64_t)k * n4];
+        s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+    }
+    if (shared) {
+        const float4 v = reinterpret_cast<const float4 *>(shared)[i];
+        s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+    }
+    reinterpret_cast<float4 *>(out)[i] = s;
+}
+
+// identity row list for a one-expert stack: tpe[0] = t, ids_map[i] = i
+__global__ void iota_list_kernel(int64_t t, uint32_t *tpe, int32_t *ids_map) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0) tpe[0] = (uint32_t)t;
+    if (i < t) ids_map[i] = (int32_t)i;
+}
+
+struct Carver {
+    uint8_t *base;
+    size_t off;
+    template <typename T>
+    T *take(size_t count) {
+        T *p = reinterpret_cast<T *>(base + off);
+        off += lmoe_align_up(count * sizeof(T), 256);
+        return p;
+    }
+};
+
+// Scratch of one grouped SwiGLU FFN over `rows` routed rows.
+size_t ffn_bytes(int64_t rows, int64_t hidden, int64_t ff, int64_t n_expert) {
+    size_t o = 0;
+    o += 2 * lmoe_align_up((size_t)rows * ff * 4, 256);      // gate, up
+    o += lmoe_align_up((size_t)rows * ff * 2, 256);          // f16 activation
+    o += lmoe_align_up((size_t)rows * 4, 256);               // row scale
+    const size_t t1 = mm_tiles_bytes(rows, n_expert, ff), t2 = mm_tiles_bytes(rows, n_expert, hidden);
+    o += t1 > t2 ? t1 : t2;
+    return o;
+}
+
+// y[rows, hidden] = row_weight * FFN_{expert of row}(x rows); lists as produced by map0.
+lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const lmoe_expert_stack *down,
+                        const __half *xh, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
+                        int64_t map_stride, const float *row_w, float *y, uint8_t *ws, uint32_t *flag,
+                        cudaStream_t s) {
+    const int64_t rows = t * top_k, ff = gate->n_out, hidden = down->n_out;
+    Carver c{ws, 0};
+    float *g = c.take<float>((size_t)rows * ff), *u = c.take<float>((size_t)rows * ff);
+    __half *act = c.take<__half>((size_t)rows * ff);
+    float *rs = c.take<float>((size_t)rows);
+    void *tiles = ws + c.off;
+    lmoe_status st;
+    if ((st = launch_mm_id(gate, xh, 1, top_k, t, tpe, ids_map, map_stride, rows, nullptr, g, tiles, flag, s))) return st;
+    if ((st = launch_mm_id(up, xh, 1, top_k, t, tpe, ids_map, map_stride, rows, nullptr, u, tiles, flag, s))) return st;
+    swiglu_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, u, row_w, rows, (int)ff, act, rs);
+    LMOE_LAUNCH_CHECK("swiglu_rows_kernel");
+    if ((st = launch_mm_id(down, act, top_k, top_k, t, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s))) return st;
+    return LMOE_OK;
+}
+
+bool layer_mm_ok(const lmoe_layer *L) {
+    return mm_id_kernel_available(L->gate->dtype, L->expert_ff, L->hidden) &&
+           mm_id_kernel_available(L->down->dtype, L->hidden, L->expert_ff) && L->expert_ff % 256 == 0 &&
+           L->hidden % 8 == 0;
+}
+
+} // namespace
+
+size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
+    if (t < 1) t = 1;
+    const int64_t rows = t * L->top_k;
+    size_t o = 65536;
+    o += lmoe_align_up((size_t)t * L->n_expert * 4, 256);            // logits
+    o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // ids, weights
+    o += lmoe_map0_scratch_bytes(L->n_expert, t);
+    o += lmoe_align_up((size_t)t * L->hidden * 2, 256);              // f16 x
+    o += lmoe_align_up((size_t)rows * L->hidden * 4, 256);           // routed partial rows
+    o += lmoe_align_up((size_t)t * L->hidden * 4, 256);              // shared expert rows
+    o += lmoe_align_up((size_t)(t + 64) * 4, 256);                   // identity list
+    o += ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
+    return o;
+}
+
+lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, float *out, uint32_t *ids_out,
+                               float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t s) {
+    if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
+    if (!workspace || workspace_bytes < prefill_workspace_bytes(L, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "prefill workspace needs %zu bytes, got %zu", prefill_workspace_bytes(L, t),
+                         workspace_bytes);
+    if (t * L->top_k > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "too many routed rows");
+    const int64_t rows = t * L->top_k, H = L->hidden;
+    Carver c{static_cast<uint8_t *>(workspace), 65536};
+    uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
+    float *logits = c.take<float>((size_t)t * L->n_expert);
+    uint32_t *ids = c.take<uint32_t>((size_t)rows);
+    float *w = c.take<float>((size_t)rows);
+    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
+    __half *xh = c.take<__half>((size_t)t * H);
+    float *y = c.take<float>((size_t)rows * H);
+    float *ysh = c.take<float>((size_t)t * H);
+    uint32_t *sh_list = c.take<uint32_t>((size_t)t + 64);
+    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+
+    LMOE_CUDA(launch_route_logits(L->router, x, (int)t, (int)H, (int)L->n_expert, logits, s));
+    LMOE_CUDA(launch_route_select(logits, L->bias, (int)t, (int)L->n_expert, (int)L->top_k, L->scale, L->norm, ids, w, s));
+    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
+    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    LMOE_CUDA(launch_map0(ids, (int)t, (int)L->top_k, (int)L->n_expert, tpe, ids_map, s));
+    LMOE_CUDA(launch_to_half_perm(x, t * H, xh, s));
+    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, xh, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s);
+    if (st) return st;
+    const float *shared = nullptr;
+    if (L->sh_gate) {
+        iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64));
+        LMOE_LAUNCH_CHECK("iota_list_kernel");
+        st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, xh, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
+                         nullptr, ysh, ffn_ws, flag, s);
+        if (st) return st;
+        shared = ysh;
+    }
+    const int64_t n = t * (H / 4);
+    sum_slots_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, shared, t, (int)L->top_k, (int)(H / 4), out);
+    LMOE_LAUNCH_CHECK("sum_slots_kernel");
+    if (ids_out) LMOE_CUDA(cudaMemcpyAsync(ids_out, ids, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
+    if (w_out) LMOE_CUDA(cudaMemcpyAsync(w_out, w, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
+    return LMOE_OK;
+}
+
+// ---- op-level entry points ------------------------------------------------------------
+extern "C" int32_t lmoe_mm_id_supported(int32_t dtype, int64_t top_k) {
+    return (dtype == LMOE_Q4_K || dtype == LMOE_Q6_K) && top_k >= 1 ? 1 : 0;
+}
+
+extern "C" size_t lmoe_mm_id_workspace_bytes(const lmoe_expert_stack *stack, int64_t t, int64_t top_k, int64_t x_per_row) {
+    if (!stack || t < 0 || top_k < 1 || x_per_row < 1) return 0;
+    return 256 + lmoe_align_up((size_t)t * x_per_row * stack->k * 2, 256) +
+           mm_tiles_bytes(t * top_k, stack->n_expert, stack->n_out);
+}
+
+static lmoe_status mm_id_run(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row, int64_t k,
+                             const uint32_t *ids, int64_t t_ids, int64_t top_k, const void *map0, float *out,
+                             void *workspace, size_t workspace_bytes, cudaStream_t s) {
+    lmoe_status st = lmoe_id_shape_check(stack, x, t, x_per_row, k, ids, t_ids, top_k, out);
+    if (st) return st;
+    if (!mm_id_kernel_available(stack->dtype, stack->n_out, stack->k))
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for dtype %d, n_out %lld, k %lld", stack->dtype,
+                         (long long)stack->n_out, (long long)stack->k);
+    const size_t need = lmoe_mm_id_workspace_bytes(stack, t, top_k, x_per_row);
+    if (!workspace || workspace_bytes < need)
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "mul_mm_id workspace needs %zu bytes, got %zu", need, workspace_bytes);
+    if (t == 0) return LMOE_OK;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    uint32_t *flag = reinterpret_cast<uint32_t *>(ws);
+    __half *xh = reinterpret_cast<__half *>(ws + 256);
+    void *tiles = ws + 256 + lmoe_align_up((size_t)t * x_per_row * k * 2, 256);
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
+    LMOE_CUDA(launch_to_half_perm(x, t * x_per_row * k, xh, s));
+    const uint32_t *tpe = static_cast<const uint32_t *>(map0);
+    const int32_t *ids_map = reinterpret_cast<const int32_t *>(static_cast<const uint8_t *>(map0) + stack->n_expert * 4);
+    return launch_mm_id(stack, xh, (int)x_per_row, (int)top_k, t, tpe, ids_map, t, t * top_k, nullptr, out, tiles, flag, s);
+}
+
+extern "C" lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
+                                             int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k,
+                                             const void *map0_scratch, int64_t map_n_expert, int64_t map_t,
+                                             int64_t map_top_k, float *out, void *workspace, size_t workspace_bytes,
+                                             void *stream) {
+    lmoe_clear_error();
+    if (!stack) return lmoe_fail(LMOE_ERR_INVALID, "expert stack is NULL");
+    if (!map0_scratch) return lmoe_fail(LMOE_ERR_INVALID, "map0 scratch is NULL");
+    // the consumer re-validates the producer's geometry, src/ops/dispatch.rs:903-909
+    if (map_n_expert != stack->n_expert || map_t != t || map_top_k != top_k)
+        return lmoe_fail(LMOE_ERR_INVALID,
+                         "shared map0 scratch geometry (n_expert=%lld, t=%lld, top_k=%lld) does not match this projection "
+                         "(n_expert=%lld, t=%lld, top_k=%lld); the ids-map offset would be wrong",
+                         (long long)map_n_expert, (long long)map_t, (long long)map_top_k, (long long)stack->n_expert,
+                         (long long)t, (long long)top_k);
+    return mm_id_run(stack, x, t, x_per_row, k, ids, t_ids, top_k, map0_scratch, out, workspace, workspace_bytes,
+                     (cudaStream_t)stream);
+}
+
+extern "C" lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
+                                      int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k, float *out,
+                                      void *workspace, size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!stack) return lmoe_fail(LMOE_ERR_INVALID, "expert stack is NULL");
+    lmoe_status st = lmoe_id_shape_check(stack, x, t, x_per_row, k, ids, t_ids, top_k, out);
+    if (st) return st;
+    const size_t mm = lmoe_mm_id_workspace_bytes(stack, t, top_k, x_per_row), mp = lmoe_map0_scratch_bytes(stack->n_expert, t);
+    if (!workspace || workspace_bytes < mm + mp)
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "mul_mm_id workspace needs %zu bytes, got %zu", mm + mp, workspace_bytes);
+    uint8_t *map0 = static_cast<uint8_t *>(workspace) + mm;
+    LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)stack->n_expert, reinterpret_cast<uint32_t *>(map0),
+                          reinterpret_cast<int32_t *>(map0 + stack->n_expert * 4), (cudaStream_t)stream));
+    return mm_id_run(stack, x, t, x_per_row, k, ids, t_ids, top_k, map0, out, workspace, mm, (cudaStream_t)stream);
+}
+
+// ---- expert-parallel pieces -------------------------------------------------------------
+static size_t rows_ws_bytes(const lmoe_layer *L, int64_t rows) {
+    return 65536 + lmoe_map0_scratch_bytes(L->n_expert, rows) + lmoe_align_up((size_t)rows * L->hidden * 2, 256) +
+           ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
+}
+
+extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *L, const float *x, const uint32_t *local_ids,
+                                                 const float *row_weights, int64_t rows, float *out, void *workspace,
+                                                 size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!L || !x || !local_ids || !out) return lmoe_fail(LMOE_ERR_INVALID, "layer/x/local_ids/out is NULL");
+    if (rows < 0 || rows > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "rows out of range");
+    if (rows == 0) return LMOE_OK;
+    if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
+    if (!workspace || workspace_bytes < rows_ws_bytes(L, rows))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", rows_ws_bytes(L, rows), workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    Carver c{static_cast<uint8_t *>(workspace), 65536};
+    uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
+    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, rows));
+    __half *xh = c.take<__half>((size_t)rows * L->hidden);
+    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
+    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    LMOE_CUDA(launch_map0(local_ids, (int)rows, 1, (int)L->n_expert, tpe, ids_map, s));
+    LMOE_CUDA(launch_to_half_perm(x, rows * L->hidden, xh, s));
+    return ffn_grouped(L->gate, L->up, L->down, xh, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s);
+}
+
+extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, int64_t t, float *out, void *workspace,
+                                           size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!L || !x || !out) return lmoe_fail(LMOE_ERR_INVALID, "layer/x/out is NULL");
+    if (!L->sh_gate) return lmoe_fail(LMOE_ERR_INVALID, "the layer has no shared expert");
+    if (t < 0 || t > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "t out of range");
+    if (t == 0) return LMOE_OK;
+    if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
+    if (!workspace || workspace_bytes < rows_ws_bytes(L, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", rows_ws_bytes(L, t), workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    Carver c{static_cast<uint8_t *>(workspace), 65536};
+    uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
+    uint32_t *list = c.take<uint32_t>((size_t)t + 64);
+    __half *xh = c.take<__half>((size_t)t * L->hidden);
+    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+    iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, list, reinterpret_cast<int32_t *>(list + 64));
+    LMOE_LAUNCH_CHECK("iota_list_kernel");
+    LMOE_CUDA(launch_to_half_perm(x, t * L->hidden, xh, s));
+    return ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, xh, 1, t, list, reinterpret_cast<int32_t *>(list + 64), t, nullptr,
+                       out, ffn_ws, flag, s);
+}
+
+extern "C" size_t lmoe_rows_workspace_bytes(const lmoe_layer *L, int64_t rows) {
+    return L ? rows_ws_bytes(L, rows < 1 ? 1 : rows) : 0;
+}

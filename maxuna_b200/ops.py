@@ -123,7 +123,7 @@ def mul_mm_id_shared(stack: ExpertStack, x: torch.Tensor, ids: torch.Tensor, scr
     _ids_dev(ids)
     t_ids, top_k = ids.shape
     out = torch.empty(t_ids, top_k, stack.n_out, dtype=torch.float32, device=x.device)
-    ws_bytes = lib().lmoe_mm_id_workspace_bytes(t, top_k, xpr, k)
+    ws_bytes = lib().lmoe_mm_id_workspace_bytes(stack.handle, t, top_k, xpr)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     check(lib().lmoe_mul_mm_id_shared(stack.handle, x.data_ptr(), t, xpr, k, ids.data_ptr(), t_ids, top_k,
                                       scratch.buffer.data_ptr(), scratch.n_expert, scratch.t, scratch.top_k,
@@ -136,7 +136,7 @@ def mul_mm_id(stack: ExpertStack, x: torch.Tensor, ids: torch.Tensor) -> torch.T
     _ids_dev(ids)
     t_ids, top_k = ids.shape
     out = torch.empty(t_ids, top_k, stack.n_out, dtype=torch.float32, device=x.device)
-    ws_bytes = lib().lmoe_mm_id_workspace_bytes(t, top_k, xpr, k) + lib().lmoe_map0_scratch_bytes(stack.n_expert, t)
+    ws_bytes = lib().lmoe_mm_id_workspace_bytes(stack.handle, t, top_k, xpr) + lib().lmoe_map0_scratch_bytes(stack.n_expert, t)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     check(lib().lmoe_mul_mm_id(stack.handle, x.data_ptr(), t, xpr, k, ids.data_ptr(), t_ids, top_k, out.data_ptr(),
                                ws.data_ptr(), ws_bytes, stream_ptr()))
