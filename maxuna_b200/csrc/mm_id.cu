@@ -7,13 +7,13 @@
 //
 // One persistent CTA per SM, warp-specialised:
 //   warp 0        raw loader : cp.async.bulk of the tile's quantized super-blocks
-//   warps 1-4     dequant    : raw Q4_K/Q6_K -> f16 A tile (128 rows x 64 k) written in the
+//   warps 1-8     dequant    : raw Q4_K/Q6_K -> f16 A tile (128 rows x 64 k) written in the
 //                              tensor core's K-major 128-byte-swizzled layout
-//   warps 5-8     B loader   : cp.async gathers of the routed rows' f16 activations
-//                              (256 rows x 64 k) into the same swizzled layout
-//   warp 9        MMA        : one thread issues tcgen05.mma (M=128, N<=256, K=16),
+//   warp 9        B loader   : one bulk copy per stage of the routed rows' f16 activations
+//                              (256 rows x 64 k), stored in global memory in tile order
+//   warp 11       MMA        : one thread issues tcgen05.mma (M=128, N<=256, K=16),
 //                              accumulators in TMEM (two buffers of 256 columns)
-//   warps 10-13   epilogue   : tcgen05.ld, optional row scale, scatter to the output rows
+//   warps 12-15   epilogue   : tcgen05.ld, optional row scale, scatter to the output rows
 // The weight tile is the A operand (M = 128 output features) and the routed
 // rows are the N dimension, so ragged per-expert row counts cost only a
 // rounding to 16.  Every wait is bounded; a wait that runs out records a flag
@@ -26,7 +26,7 @@ namespace {
 constexpr int MM_M = 128;      // weight rows per tile
 constexpr int MM_N = 256;      // routed rows per tile
 constexpr int MM_K = 64;       // k per pipeline stage (one 128-byte swizzle row of f16)
-constexpr int MM_THREADS = 14 * 32;
+constexpr int MM_THREADS = 16 * 32;
 constexpr int A_STAGE_BYTES = MM_M * MM_K * 2; // 16 KB
 constexpr int B_STAGE_BYTES = MM_N * MM_K * 2; // 32 KB
 constexpr uint32_t MM_SPIN = 1u << 24;
@@ -35,17 +35,16 @@ struct MmParams {
     const uint8_t *w;        // stack blocks
     int64_t expert_bytes;
     int dtype, n_expert, n_out, k;
-    const __half *xh;        // f16 activations [src_rows, k]
-    int x_per_row, top_k, t; // source row of flat id f: x_per_row == 1 ? f / top_k : f
+    const uint8_t *xt;       // f16 activations, already in tile order (see gather_tiles_kernel)
     const uint32_t *tpe;     // [n_expert] rows per expert
     const int32_t *ids_map;  // [n_expert, map_stride] flat ids
     int map_stride;
-    const int32_t *tiles;    // [n_tiles][4] = expert, first list index, valid rows, m0
+    const int32_t *tiles;    // [n_tiles][8] = expert, first list index, valid rows, m0, row-tile slot
     const int32_t *n_tiles;  // device scalar
     const float *row_scale;  // per flat id, or NULL
     float *out;              // [t*top_k, n_out] f32
     uint32_t *flag;          // device flag words
-    int n_stage, raw_slots, raw_slot_bytes;
+    int n_stage, n_stage_b, raw_slots, raw_slot_bytes;
 };
 
 // ---- PTX helpers ---------------------------------------------------------------
@@ -126,32 +125,29 @@ __device__ __forceinline__ uint32_t h2_sub_fma(uint32_t v, uint32_t off, __half2
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
-// One row, 64 weights of a Q4_K super-block (sub-block pair j) -> 8 chunks of 8 halfs.
+// Half a row-stage: the 32 weights of one Q4_K sub-block (sub-block 2j + half) -> 4 chunks of 8 halfs.
 // Within a chunk the order is [0 2 1 3 4 6 5 7]; the activation rows use the same order.
-__device__ __forceinline__ void dequant_q4k_row64(const uint8_t *blk, int j, uint8_t *a_stage, int r) {
+__device__ __forceinline__ void dequant_q4k_row32(const uint8_t *blk, int j, int half, uint8_t *a_stage, int r) {
     const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
     const float d = lmoe_h2f((uint16_t)(dm & 0xffff)), dmin = lmoe_h2f((uint16_t)(dm >> 16));
-    int sc0, mn0, sc1, mn1;
-    q4k_scale_min(blk + 4, 2 * j, sc0, mn0);
-    q4k_scale_min(blk + 4, 2 * j + 1, sc1, mn1);
-    const __half2 s_lo = __float2half2_rn(d * (float)sc0), m_lo = __float2half2_rn(-dmin * (float)mn0);
-    const __half2 s_hi = __float2half2_rn(d * (float)sc1), m_hi = __float2half2_rn(-dmin * (float)mn1);
+    int sc, mn;
+    q4k_scale_min(blk + 4, 2 * j + half, sc, mn);
+    const __half2 s = __float2half2_rn(d * (float)sc), m = __float2half2_rn(-dmin * (float)mn);
     const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j);
     const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * j);
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    // low nibble -> 1024 + q (magic 0x6400); high nibble in place -> 64 + q (magic 0x5400)
+    const uint32_t mask = half ? 0x00F000F0u : 0x000F000Fu, magic = half ? 0x54005400u : 0x64006400u;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-        uint32_t lo[4], hi[4];
+        uint32_t o[4];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint32_t v = w[2 * c + h], v8 = v >> 8;
-            lo[2 * h] = h2_sub_fma((v & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
-            lo[2 * h + 1] = h2_sub_fma((v8 & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
-            hi[2 * h] = h2_sub_fma((v & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
-            hi[2 * h + 1] = h2_sub_fma((v8 & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+            const uint32_t v = w[2 * c + h];
+            o[2 * h] = h2_sub_fma((v & mask) | magic, magic, s, m);
+            o[2 * h + 1] = h2_sub_fma(((v >> 8) & mask) | magic, magic, s, m);
         }
-        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c + 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c + 4 * half)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -160,9 +156,9 @@ __device__ __forceinline__ uint32_t ld32_a2(const uint8_t *p) {
     return (uint32_t)q[0] | ((uint32_t)q[1] << 16);
 }
 
-// One row, 64 weights of a Q6_K super-block: quarter js (k = 64*js .. 64*js+63), i.e. the
-// groups i = 2*(js&1) and i+1 of half n = js>>1 (group i: 4 bits from ql, 2 bits (2i, 2i+1) from qh).
-__device__ __forceinline__ void dequant_q6k_row64(const uint8_t *blk, int js, uint8_t *a_stage, int r) {
+// Half a row-stage of a Q6_K super-block: quarter js (k = 64*js .. 64*js+63) holds the groups
+// i = 2*(js&1) + gi, gi = 0, 1, of half n = js>>1 (group i: 4 bits from ql, 2 bits (2i, 2i+1) from qh).
+__device__ __forceinline__ void dequant_q6k_row32(const uint8_t *blk, int js, int gi, uint8_t *a_stage, int r) {
     const int n = js >> 1, hi_nib = js & 1; // groups 0,1 use the low nibbles of ql, groups 2,3 the high nibbles
     const float d = lmoe_h2f(*reinterpret_cast<const uint16_t *>(blk + 208));
     const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192) + 8 * n + 4 * hi_nib;
@@ -172,8 +168,7 @@ __device__ __forceinline__ void dequant_q6k_row64(const uint8_t *blk, int js, ui
     const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u; // 1024 + 16*32 | 1024 + 32
     const float pw = hi_nib ? 0.0625f : 1.0f;
     const __half2 zero = __float2half2_rn(0.f);
-#pragma unroll
-    for (int gi = 0; gi < 2; gi++) {
+    {
 #pragma unroll
         for (int c = 0; c < 4; c++) { // 8 l-values per chunk
             const __half2 s = __float2half2_rn(d * (float)sc[2 * gi + (c >> 1)] * pw);
@@ -195,7 +190,7 @@ __device__ __forceinline__ void dequant_q6k_row64(const uint8_t *blk, int js, ui
 }
 
 // ---- tile list -----------------------------------------------------------------------
-// tiles[i] = {expert, first list index, valid rows, first weight row}; m tiles vary fastest so
+// tiles[i] = {expert, first list index, valid rows, first weight row, row-tile slot}; m tiles vary fastest so
 // CTAs running side by side share the same activation rows in L2.
 __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__restrict__ tpe, int n_expert, int n_out,
                                                           int32_t *__restrict__ tiles, int32_t *__restrict__ n_tiles,
@@ -216,53 +211,94 @@ __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__rest
         for (int n0 = 0; n0 < rows; n0 += MM_N)
             for (int m = 0; m < m_tiles; m++, o++) {
                 if (o >= max_tiles) break;
-                tiles[4 * o + 0] = e;
-                tiles[4 * o + 1] = n0;
-                tiles[4 * o + 2] = min(MM_N, rows - n0);
-                tiles[4 * o + 3] = m * MM_M;
+                tiles[8 * o + 0] = e;
+                tiles[8 * o + 1] = n0;
+                tiles[8 * o + 2] = min(MM_N, rows - n0);
+                tiles[8 * o + 3] = m * MM_M;
+                tiles[8 * o + 4] = pre[e] / m_tiles + n0 / MM_N;
             }
     }
     if (e == 0) *n_tiles = min(pre[512], max_tiles);
 }
 
-// f32 rows -> f16 rows, each aligned group of 8 stored as [0 2 1 3 4 6 5 7]
-// (the order in which the dequantiser emits a chunk of weights).
-__global__ void to_half_perm_kernel(const float *__restrict__ x, int64_t n8, __half *__restrict__ out) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n8) return;
-    const float4 a = reinterpret_cast<const float4 *>(x)[2 * i], b = reinterpret_cast<const float4 *>(x)[2 * i + 1];
-    __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.z), __floats2half2_rn(a.y, a.w), __floats2half2_rn(b.x, b.z),
-                                  __floats2half2_rn(b.y, b.w)};
-    reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(h);
+// Routed rows -> the f16 B operand in TILE ORDER.  Row tile `slot` (256 routed rows of one expert)
+// and k-stage ks (64 values) form one contiguous 32 KB block that is the exact shared-memory image
+// of a B stage: row rr at rr*128 B, its 16-byte chunk c at position c ^ (rr & 7) (the 128-byte
+// swizzle of the tensor core's K-major layout), 8 values per chunk in the order [0 2 1 3 4 6 5 7]
+// (the order in which the dequantiser emits a chunk of weights).  A B stage is then ONE bulk copy.
+// pos[flat id] = slot*256 + rr lets later kernels (SwiGLU) write rows in the same order.
+__device__ __forceinline__ size_t tiled_off(int slot, int k_stages, int ks, int rr, int c) {
+    return (((size_t)slot * k_stages + ks) * MM_N + rr) * 128 + ((size_t)(c ^ (rr & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(256) gather_tiles_kernel(const float *__restrict__ x, int x_per_row, int top_k, int k,
+                                                           const uint32_t *__restrict__ tpe, const int32_t *__restrict__ ids_map,
+                                                           int map_stride, int n_expert, uint8_t *__restrict__ xt,
+                                                           int32_t *__restrict__ pos) {
+    __shared__ int warp_sum[8];
+    __shared__ int slot0_s;
+    const int e = blockIdx.x;
+    // slot of this expert's first row tile = number of row tiles of all earlier experts
+    int part = 0;
+    for (int i = threadIdx.x; i < e; i += 256) part += (int)((tpe[i] + MM_N - 1) / MM_N);
+    for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int i = 0; i < 8; i++) t += warp_sum[i];
+        slot0_s = t;
+    }
+    __syncthreads();
+    const int slot0 = slot0_s, rows = (int)tpe[e], k_stages = k / MM_K, chunks = k / 8;
+    for (int i = blockIdx.y; i < rows; i += gridDim.y) {
+        const int fid = ids_map[(size_t)e * map_stride + i];
+        const float *src = x + (size_t)(x_per_row == 1 ? fid / top_k : fid) * k;
+        const int slot = slot0 + i / MM_N, rr = i % MM_N;
+        if (pos && threadIdx.x == 0) pos[fid] = slot * MM_N + rr;
+        for (int ci = threadIdx.x; ci < chunks; ci += 256) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci + 1);
+            __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.z), __floats2half2_rn(a.y, a.w),
+                                          __floats2half2_rn(b.x, b.z), __floats2half2_rn(b.y, b.w)};
+            *reinterpret_cast<uint4 *>(xt + tiled_off(slot, k_stages, ci >> 3, rr, ci & 7)) = *reinterpret_cast<const uint4 *>(h);
+        }
+    }
 }
 
 struct MmSmem {
     int o_raw, o_a, o_b, o_bar, o_tmem, total;
-    __host__ __device__ MmSmem(int n_stage, int raw_slots, int raw_slot_bytes) {
+    __host__ __device__ MmSmem(int n_stage, int n_stage_b, int raw_slots, int raw_slot_bytes) {
         int o = 0;
         o_a = o; o += n_stage * A_STAGE_BYTES;
-        o_b = o; o += n_stage * B_STAGE_BYTES;
+        o_b = o; o += n_stage_b * B_STAGE_BYTES;
         o_raw = o; o += raw_slots * ((raw_slot_bytes + 127) / 128 * 128);
-        o_bar = o; o += 8 * (3 * 8 + 2 * 4 + 4);
+        o_bar = o; o += 8 * (4 * 8 + 2 * 4 + 4);
         o_tmem = o; o += 16;
         total = o + 1024; // slack to align the base to 1024 B
     }
 };
+
+#ifdef MM_DBG_STAMP
+#define MSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && DT == LMOE_Q4_K && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
+#else
+#define MSTAMP(role, g, i) do { } while (0)
+#endif
 
 // ---- the grouped GEMM kernel -------------------------------------------------------------
 template <int DT>
 __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_constant__ MmParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const MmSmem L(P.n_stage, P.raw_slots, P.raw_slot_bytes);
+    const MmSmem L(P.n_stage, P.n_stage_b, P.raw_slots, P.raw_slot_bytes);
     uint8_t *a_st = smem + L.o_a, *b_st = smem + L.o_b, *raw = smem + L.o_raw;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.o_bar);
     uint64_t *a_full = bars, *b_full = bars + 8, *ab_empty = bars + 16, *raw_full = bars + 24, *raw_empty = bars + 28;
-    uint64_t *acc_full = bars + 32, *acc_empty = bars + 34;
+    uint64_t *acc_full = bars + 32, *acc_empty = bars + 34, *b_empty = bars + 36;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L.o_tmem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NS = P.n_stage;
+    const int NS = P.n_stage, NSB = P.n_stage_b;
     const int n_tiles = *P.n_tiles;
     const int k_stages = P.k / MM_K;
     const int ts = DT == LMOE_Q4_K ? Q4K_BYTES : Q6K_BYTES;
@@ -271,13 +307,16 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
-            mb_init(&a_full[s], 4);
-            mb_init(&b_full[s], 128);
+            mb_init(&a_full[s], 8);
             mb_init(&ab_empty[s], 1);
+        }
+        for (int s = 0; s < NSB; s++) {
+            mb_init(&b_full[s], 1);
+            mb_init(&b_empty[s], 1);
         }
         for (int s = 0; s < P.raw_slots; s++) {
             mb_init(&raw_full[s], 1);
-            mb_init(&raw_empty[s], 4);
+            mb_init(&raw_empty[s], 8);
         }
         for (int s = 0; s < 2; s++) {
             mb_init(&acc_full[s], 1);
@@ -285,7 +324,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == 11) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -299,7 +338,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
         uint32_t rg = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int e = P.tiles[4 * tile], m0 = P.tiles[4 * tile + 3];
+            const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
             const int vrows = min(MM_M, P.n_out - m0);
             const uint8_t *wt = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
             if (DT == LMOE_Q4_K) {
@@ -309,7 +348,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                     if (lane == 0) mb_expect_tx(&raw_full[slot], (uint32_t)vrows * Q4K_BYTES);
                     __syncwarp();
                     uint8_t *dst = raw + (size_t)slot * raw_slot_stride;
+#ifdef MM_DBG_NORAW
+                    if (lane == 0) bulk_g2s(dst, wt, (uint32_t)vrows * Q4K_BYTES, &raw_full[slot]);
+                    for (int r = lane; r < 0; r += 32)
+#else
                     for (int r = lane; r < vrows; r += 32)
+#endif
                         bulk_g2s(dst + r * Q4K_BYTES, wt + (size_t)r * row_bytes + (size_t)sb * Q4K_BYTES, Q4K_BYTES,
                                  &raw_full[slot]);
                 }
@@ -325,32 +369,43 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 rg++;
             }
         }
-    } else if (warp <= 4) {
-        // ================= dequant: thread = weight row =================
-        const int r = (warp - 1) * 32 + lane;
+    } else if (warp <= 8) {
+        // ================= dequant: thread = (weight row, half of the 64-wide stage) =================
+        const int r = ((warp - 1) * 32 + lane) & 127, half = (warp - 1) >> 2;
         uint32_t g = 0, rg = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int m0 = P.tiles[4 * tile + 3];
+            const int m0 = P.tiles[8 * tile + 3];
             const bool rvalid = m0 + r < P.n_out;
             for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                 const int s = g % NS;
                 const int slot = rg % P.raw_slots;
                 const bool first = DT == LMOE_Q4_K ? (ks & 3) == 0 : ks == 0;
                 const bool last = DT == LMOE_Q4_K ? (ks & 3) == 3 : ks == k_stages - 1;
+                if (tid == 32) MSTAMP(0, g, 0);
                 if (first) ok = mb_wait(&raw_full[slot], (rg / P.raw_slots) & 1, P.flag, 2);
+                if (tid == 32) MSTAMP(0, g, 1);
                 ok = ok && mb_wait(&ab_empty[s], ((g / NS) & 1) ^ 1, P.flag, 3);
+                if (tid == 32) MSTAMP(0, g, 2);
                 uint8_t *ast = a_st + (size_t)s * A_STAGE_BYTES;
                 const uint8_t *rs = raw + (size_t)slot * raw_slot_stride;
+#ifdef MM_DBG_NODEQ
+                if (false) {
+#else
                 if (rvalid) {
-                    if (DT == LMOE_Q4_K) dequant_q4k_row64(rs + r * Q4K_BYTES, ks & 3, ast, r);
-                    else dequant_q6k_row64(rs + (size_t)r * row_bytes + (ks >> 2) * Q6K_BYTES, ks & 3, ast, r);
+#endif
+                    if (DT == LMOE_Q4_K) dequant_q4k_row32(rs + r * Q4K_BYTES, ks & 3, half, ast, r);
+                    else dequant_q6k_row32(rs + (size_t)r * row_bytes + (ks >> 2) * Q6K_BYTES, ks & 3, half, ast, r);
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c = 0; c < 4; c++)
+                        *reinterpret_cast<uint4 *>(ast + swz_off(r, c + 4 * half)) = make_uint4(0u, 0u, 0u, 0u);
                 }
+#ifndef MM_DBG_NOFENCE
                 fence_async_smem();
+#endif
                 __syncwarp();
+                if (tid == 32) MSTAMP(0, g, 3);
                 if (lane == 0) {
                     mb_arrive(&a_full[s]);
                     if (last) mb_arrive(&raw_empty[slot]);
@@ -358,53 +413,29 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 if (last) rg++;
             }
         }
-    } else if (warp <= 8) {
-        // ================= B loader: gathered f16 activation rows =================
-        const int bt = (warp - 5) * 32 + lane;
-        const int c = bt & 7, r0 = bt >> 3; // this thread copies chunk c of rows r0, r0+16, ...
-        uint32_t g = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int e = P.tiles[4 * tile], l0 = P.tiles[4 * tile + 1], nv = P.tiles[4 * tile + 2];
-            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
-            const __half *src[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int rr = r0 + 16 * i;
-                const int fid = rr < nv ? list[rr] : 0;
-                const int srow = P.x_per_row == 1 ? fid / P.top_k : fid;
-                src[i] = P.xh + (size_t)srow * P.k + c * 8;
-            }
-            for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                const int s = g % NS;
-                ok = mb_wait(&ab_empty[s], ((g / NS) & 1) ^ 1, P.flag, 4);
-                uint8_t *bst = b_st + (size_t)s * B_STAGE_BYTES;
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int rr = r0 + 16 * i;
-                    if (rr < nv) cp_async16(bst + swz_off(rr, c), src[i] + ks * MM_K);
-                }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                // the previous stage's copies have landed: make them visible to the tensor core, then signal
-                if (g > 0) {
-                    asm volatile("cp.async.wait_group 1;" ::: "memory");
-                    fence_async_smem();
-                    mb_arrive(&b_full[(g - 1) % NS]);
+    } else if (warp <= 10) {
+        // ================= B loader: one bulk copy per stage (the operand is stored in tile order) =======
+        if (warp == 9 && lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
+                const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % NSB;
+                    ok = mb_wait(&b_empty[s], ((g / NSB) & 1) ^ 1, P.flag, 4);
+                    mb_expect_tx(&b_full[s], (uint32_t)nv * 128u);
+                    bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &b_full[s]);
                 }
             }
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (g > 0) {
-            fence_async_smem();
-            mb_arrive(&b_full[(g - 1) % NS]);
-        }
-    } else if (warp == 9) {
+    } else if (warp == 11) {
         // ================= MMA issuer =================
         if (lane == 0) {
             uint32_t g = 0, it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
-                const int nv = P.tiles[4 * tile + 2];
+                const int nv = P.tiles[8 * tile + 2];
                 const int npad = (nv + 15) & ~15;
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
                 const uint32_t buf = it & 1;
@@ -412,15 +443,21 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                    const int s = g % NS;
-                    ok = mb_wait(&a_full[s], (g / NS) & 1, P.flag, 6) && mb_wait(&b_full[s], (g / NS) & 1, P.flag, 7);
+                    const int s = g % NS, sb = g % NSB;
+                    MSTAMP(1, g, 0);
+                    ok = mb_wait(&a_full[s], (g / NS) & 1, P.flag, 6);
+                    MSTAMP(1, g, 1);
+                    ok = ok && mb_wait(&b_full[sb], (g / NSB) & 1, P.flag, 7);
+                    MSTAMP(1, g, 2);
                     tc_fence_after();
                     const uint64_t ad = umma_desc(s32(a_st + (size_t)s * A_STAGE_BYTES));
-                    const uint64_t bd = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
+                    const uint64_t bd = umma_desc(s32(b_st + (size_t)sb * B_STAGE_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < MM_K / 16; kk++)
                         tc_mma_f16(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                    tc_commit(&ab_empty[s]); // frees the stage when these MMAs have read it
+                    tc_commit(&ab_empty[s]); // frees both stages when these MMAs have read them
+                    tc_commit(&b_empty[sb]);
+                    MSTAMP(1, g, 3);
                 }
                 tc_commit(&acc_full[buf]);
             }
@@ -433,7 +470,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
-            const int e = P.tiles[4 * tile], l0 = P.tiles[4 * tile + 1], nv = P.tiles[4 * tile + 2], m0 = P.tiles[4 * tile + 3];
+            const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
             const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
             const uint32_t buf = it & 1;
             ok = mb_wait(&acc_full[buf], (it >> 1) & 1, P.flag, 8);
@@ -459,6 +496,213 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
     }
     tc_fence_before();
     __syncthreads();
+    if (warp == 11) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+
+// ================= gate + up in one pass, SwiGLU in the epilogue =========================
+// Same tile list as above, but a CTA multiplies one block of routed rows by 128 gate rows AND the
+// matching 128 up rows (two accumulators of 256 TMEM columns), so every activation stage is
+// loaded once for both projections.  The quantized rows are read straight from global memory
+// by the dequantising threads (one thread per weight row, two stages prefetched in registers):
+// no staging ring for raw blocks.  Epilogue: act = silu(gate) * up, f32, one row per routed row.
+//   warps 0-7   dequant (thread = (projection, weight row))     warp 8   B loader (bulk copy)
+//   warp 9      MMA issuer                                        warps 10-13  epilogue
+constexpr int GU_THREADS = 14 * 32;
+constexpr int GU_A_STAGE = 2 * A_STAGE_BYTES;
+constexpr int GU_NS = 3;
+
+struct GuParams {
+    const uint8_t *wg, *wu; // gate / up stacks (Q4_K)
+    int64_t expert_bytes;
+    int n_out, k;
+    const uint8_t *xt;
+    const int32_t *ids_map;
+    int map_stride;
+    const int32_t *tiles, *n_tiles;
+    float *act; // [rows, n_out] f32
+    uint32_t *flag;
+};
+
+// 64 weights (sub-block pair j) of one Q4_K row from registers -> 8 swizzled chunks
+__device__ __forceinline__ void dequant_q4k_regs(const uint4 hdr, const uint4 qa, const uint4 qb, int j, uint8_t *a_stage, int r) {
+    const float d = lmoe_h2f((uint16_t)(hdr.x & 0xffff)), dmin = lmoe_h2f((uint16_t)(hdr.x >> 16));
+    uint32_t sc[2], mn[2];
+    q4k_unpack_scales(hdr.y, hdr.z, hdr.w, sc[0], sc[1], mn[0], mn[1]);
+    const uint32_t scw = sc[j >> 1] >> (16 * (j & 1)), mnw = mn[j >> 1] >> (16 * (j & 1));
+    const __half2 s_lo = __float2half2_rn(d * (float)(scw & 0xff)), m_lo = __float2half2_rn(-dmin * (float)(mnw & 0xff));
+    const __half2 s_hi = __float2half2_rn(d * (float)((scw >> 8) & 0xff)), m_hi = __float2half2_rn(-dmin * (float)((mnw >> 8) & 0xff));
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t v = w[2 * c + h], v8 = v >> 8;
+            lo[2 * h] = h2_sub_fma((v & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            lo[2 * h + 1] = h2_sub_fma((v8 & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            hi[2 * h] = h2_sub_fma((v & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+            hi[2 * h + 1] = h2_sub_fma((v8 & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+        }
+        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c + 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+__global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_constant__ GuParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_st = smem, *b_st = smem + GU_NS * GU_A_STAGE;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(b_st + GU_NS * B_STAGE_BYTES);
+    uint64_t *a_full = bars, *b_full = bars + 4, *a_empty = bars + 8, *b_empty = bars + 12, *acc_full = bars + 16, *acc_empty = bars + 17;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = *P.n_tiles;
+    const int k_stages = P.k / MM_K;
+    const int row_bytes = P.k / QK_K * Q4K_BYTES;
+
+    if (tid == 0) {
+        for (int s = 0; s < GU_NS; s++) {
+            mb_init(&a_full[s], 8);
+            mb_init(&b_full[s], 1);
+            mb_init(&a_empty[s], 1);
+            mb_init(&b_empty[s], 1);
+        }
+        mb_init(acc_full, 1);
+        mb_init(acc_empty, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // ---------------- dequant: thread = (projection, weight row) ----------------
+        const int sub = warp >> 2, r = tid & 127;
+        const uint8_t *wbase = sub ? P.wu : P.wg;
+        uint32_t g = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
+            const bool rvalid = m0 + r < P.n_out;
+            const uint8_t *row = wbase + (size_t)e * P.expert_bytes + (size_t)(rvalid ? m0 + r : m0) * row_bytes;
+            // two stages of quantized bytes and one header ahead, in registers
+            uint4 qa0 = __ldg(reinterpret_cast<const uint4 *>(row + 16)), qb0 = __ldg(reinterpret_cast<const uint4 *>(row + 32));
+            uint4 qa1 = __ldg(reinterpret_cast<const uint4 *>(row + 48)), qb1 = __ldg(reinterpret_cast<const uint4 *>(row + 64));
+            uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(row)), hdr_n = hdr;
+            for (int ks = 0; ks < k_stages && ok; ks += 2) {
+#pragma unroll
+                for (int h = 0; h < 2; h++, g++) {
+                    const int kk = ks + h, s = g % GU_NS;
+                    if ((kk & 3) == 0 && kk + 4 < k_stages)
+                        hdr_n = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)((kk >> 2) + 1) * Q4K_BYTES));
+                    ok = ok && mb_wait(&a_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
+                    uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
+                    if (rvalid) {
+                        dequant_q4k_regs(hdr, h ? qa1 : qa0, h ? qb1 : qb0, kk & 3, ast, r);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    // refill this register pair with the stage two ahead
+                    const int kn = kk + 2;
+                    if (kn < k_stages) {
+                        const uint8_t *p = row + (size_t)(kn >> 2) * Q4K_BYTES + 16 + 32 * (kn & 3);
+                        if (h) { qa1 = __ldg(reinterpret_cast<const uint4 *>(p)); qb1 = __ldg(reinterpret_cast<const uint4 *>(p + 16)); }
+                        else { qa0 = __ldg(reinterpret_cast<const uint4 *>(p)); qb0 = __ldg(reinterpret_cast<const uint4 *>(p + 16)); }
+                    }
+                    if ((kk & 3) == 3) hdr = hdr_n;
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mb_arrive(&a_full[s]);
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ---------------- B loader ----------------
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
+                const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % GU_NS;
+                    ok = mb_wait(&b_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 4);
+                    mb_expect_tx(&b_full[s], (uint32_t)nv * 128u);
+                    bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &b_full[s]);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+                const int nv = P.tiles[8 * tile + 2];
+                const int npad = (nv + 15) & ~15;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
+                ok = mb_wait(acc_empty, (it & 1) ^ 1, P.flag, 5);
+                tc_fence_after();
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % GU_NS;
+                    ok = mb_wait(&a_full[s], (g / GU_NS) & 1, P.flag, 6) && mb_wait(&b_full[s], (g / GU_NS) & 1, P.flag, 7);
+                    tc_fence_after();
+                    const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
+                    const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
+                    const uint64_t bd = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < MM_K / 16; kk++) {
+                        tc_mma_f16(tmem_base, ad0 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16(tmem_base + 256, ad1 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&a_empty[s]);
+                    tc_commit(&b_empty[s]);
+                }
+                tc_commit(acc_full);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: act = silu(gate) * up ----------------
+        const int q = warp & 3;
+        const int m = 32 * q + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+            const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
+            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            ok = mb_wait(acc_full, it & 1, P.flag, 8);
+            tc_fence_after();
+            const bool mvalid = m0 + m < P.n_out;
+            for (int cb = 0; cb < nv; cb += 32) {
+                uint32_t vg[32], vu[32];
+                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + cb, vg);
+                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + 256 + cb, vu);
+                const int my = cb + lane;
+                const int myfid = my < nv ? list[my] : 0;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                    const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
+                    const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                    if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mb_arrive(acc_empty);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
     if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
@@ -472,54 +716,59 @@ int64_t mm_max_tiles(int64_t rows, int64_t n_expert, int64_t n_out) {
 }
 
 // Pipeline shape for a stack; false when the tile does not fit in shared memory.
-static bool mm_shape(int dtype, int64_t k, int &n_stage, int &raw_slots, int &raw_slot_bytes) {
+static bool mm_shape(int dtype, int64_t k, int &n_stage, int &n_stage_b, int &raw_slots, int &raw_slot_bytes) {
     if (dtype == LMOE_Q4_K) {
-        n_stage = 3; raw_slots = 2; raw_slot_bytes = MM_M * Q4K_BYTES;
+        n_stage = 3; n_stage_b = 4; raw_slots = 2; raw_slot_bytes = MM_M * Q4K_BYTES;
     } else {
-        n_stage = 2; raw_slots = 1; raw_slot_bytes = (int)(MM_M * (k / QK_K) * Q6K_BYTES);
+        n_stage = 2; n_stage_b = 2; raw_slots = 1; raw_slot_bytes = (int)(MM_M * (k / QK_K) * Q6K_BYTES);
     }
-    return MmSmem(n_stage, raw_slots, raw_slot_bytes).total <= 227 * 1024;
+    return MmSmem(n_stage, n_stage_b, raw_slots, raw_slot_bytes).total <= 227 * 1024;
 }
 
 bool mm_id_kernel_available(int dtype, int64_t n_out, int64_t k) {
-    int a, b, c;
+    int a, b, c, d;
     if (dtype != LMOE_Q4_K && dtype != LMOE_Q6_K) return false;
     if (k <= 0 || k % QK_K) return false;
     if (dtype == LMOE_Q6_K && (n_out & 1)) return false; // whole-tile bulk copies need 16-byte multiples
-    return mm_shape(dtype, k, a, b, c);
+    return mm_shape(dtype, k, a, b, c, d);
 }
 
 size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out) {
-    return lmoe_align_up((size_t)mm_max_tiles(rows, n_expert, n_out) * 16 + 256, 256);
+    return lmoe_align_up((size_t)mm_max_tiles(rows, n_expert, n_out) * 32 + 256, 256);
 }
 
-cudaError_t launch_to_half_perm(const float *x, int64_t n, __half *out, cudaStream_t s) {
-    const int64_t n8 = n / 8;
-    if (n8 == 0) return cudaSuccess;
-    to_half_perm_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(x, n8, out);
+// Bytes of the tile-ordered f16 operand for `rows` routed rows of width k.
+size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k) {
+    return lmoe_align_up((size_t)((rows + MM_N - 1) / MM_N + n_expert) * (size_t)(k / MM_K) * B_STAGE_BYTES, 256);
+}
+
+cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
+                                const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
+                                cudaStream_t s) {
+    gather_tiles_kernel<<<dim3(n_expert, 16), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
+                                                           static_cast<uint8_t *>(xt), pos);
     return cudaGetLastError();
 }
 
-// One grouped projection. `xh`: f16 rows (permuted groups of 8); `tiles_ws`: mm_tiles_bytes() scratch
+// One grouped projection. `xt`: the f16 operand in tile order; `tiles_ws`: mm_tiles_bytes() scratch
 // whose last 256 bytes hold the tile count; `flag`: 4 device words (zero = clean).
-lmoe_status launch_mm_id(const lmoe_expert_stack *st, const __half *xh, int x_per_row, int top_k, int64_t t,
-                         const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
+lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
                          const float *row_scale, float *out, void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
     MmParams P;
-    if (!mm_shape(st->dtype, st->k, P.n_stage, P.raw_slots, P.raw_slot_bytes))
+    if (!mm_shape(st->dtype, st->k, P.n_stage, P.n_stage_b, P.raw_slots, P.raw_slot_bytes))
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM tile for k=%lld does not fit in shared memory", (long long)st->k);
     if (st->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
     const int64_t max_tiles = mm_max_tiles(list_rows, st->n_expert, st->n_out);
     int32_t *tiles = static_cast<int32_t *>(tiles_ws);
-    int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 16, 256));
+    int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
     build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)st->n_expert, (int)st->n_out, tiles, n_tiles, (int)max_tiles);
     LMOE_LAUNCH_CHECK("build_tiles_kernel");
     P.w = st->blocks(); P.expert_bytes = st->expert_bytes();
     P.dtype = st->dtype; P.n_expert = (int)st->n_expert; P.n_out = (int)st->n_out; P.k = (int)st->k;
-    P.xh = xh; P.x_per_row = x_per_row; P.top_k = top_k; P.t = (int)t;
+    P.xt = static_cast<const uint8_t *>(xt);
     P.tpe = tpe; P.ids_map = ids_map; P.map_stride = (int)map_stride;
     P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.flag = flag;
-    const MmSmem L(P.n_stage, P.raw_slots, P.raw_slot_bytes);
+    const MmSmem L(P.n_stage, P.n_stage_b, P.raw_slots, P.raw_slot_bytes);
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));
@@ -532,5 +781,35 @@ lmoe_status launch_mm_id(const lmoe_expert_stack *st, const __half *xh, int x_pe
     if (st->dtype == LMOE_Q4_K) mm_id_kernel<LMOE_Q4_K><<<c_sms, MM_THREADS, L.total, stream>>>(P);
     else mm_id_kernel<LMOE_Q6_K><<<c_sms, MM_THREADS, L.total, stream>>>(P);
     LMOE_LAUNCH_CHECK("mm_id_kernel");
+    return LMOE_OK;
+}
+
+// gate and up of one expert block in one kernel, SwiGLU applied: act[rows, ff] (f32).
+lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
+                             const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
+                             float *act, void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
+    if (gate->dtype != LMOE_Q4_K || up->dtype != LMOE_Q4_K)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the fused gate/up kernel is built for Q4_K stacks");
+    if (gate->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
+    const int64_t max_tiles = mm_max_tiles(list_rows, gate->n_expert, gate->n_out);
+    int32_t *tiles = static_cast<int32_t *>(tiles_ws);
+    int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)gate->n_expert, (int)gate->n_out, tiles, n_tiles, (int)max_tiles);
+    LMOE_LAUNCH_CHECK("build_tiles_kernel");
+    GuParams P;
+    P.wg = gate->blocks(); P.wu = up->blocks(); P.expert_bytes = gate->expert_bytes();
+    P.n_out = (int)gate->n_out; P.k = (int)gate->k; P.xt = static_cast<const uint8_t *>(xt);
+    P.ids_map = ids_map; P.map_stride = (int)map_stride; P.tiles = tiles; P.n_tiles = n_tiles; P.act = act; P.flag = flag;
+    const int smem = GU_NS * (GU_A_STAGE + B_STAGE_BYTES) + 256 + 1024;
+    static thread_local int c_dev = -1, c_sms = 0;
+    int dev = 0;
+    LMOE_CUDA(cudaGetDevice(&dev));
+    if (dev != c_dev) {
+        LMOE_CUDA(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
+        LMOE_CUDA(cudaFuncSetAttribute(mm_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        c_dev = dev;
+    }
+    mm_gateup_kernel<<<c_sms, GU_THREADS, smem, stream>>>(P);
+    LMOE_LAUNCH_CHECK("mm_gateup_kernel");
     return LMOE_OK;
 }

@@ -8,20 +8,28 @@
 int64_t mm_max_tiles(int64_t rows, int64_t n_expert, int64_t n_out);
 bool mm_id_kernel_available(int dtype, int64_t n_out, int64_t k);
 size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out);
-cudaError_t launch_to_half_perm(const float *x, int64_t n, __half *out, cudaStream_t s);
-lmoe_status launch_mm_id(const lmoe_expert_stack *st, const __half *xh, int x_per_row, int top_k, int64_t t,
-                         const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
-                         const float *row_scale, float *out, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
+size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k);
+cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
+                                const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
+                                cudaStream_t s);
+lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
+                             const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
+                             float *act, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
+lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
+                         int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
+                         uint32_t *flag, cudaStream_t stream);
 
 namespace {
 
 // One warp per row: act = silu(g) * u; l2 = clamp(||act||, 1e-8, 1e30); the f16 operand of the
-// down projection is act * 32768 / l2 (src/moe.rs:292-302) stored with groups of 8 permuted
-// [0 2 1 3 4 6 5 7]; scale[row] = l2 * 2^-15 * weight[row] undoes it in the down epilogue
-// together with the routing weight (src/ops/combine.metal:102-133).
+// down projection is act * 32768 / l2 (src/moe.rs:292-302), written in the grouped GEMM's tile
+// order (row tile pos>>8, row pos&255, 128-byte swizzle, groups of 8 as [0 2 1 3 4 6 5 7]);
+// scale[row] = l2 * 2^-15 * weight[row] undoes it in the down epilogue together with the
+// routing weight (src/ops/combine.metal:102-133).
 __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restrict__ g, const float *__restrict__ u,
-                                                          const float *__restrict__ w, int64_t rows, int ff,
-                                                          __half *__restrict__ act, float *__restrict__ scale) {
+                                                          const float *__restrict__ w, const int32_t *__restrict__ pos,
+                                                          int64_t rows, int ff, uint8_t *__restrict__ act,
+                                                          float *__restrict__ scale) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -42,6 +50,7 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restric
     for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float l2 = fminf(fmaxf(sqrtf(ss), 1e-8f), 1e30f);
     const float k = 32768.0f / l2;
+    const int p = pos[row];
     for (int i = lane * 8; i < ff; i += 256) {
         const float4 g0 = *reinterpret_cast<const float4 *>(gr + i), g1 = *reinterpret_cast<const float4 *>(gr + i + 4);
         const float4 u0 = *reinterpret_cast<const float4 *>(ur + i), u1 = *reinterpret_cast<const float4 *>(ur + i + 4);
@@ -52,7 +61,40 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restric
         for (int j = 0; j < 8; j++) a[j] = __fmul_rn(__fdiv_rn(gv[j], __fadd_rn(1.0f, expf(-gv[j]))), uv[j]) * k;
         __align__(16) __half2 h[4] = {__floats2half2_rn(a[0], a[2]), __floats2half2_rn(a[1], a[3]),
                                       __floats2half2_rn(a[4], a[6]), __floats2half2_rn(a[5], a[7])};
-        *reinterpret_cast<uint4 *>(act + row * ff + i) = *reinterpret_cast<const uint4 *>(h);
+        const int ci = i >> 3;
+        const size_t off = (((size_t)(p >> 8) * (ff / 64) + (ci >> 3)) * 256 + (p & 255)) * 128 +
+                           ((size_t)((ci & 7) ^ (p & 7)) << 4);
+        *reinterpret_cast<uint4 *>(act + off) = *reinterpret_cast<const uint4 *>(h);
+    }
+    if (lane == 0) scale[row] = l2 * 0x1p-15f * (w ? w[row] : 1.0f);
+}
+
+// Same range guard for an activation that is already silu(g)*u (f32): l2, rescale, f16, tile order.
+__global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restrict__ a, const float *__restrict__ w,
+                                                           const int32_t *__restrict__ pos, int64_t rows, int ff,
+                                                           uint8_t *__restrict__ act, float *__restrict__ scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float *ar = a + row * ff;
+    float ss = 0.f;
+    for (int i = lane * 8; i < ff; i += 256) {
+        const float4 a0 = *reinterpret_cast<const float4 *>(ar + i), a1 = *reinterpret_cast<const float4 *>(ar + i + 4);
+        ss += a0.x * a0.x + a0.y * a0.y + a0.z * a0.z + a0.w * a0.w + a1.x * a1.x + a1.y * a1.y + a1.z * a1.z + a1.w * a1.w;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float l2 = fminf(fmaxf(sqrtf(ss), 1e-8f), 1e30f);
+    const float k = 32768.0f / l2;
+    const int p = pos[row];
+    for (int i = lane * 8; i < ff; i += 256) {
+        const float4 a0 = *reinterpret_cast<const float4 *>(ar + i), a1 = *reinterpret_cast<const float4 *>(ar + i + 4);
+        __align__(16) __half2 h[4] = {__floats2half2_rn(a0.x * k, a0.z * k), __floats2half2_rn(a0.y * k, a0.w * k),
+                                      __floats2half2_rn(a1.x * k, a1.z * k), __floats2half2_rn(a1.y * k, a1.w * k)};
+        const int ci = i >> 3;
+        const size_t off = (((size_t)(p >> 8) * (ff / 64) + (ci >> 3)) * 256 + (p & 255)) * 128 +
+                           ((size_t)((ci & 7) ^ (p & 7)) << 4);
+        *reinterpret_cast<uint4 *>(act + off) = *reinterpret_cast<const uint4 *>(h);
     }
     if (lane == 0) scale[row] = l2 * 0x1p-15f * (w ? w[row] : 1.0f);
 }
@@ -97,31 +139,43 @@ struct Carver {
 // Scratch of one grouped SwiGLU FFN over `rows` routed rows.
 size_t ffn_bytes(int64_t rows, int64_t hidden, int64_t ff, int64_t n_expert) {
     size_t o = 0;
+    o += mm_tiled_bytes(rows, n_expert, hidden);             // x in tile order
+    o += lmoe_align_up((size_t)rows * 4, 256);               // position of every flat id
     o += 2 * lmoe_align_up((size_t)rows * ff * 4, 256);      // gate, up
-    o += lmoe_align_up((size_t)rows * ff * 2, 256);          // f16 activation
+    o += mm_tiled_bytes(rows, n_expert, ff);                 // f16 activation in tile order
     o += lmoe_align_up((size_t)rows * 4, 256);               // row scale
     const size_t t1 = mm_tiles_bytes(rows, n_expert, ff), t2 = mm_tiles_bytes(rows, n_expert, hidden);
     o += t1 > t2 ? t1 : t2;
     return o;
 }
 
-// y[rows, hidden] = row_weight * FFN_{expert of row}(x rows); lists as produced by map0.
+// y[rows, hidden] = row_weight * FFN_{expert of row}(x[row / top_k]); lists as produced by map0.
 lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const lmoe_expert_stack *down,
-                        const __half *xh, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
+                        const float *x, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
                         int64_t map_stride, const float *row_w, float *y, uint8_t *ws, uint32_t *flag,
                         cudaStream_t s) {
-    const int64_t rows = t * top_k, ff = gate->n_out, hidden = down->n_out;
+    const int64_t rows = t * top_k, ff = gate->n_out, hidden = gate->k, ne = gate->n_expert;
     Carver c{ws, 0};
+    uint8_t *xt = c.take<uint8_t>(mm_tiled_bytes(rows, ne, hidden));
+    int32_t *pos = c.take<int32_t>((size_t)rows);
     float *g = c.take<float>((size_t)rows * ff), *u = c.take<float>((size_t)rows * ff);
-    __half *act = c.take<__half>((size_t)rows * ff);
+    uint8_t *act = c.take<uint8_t>(mm_tiled_bytes(rows, ne, ff));
     float *rs = c.take<float>((size_t)rows);
     void *tiles = ws + c.off;
     lmoe_status st;
-    if ((st = launch_mm_id(gate, xh, 1, top_k, t, tpe, ids_map, map_stride, rows, nullptr, g, tiles, flag, s))) return st;
-    if ((st = launch_mm_id(up, xh, 1, top_k, t, tpe, ids_map, map_stride, rows, nullptr, u, tiles, flag, s))) return st;
-    swiglu_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, u, row_w, rows, (int)ff, act, rs);
-    LMOE_LAUNCH_CHECK("swiglu_rows_kernel");
-    if ((st = launch_mm_id(down, act, top_k, top_k, t, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s))) return st;
+    LMOE_CUDA(launch_gather_tiles(x, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos, s));
+    if (gate->dtype == LMOE_Q4_K && up->dtype == LMOE_Q4_K) {
+        // both projections in one pass over the activations, SwiGLU in the epilogue
+        if ((st = launch_mm_gateup(gate, up, xt, tpe, ids_map, map_stride, rows, g, tiles, flag, s))) return st;
+        rescale_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, row_w, pos, rows, (int)ff, act, rs);
+        LMOE_LAUNCH_CHECK("rescale_rows_kernel");
+    } else {
+        if ((st = launch_mm_id(gate, xt, tpe, ids_map, map_stride, rows, nullptr, g, tiles, flag, s))) return st;
+        if ((st = launch_mm_id(up, xt, tpe, ids_map, map_stride, rows, nullptr, u, tiles, flag, s))) return st;
+        swiglu_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, u, row_w, pos, rows, (int)ff, act, rs);
+        LMOE_LAUNCH_CHECK("swiglu_rows_kernel");
+    }
+    if ((st = launch_mm_id(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s))) return st;
     return LMOE_OK;
 }
 
@@ -140,7 +194,6 @@ size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
     o += lmoe_align_up((size_t)t * L->n_expert * 4, 256);            // logits
     o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // ids, weights
     o += lmoe_map0_scratch_bytes(L->n_expert, t);
-    o += lmoe_align_up((size_t)t * L->hidden * 2, 256);              // f16 x
     o += lmoe_align_up((size_t)rows * L->hidden * 4, 256);           // routed partial rows
     o += lmoe_align_up((size_t)t * L->hidden * 4, 256);              // shared expert rows
     o += lmoe_align_up((size_t)(t + 64) * 4, 256);                   // identity list
@@ -162,7 +215,6 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     uint32_t *ids = c.take<uint32_t>((size_t)rows);
     float *w = c.take<float>((size_t)rows);
     uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
-    __half *xh = c.take<__half>((size_t)t * H);
     float *y = c.take<float>((size_t)rows * H);
     float *ysh = c.take<float>((size_t)t * H);
     uint32_t *sh_list = c.take<uint32_t>((size_t)t + 64);
@@ -173,14 +225,13 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
     LMOE_CUDA(launch_map0(ids, (int)t, (int)L->top_k, (int)L->n_expert, tpe, ids_map, s));
-    LMOE_CUDA(launch_to_half_perm(x, t * H, xh, s));
-    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, xh, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s);
+    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s);
     if (st) return st;
     const float *shared = nullptr;
     if (L->sh_gate) {
         iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64));
         LMOE_LAUNCH_CHECK("iota_list_kernel");
-        st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, xh, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
+        st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
                          nullptr, ysh, ffn_ws, flag, s);
         if (st) return st;
         shared = ysh;
@@ -200,7 +251,7 @@ extern "C" int32_t lmoe_mm_id_supported(int32_t dtype, int64_t top_k) {
 
 extern "C" size_t lmoe_mm_id_workspace_bytes(const lmoe_expert_stack *stack, int64_t t, int64_t top_k, int64_t x_per_row) {
     if (!stack || t < 0 || top_k < 1 || x_per_row < 1) return 0;
-    return 256 + lmoe_align_up((size_t)t * x_per_row * stack->k * 2, 256) +
+    return 256 + mm_tiled_bytes(t * top_k, stack->n_expert, stack->k) +
            mm_tiles_bytes(t * top_k, stack->n_expert, stack->n_out);
 }
 
@@ -218,13 +269,14 @@ static lmoe_status mm_id_run(const lmoe_expert_stack *stack, const float *x, int
     if (t == 0) return LMOE_OK;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     uint32_t *flag = reinterpret_cast<uint32_t *>(ws);
-    __half *xh = reinterpret_cast<__half *>(ws + 256);
-    void *tiles = ws + 256 + lmoe_align_up((size_t)t * x_per_row * k * 2, 256);
+    uint8_t *xt = ws + 256;
+    void *tiles = ws + 256 + mm_tiled_bytes(t * top_k, stack->n_expert, k);
     LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
-    LMOE_CUDA(launch_to_half_perm(x, t * x_per_row * k, xh, s));
     const uint32_t *tpe = static_cast<const uint32_t *>(map0);
     const int32_t *ids_map = reinterpret_cast<const int32_t *>(static_cast<const uint8_t *>(map0) + stack->n_expert * 4);
-    return launch_mm_id(stack, xh, (int)x_per_row, (int)top_k, t, tpe, ids_map, t, t * top_k, nullptr, out, tiles, flag, s);
+    LMOE_CUDA(launch_gather_tiles(x, (int)x_per_row, (int)top_k, (int)k, tpe, ids_map, (int)t, (int)stack->n_expert, xt,
+                                  nullptr, s));
+    return launch_mm_id(stack, xt, tpe, ids_map, t, t * top_k, nullptr, out, tiles, flag, s);
 }
 
 extern "C" lmoe_status lmoe_mul_mm_id_shared(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
@@ -264,7 +316,7 @@ extern "C" lmoe_status lmoe_mul_mm_id(const lmoe_expert_stack *stack, const floa
 
 // ---- expert-parallel pieces -------------------------------------------------------------
 static size_t rows_ws_bytes(const lmoe_layer *L, int64_t rows) {
-    return 65536 + lmoe_map0_scratch_bytes(L->n_expert, rows) + lmoe_align_up((size_t)rows * L->hidden * 2, 256) +
+    return 65536 + lmoe_map0_scratch_bytes(L->n_expert, rows) + lmoe_align_up((size_t)(rows + 64) * 4, 256) +
            ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
 }
 
@@ -282,13 +334,11 @@ extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *L, const floa
     Carver c{static_cast<uint8_t *>(workspace), 65536};
     uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
     uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, rows));
-    __half *xh = c.take<__half>((size_t)rows * L->hidden);
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
     LMOE_CUDA(launch_map0(local_ids, (int)rows, 1, (int)L->n_expert, tpe, ids_map, s));
-    LMOE_CUDA(launch_to_half_perm(x, rows * L->hidden, xh, s));
-    return ffn_grouped(L->gate, L->up, L->down, xh, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s);
+    return ffn_grouped(L->gate, L->up, L->down, x, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s);
 }
 
 extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, int64_t t, float *out, void *workspace,
@@ -305,12 +355,10 @@ extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, 
     Carver c{static_cast<uint8_t *>(workspace), 65536};
     uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
     uint32_t *list = c.take<uint32_t>((size_t)t + 64);
-    __half *xh = c.take<__half>((size_t)t * L->hidden);
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
     iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, list, reinterpret_cast<int32_t *>(list + 64));
     LMOE_LAUNCH_CHECK("iota_list_kernel");
-    LMOE_CUDA(launch_to_half_perm(x, t * L->hidden, xh, s));
-    return ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, xh, 1, t, list, reinterpret_cast<int32_t *>(list + 64), t, nullptr,
+    return ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, list, reinterpret_cast<int32_t *>(list + 64), t, nullptr,
                        out, ffn_ws, flag, s);
 }
 

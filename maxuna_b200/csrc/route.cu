@@ -75,6 +75,43 @@ route_logits_kernel(const float *__restrict__ router, const float *__restrict__ 
     }
 }
 
+// Prefill-sized variant for hidden = 128*HB: a block stages TTB tokens in shared memory; each of
+// its 8 warps walks experts warp, warp+8, ... with the router row in registers (all of its loads
+// in flight together) and runs the same per-lane fmaf chains, so the logits are bit-identical.
+template <int HB, int TTB>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_logits_tiled_kernel(const float *__restrict__ router, const float *__restrict__ x, int t, int n_expert,
+                          float *__restrict__ logits) {
+    extern __shared__ float xs[];
+    constexpr int H = 128 * HB;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * TTB;
+    const int nt = min(TTB, t - t0);
+    for (int i = threadIdx.x; i < nt * (H / 4); i += ROUTE_WARPS * 32)
+        reinterpret_cast<float4 *>(xs)[i] = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t0 * H) + i);
+    __syncthreads();
+    for (int e = warp; e < n_expert; e += ROUTE_WARPS) {
+        float4 wv[HB];
+        const float4 *wr = reinterpret_cast<const float4 *>(router + (size_t)e * H) + lane;
+#pragma unroll
+        for (int j = 0; j < HB; j++) wv[j] = __ldg(wr + 32 * j);
+        for (int i = 0; i < nt; i++) {
+            const float4 *xr = reinterpret_cast<const float4 *>(xs + i * H) + lane;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int j = 0; j < HB; j++) {
+                const float4 xv = xr[32 * j];
+                a0 = __fmaf_rn(xv.x, wv[j].x, a0);
+                a1 = __fmaf_rn(xv.y, wv[j].y, a1);
+                a2 = __fmaf_rn(xv.z, wv[j].z, a2);
+                a3 = __fmaf_rn(xv.w, wv[j].w, a3);
+            }
+            const float v = lmoe_router_fold(a0, a1, a2, a3);
+            if (lane == 0) logits[(size_t)(t0 + i) * n_expert + e] = v;
+        }
+    }
+}
+
 // One warp per token; scores staged in shared memory (2 * n_expert floats per warp).
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_select_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int t, int n_expert,
@@ -105,6 +142,15 @@ cudaError_t launch_route_logits(const float *router, const float *x, int t, int 
         route_logits_kernel<1><<<dim3(gx, t), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
     } else if (t <= 64) {
         route_logits_kernel<4><<<dim3(gx, (t + 3) / 4), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
+    } else if (hidden == 128 * 24) {
+        constexpr int TTB = 8;
+        const size_t smem = (size_t)TTB * hidden * sizeof(float);
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(route_logits_tiled_kernel<24, TTB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr_set = true;
+        }
+        route_logits_tiled_kernel<24, TTB><<<(t + TTB - 1) / TTB, ROUTE_WARPS * 32, smem, s>>>(router, x, t, n_expert, logits);
     } else {
         route_logits_kernel<8><<<dim3(gx, (t + 7) / 8), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
     }
