@@ -194,9 +194,9 @@ __device__ __forceinline__ void dequant_q6k_row32(const uint8_t *blk, int js, in
 // CTAs running side by side share the same activation rows in L2.
 __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__restrict__ tpe, int n_expert, int n_out,
                                                           int32_t *__restrict__ tiles, int32_t *__restrict__ n_tiles,
-                                                          int max_tiles) {
+                                                          int max_tiles, int m_step) {
     __shared__ int pre[513];
-    const int m_tiles = (n_out + MM_M - 1) / MM_M;
+    const int m_tiles = (n_out + m_step - 1) / m_step;
     const int e = threadIdx.x;
     const int cnt = e < n_expert ? (int)((tpe[e] + MM_N - 1) / MM_N) * m_tiles : 0;
     pre[e + 1] = cnt;
@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__rest
                 tiles[8 * o + 0] = e;
                 tiles[8 * o + 1] = n0;
                 tiles[8 * o + 2] = min(MM_N, rows - n0);
-                tiles[8 * o + 3] = m * MM_M;
+                tiles[8 * o + 3] = m * m_step;
                 tiles[8 * o + 4] = pre[e] / m_tiles + n0 / MM_N;
             }
     }
@@ -500,6 +500,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
 }
 
 
+#ifdef MM_DBG_STAMP
+#define GSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
+#else
+#define GSTAMP(role, g, i) do { } while (0)
+#endif
+
 // ================= gate + up in one pass, SwiGLU in the epilogue =========================
 // Same tile list as above, but a CTA multiplies one block of routed rows by 128 gate rows AND the
 // matching 128 up rows (two accumulators of 256 TMEM columns), so every activation stage is
@@ -592,35 +598,41 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
             const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
             const bool rvalid = m0 + r < P.n_out;
             const uint8_t *row = wbase + (size_t)e * P.expert_bytes + (size_t)(rvalid ? m0 + r : m0) * row_bytes;
-            // two stages of quantized bytes and one header ahead, in registers
-            uint4 qa0 = __ldg(reinterpret_cast<const uint4 *>(row + 16)), qb0 = __ldg(reinterpret_cast<const uint4 *>(row + 32));
-            uint4 qa1 = __ldg(reinterpret_cast<const uint4 *>(row + 48)), qb1 = __ldg(reinterpret_cast<const uint4 *>(row + 64));
-            uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(row)), hdr_n = hdr;
-            for (int ks = 0; ks < k_stages && ok; ks += 2) {
+            // a whole super-block (144 B) ahead in registers: while block b is dequantised, block b+1 loads
+            const int n_blk = P.k / QK_K;
+            uint4 ra[9], rb[9];
 #pragma unroll
-                for (int h = 0; h < 2; h++, g++) {
-                    const int kk = ks + h, s = g % GU_NS;
-                    if ((kk & 3) == 0 && kk + 4 < k_stages)
-                        hdr_n = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)((kk >> 2) + 1) * Q4K_BYTES));
-                    ok = ok && mb_wait(&a_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
-                    uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
-                    if (rvalid) {
-                        dequant_q4k_regs(hdr, h ? qa1 : qa0, h ? qb1 : qb0, kk & 3, ast, r);
-                    } else {
+            for (int i = 0; i < 9; i++) ra[i] = __ldg(reinterpret_cast<const uint4 *>(row) + i);
+            for (int b = 0; b < n_blk && ok; b += 2) {
 #pragma unroll
-                        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                for (int h = 0; h < 2; h++) {
+                    if (b + h >= n_blk) break;
+                    if (b + h + 1 < n_blk) {
+                        const uint4 *nx = reinterpret_cast<const uint4 *>(row + (size_t)(b + h + 1) * Q4K_BYTES);
+                        if (b + h + 2 < n_blk) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 9));
+#pragma unroll
+                        for (int i = 0; i < 9; i++) (h ? ra : rb)[i] = __ldg(nx + i);
                     }
-                    // refill this register pair with the stage two ahead
-                    const int kn = kk + 2;
-                    if (kn < k_stages) {
-                        const uint8_t *p = row + (size_t)(kn >> 2) * Q4K_BYTES + 16 + 32 * (kn & 3);
-                        if (h) { qa1 = __ldg(reinterpret_cast<const uint4 *>(p)); qb1 = __ldg(reinterpret_cast<const uint4 *>(p + 16)); }
-                        else { qa0 = __ldg(reinterpret_cast<const uint4 *>(p)); qb0 = __ldg(reinterpret_cast<const uint4 *>(p + 16)); }
+#pragma unroll
+                    for (int j = 0; j < 4; j++, g++) {
+                        const int s = g % GU_NS;
+                        if (tid == 0) GSTAMP(0, g, 0);
+                        ok = ok && mb_wait(&a_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
+                        if (tid == 0) GSTAMP(0, g, 1);
+                        uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
+                        if (rvalid) {
+                            const uint4 *cur = h ? rb : ra;
+                            dequant_q4k_regs(cur[0], cur[1 + 2 * j], cur[2 + 2 * j], j, ast, r);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        if (tid == 0) GSTAMP(0, g, 2);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mb_arrive(&a_full[s]);
+                        if (tid == 0) GSTAMP(0, g, 3);
                     }
-                    if ((kk & 3) == 3) hdr = hdr_n;
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mb_arrive(&a_full[s]);
                 }
             }
         }
@@ -653,7 +665,11 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % GU_NS;
-                    ok = mb_wait(&a_full[s], (g / GU_NS) & 1, P.flag, 6) && mb_wait(&b_full[s], (g / GU_NS) & 1, P.flag, 7);
+                    GSTAMP(1, g, 0);
+                    ok = mb_wait(&a_full[s], (g / GU_NS) & 1, P.flag, 6);
+                    GSTAMP(1, g, 1);
+                    ok = ok && mb_wait(&b_full[s], (g / GU_NS) & 1, P.flag, 7);
+                    GSTAMP(1, g, 2);
                     tc_fence_after();
                     const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
                     const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
@@ -665,6 +681,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                     }
                     tc_commit(&a_empty[s]);
                     tc_commit(&b_empty[s]);
+                    GSTAMP(1, g, 3);
                 }
                 tc_commit(acc_full);
             }
@@ -694,6 +711,256 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                     const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
                     const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                     if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mb_arrive(acc_empty);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+}
+
+
+// ================= down projection (Q6_K), 256 weight rows per CTA ===========================
+// Two 128-row sub-tiles of the same stack share every activation stage (two accumulators of
+// 256 TMEM columns).  The quantized rows are read straight from global memory, coalesced:
+// eight consecutive lanes own one (row, 128-weight half of a super-block) and read its ql / qh
+// words side by side; each lane turns its 4 l-positions of the four 32-weight groups into
+// f16 and writes 8-byte pieces of the swizzled A stages of TWO consecutive k-stages.
+//   warps 0-7 dequant    warp 8 B loader    warp 9 MMA issuer    warps 10-13 epilogue
+constexpr int DN_THREADS = 14 * 32;
+constexpr int DN_NSA = 4, DN_NSB = 2;
+
+struct DnParams {
+    const uint8_t *w; // down stack (Q6_K)
+    int64_t expert_bytes;
+    int n_out, k;
+    const uint8_t *xt;
+    const int32_t *ids_map;
+    int map_stride;
+    const int32_t *tiles, *n_tiles;
+    const float *row_scale;
+    float *out; // [rows, n_out]
+    uint32_t *flag;
+};
+
+// aligned-or-not 32-bit load from a 2-byte aligned global address (uniform branch per super-block)
+template <bool MIS>
+__device__ __forceinline__ uint32_t ldg32_a2(const uint8_t *p) {
+    if (MIS) {
+        const uint32_t lo = __ldg(reinterpret_cast<const uint32_t *>(p - 2)), hi = __ldg(reinterpret_cast<const uint32_t *>(p + 2));
+        return __byte_perm(lo, hi, 0x5432);
+    }
+    return __ldg(reinterpret_cast<const uint32_t *>(p));
+}
+
+struct DnRegs {
+    uint32_t qa[8], qb[8], qh[8], sx[8];
+};
+
+// loads of one (super-block b, half n) for this thread's eight rows
+template <bool MIS>
+__device__ __forceinline__ void dn_load(DnRegs &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int n, int w,
+                                        int row0) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = row0 + 32 * i;
+        if (row < rows_valid) {
+            const uint8_t *blk = tile_w + (size_t)row * row_bytes + (size_t)b * Q6K_BYTES;
+            R.qa[i] = ldg32_a2<MIS>(blk + 64 * n + 4 * w);
+            R.qb[i] = ldg32_a2<MIS>(blk + 64 * n + 32 + 4 * w);
+            R.qh[i] = ldg32_a2<MIS>(blk + 128 + 32 * n + 4 * w);
+            // lanes 0,1 of the group fetch the half's eight scales, lane 2 the block scale d
+            R.sx[i] = w < 2 ? ldg32_a2<MIS>(blk + 192 + 8 * n + 4 * w)
+                            : (w == 2 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t *>(blk + 208)) : 0u);
+        } else {
+            R.qa[i] = R.qb[i] = R.qh[i] = R.sx[i] = 0u;
+        }
+    }
+}
+
+// 16 weights per row (4 l-positions x 4 groups) -> two k-stages of the A tile
+__device__ __forceinline__ void dn_dequant(const DnRegs &R, uint8_t *st_even, uint8_t *st_odd, int w, int row0, int lane) {
+    const int gb = lane & ~7;
+    const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = row0 + 32 * i;
+        const uint32_t scw0 = __shfl_sync(0xffffffffu, R.sx[i], gb), scw1 = __shfl_sync(0xffffffffu, R.sx[i], gb + 1);
+        const float d = lmoe_h2f((uint16_t)__shfl_sync(0xffffffffu, R.sx[i], gb + 2));
+        const uint32_t qa = R.qa[i], qb = R.qb[i], hh = R.qh[i];
+        uint8_t *base_e = st_even + (row >> 7) * A_STAGE_BYTES, *base_o = st_odd + (row >> 7) * A_STAGE_BYTES;
+        const int r = row & 127;
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+            const uint32_t scw = (gi & 2) ? scw1 : scw0;
+            // scale index inside the word: 2*(gi&1) + (l / 16), l / 16 = w >> 2
+            const int sb = (int)(int8_t)((scw >> (8 * (2 * (gi & 1) + (w >> 2)))) & 0xff);
+            const bool hi_nib = gi & 2;
+            const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
+            const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u;
+            const __half2 s = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
+            const uint32_t q = (gi & 1) ? qb : qa;
+            const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
+            const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
+            const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
+            const uint2 o = make_uint2(h2_sub_fma(v02, off, s, zero), h2_sub_fma(v13, off, s, zero));
+            uint8_t *dst = (hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + (w >> 1)) + 8 * (w & 1);
+            *reinterpret_cast<uint2 *>(dst) = o;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_constant__ DnParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_st = smem, *b_st = smem + DN_NSA * GU_A_STAGE;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(b_st + DN_NSB * B_STAGE_BYTES);
+    uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 10, *acc_full = bars + 12, *acc_empty = bars + 13;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = *P.n_tiles;
+    const int k_stages = P.k / MM_K, n_blk = P.k / QK_K;
+    const int row_bytes = n_blk * Q6K_BYTES;
+
+    if (tid == 0) {
+        for (int s = 0; s < DN_NSA; s++) {
+            mb_init(&a_full[s], 8);
+            mb_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < DN_NSB; s++) {
+            mb_init(&b_full[s], 1);
+            mb_init(&b_empty[s], 1);
+        }
+        mb_init(acc_full, 1);
+        mb_init(acc_empty, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // ---------------- dequant ----------------
+        const int w = tid & 7, row0 = tid >> 3; // this thread: l = 4w..4w+3 of rows row0, row0+32, ...
+        uint32_t g = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
+            const int rows_valid = min(2 * MM_M, P.n_out - m0);
+            const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
+            const bool mis0 = (reinterpret_cast<uintptr_t>(tw) & 2) != 0; // parity of even blocks (row_bytes % 4 == 0 when n_blk is even)
+            DnRegs RA, RB;
+            if (mis0) dn_load<true>(RA, tw, row_bytes, rows_valid, 0, 0, w, row0);
+            else dn_load<false>(RA, tw, row_bytes, rows_valid, 0, 0, w, row0);
+            for (int b = 0; b < n_blk && ok; b++) {
+                const bool mis = mis0 != ((b & 1) != 0);
+#pragma unroll
+                for (int n = 0; n < 2; n++, g += 2) {
+                    // prefetch the next half while this one is converted
+                    DnRegs &cur = n ? RB : RA;
+                    DnRegs &nxt = n ? RA : RB;
+                    const int nb = n ? b + 1 : b, nn = n ? 0 : 1;
+                    if (nb < n_blk) {
+                        const bool nmis = mis0 != ((nb & 1) != 0);
+                        if (nmis) dn_load<true>(nxt, tw, row_bytes, rows_valid, nb, nn, w, row0);
+                        else dn_load<false>(nxt, tw, row_bytes, rows_valid, nb, nn, w, row0);
+                    }
+                    const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
+                    ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3) &&
+                         mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
+                    dn_dequant(cur, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, w, row0, lane);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mb_arrive(&a_full[s0]);
+                        mb_arrive(&a_full[s1]);
+                    }
+                }
+                (void)mis;
+            }
+        }
+    } else if (warp == 8) {
+        // ---------------- B loader ----------------
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
+                const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % DN_NSB;
+                    ok = mb_wait(&b_empty[s], ((g / DN_NSB) & 1) ^ 1, P.flag, 4);
+                    mb_expect_tx(&b_full[s], (uint32_t)nv * 128u);
+                    bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &b_full[s]);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+                const int nv = P.tiles[8 * tile + 2];
+                const int npad = (nv + 15) & ~15;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
+                ok = mb_wait(acc_empty, (it & 1) ^ 1, P.flag, 5);
+                tc_fence_after();
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    const int s = g % DN_NSA, sb = g % DN_NSB;
+                    ok = mb_wait(&a_full[s], (g / DN_NSA) & 1, P.flag, 6) && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
+                    tc_fence_after();
+                    const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
+                    const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
+                    const uint64_t bd = umma_desc(s32(b_st + (size_t)sb * B_STAGE_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < MM_K / 16; kk++) {
+                        tc_mma_f16(tmem_base, ad0 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16(tmem_base + 256, ad1 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&a_empty[s]);
+                    tc_commit(&b_empty[sb]);
+                }
+                tc_commit(acc_full);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: scaled rows ----------------
+        const int q = warp & 3;
+        const int m = 32 * q + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+            const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
+            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            ok = mb_wait(acc_full, it & 1, P.flag, 8);
+            tc_fence_after();
+            for (int sub = 0; sub < 2; sub++) {
+                const int mrow = m0 + sub * MM_M + m;
+                const bool mvalid = mrow < P.n_out;
+                for (int cb = 0; cb < nv; cb += 32) {
+                    uint32_t v[32];
+                    tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + sub * 256 + cb, v);
+                    const int my = cb + lane;
+                    const int myfid = my < nv ? list[my] : 0;
+                    const float mysc = (P.row_scale && my < nv) ? P.row_scale[myfid] : 1.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                        const float sc = __shfl_sync(0xffffffffu, mysc, j);
+                        if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + mrow] = __uint_as_float(v[j]) * sc;
+                    }
                 }
             }
             tc_fence_before();
@@ -745,7 +1012,9 @@ size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k) {
 cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
                                 const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
                                 cudaStream_t s) {
-    gather_tiles_kernel<<<dim3(n_expert, 16), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
+    // enough blocks per expert to cover the device even when one expert holds all the rows
+    const int gy = n_expert >= 64 ? 16 : (n_expert >= 8 ? 128 : 1024);
+    gather_tiles_kernel<<<dim3(n_expert, gy), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
                                                            static_cast<uint8_t *>(xt), pos);
     return cudaGetLastError();
 }
@@ -761,7 +1030,7 @@ lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint
     const int64_t max_tiles = mm_max_tiles(list_rows, st->n_expert, st->n_out);
     int32_t *tiles = static_cast<int32_t *>(tiles_ws);
     int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
-    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)st->n_expert, (int)st->n_out, tiles, n_tiles, (int)max_tiles);
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)st->n_expert, (int)st->n_out, tiles, n_tiles, (int)max_tiles, MM_M);
     LMOE_LAUNCH_CHECK("build_tiles_kernel");
     P.w = st->blocks(); P.expert_bytes = st->expert_bytes();
     P.dtype = st->dtype; P.n_expert = (int)st->n_expert; P.n_out = (int)st->n_out; P.k = (int)st->k;
@@ -794,7 +1063,7 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     const int64_t max_tiles = mm_max_tiles(list_rows, gate->n_expert, gate->n_out);
     int32_t *tiles = static_cast<int32_t *>(tiles_ws);
     int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
-    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)gate->n_expert, (int)gate->n_out, tiles, n_tiles, (int)max_tiles);
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)gate->n_expert, (int)gate->n_out, tiles, n_tiles, (int)max_tiles, MM_M);
     LMOE_LAUNCH_CHECK("build_tiles_kernel");
     GuParams P;
     P.wg = gate->blocks(); P.wu = up->blocks(); P.expert_bytes = gate->expert_bytes();
@@ -811,5 +1080,35 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     }
     mm_gateup_kernel<<<c_sms, GU_THREADS, smem, stream>>>(P);
     LMOE_LAUNCH_CHECK("mm_gateup_kernel");
+    return LMOE_OK;
+}
+
+// The down projection: 256 Q6_K weight rows per CTA, optional per-row scale in the epilogue.
+lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
+                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
+                           uint32_t *flag, cudaStream_t stream) {
+    if (down->dtype != LMOE_Q6_K || (down->k / QK_K) % 2 != 0 || (down->n_out & 1))
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the 256-row down kernel needs a Q6_K stack with k %% 512 == 0 and even n_out");
+    if (down->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
+    const int64_t max_tiles = mm_max_tiles(list_rows, down->n_expert, down->n_out);
+    int32_t *tiles = static_cast<int32_t *>(tiles_ws);
+    int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)down->n_expert, (int)down->n_out, tiles, n_tiles, (int)max_tiles, 2 * MM_M);
+    LMOE_LAUNCH_CHECK("build_tiles_kernel");
+    DnParams P;
+    P.w = down->blocks(); P.expert_bytes = down->expert_bytes(); P.n_out = (int)down->n_out; P.k = (int)down->k;
+    P.xt = static_cast<const uint8_t *>(xt); P.ids_map = ids_map; P.map_stride = (int)map_stride;
+    P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.flag = flag;
+    const int smem = DN_NSA * GU_A_STAGE + DN_NSB * B_STAGE_BYTES + 256 + 1024;
+    static thread_local int c_dev = -1, c_sms = 0;
+    int dev = 0;
+    LMOE_CUDA(cudaGetDevice(&dev));
+    if (dev != c_dev) {
+        LMOE_CUDA(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
+        LMOE_CUDA(cudaFuncSetAttribute(mm_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        c_dev = dev;
+    }
+    mm_down_kernel<<<c_sms, DN_THREADS, smem, stream>>>(P);
+    LMOE_LAUNCH_CHECK("mm_down_kernel");
     return LMOE_OK;
 }

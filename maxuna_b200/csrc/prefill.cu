@@ -15,6 +15,9 @@ cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k,
 lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
                              const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
                              float *act, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
+lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
+                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
+                           uint32_t *flag, cudaStream_t stream);
 lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
                          int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
                          uint32_t *flag, cudaStream_t stream);
@@ -175,8 +178,11 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
         swiglu_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, u, row_w, pos, rows, (int)ff, act, rs);
         LMOE_LAUNCH_CHECK("swiglu_rows_kernel");
     }
-    if ((st = launch_mm_id(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s))) return st;
-    return LMOE_OK;
+    if (down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0)
+        st = launch_mm_down(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s);
+    else
+        st = launch_mm_id(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s);
+    return st;
 }
 
 bool layer_mm_ok(const lmoe_layer *L) {

@@ -110,6 +110,17 @@ def test_prefill_block_tiny(orc, dev):
     assert orc.rel_l2(got, want) < 2e-3
 
 
+def test_prefill_block_wide_ff(orc, dev):
+    # expert_ff = 512: two Q6_K super-blocks per down row (the 256-row down kernel), ragged row tiles
+    from maxuna_b200.moe import MoeBlock
+
+    blk = MoeBlock.random(256, 512, 6, 2, seed=31, device=dev, weight_std=0.25)
+    host = blk.host_layer(orc)
+    rng = np.random.default_rng(32)
+    for t in (40, 700):
+        _check_block(orc, blk, host, rng.standard_normal((t, 256)).astype(np.float32), 2e-3)
+
+
 def test_prefill_block_production_shape(orc, dev):
     from maxuna_b200.moe import MoeBlock
 
