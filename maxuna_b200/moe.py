@@ -196,6 +196,44 @@ class MoeBlock:
                                           ws.data_ptr(), ws.numel(), stream_ptr()))
         return out_host
 
+    # ---- expert-parallel pieces (rows already dispatched to this GPU) -------------------
+    def _rows_ws(self, rows: int) -> torch.Tensor:
+        n = lib().lmoe_rows_workspace_bytes(self._h, rows)
+        if getattr(self, "_rws", None) is None or self._rws.numel() < n:
+            self._rws = torch.zeros(n, dtype=torch.uint8, device=self.router.device)
+        return self._rws
+
+    def experts_forward_rows(self, x: torch.Tensor, local_ids: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
+        """`lmoe_experts_forward_rows`: y[r] = row_w[r] * FFN_{local_ids[r]}(x[r])."""
+        x = x.to(torch.float32).contiguous()
+        rows = x.shape[0]
+        out = torch.empty(rows, self.hidden, dtype=torch.float32, device=x.device)
+        ws = self._rows_ws(rows)
+        check(lib().lmoe_experts_forward_rows(self._h, x.data_ptr(), local_ids.contiguous().data_ptr(),
+                                              row_w.contiguous().data_ptr(), rows, out.data_ptr(), ws.data_ptr(),
+                                              ws.numel(), stream_ptr()))
+        return out
+
+    def shared_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """`lmoe_shared_forward`: the shared expert alone."""
+        x = x.to(torch.float32).contiguous()
+        out = torch.empty(x.shape[0], self.hidden, dtype=torch.float32, device=x.device)
+        ws = self._rows_ws(x.shape[0])
+        check(lib().lmoe_shared_forward(self._h, x.data_ptr(), x.shape[0], out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                        stream_ptr()))
+        return out
+
+    def shard(self, rank: int, world: int) -> "MoeBlock":
+        """Zero-copy expert-parallel shard: experts [rank*E/world, (rank+1)*E/world), shared expert kept."""
+        e = self.experts
+        n = self.n_expert // world
+        sh = self.shared
+        return MoeBlock(self.router[rank * n:(rank + 1) * n], None, e.gate.slice_experts(rank * n, n),
+                        e.up.slice_experts(rank * n, n), e.down.slice_experts(rank * n, n),
+                        None if sh is None else sh.gate, None if sh is None else sh.up,
+                        None if sh is None else sh.down, min(self.n_expert_used, n), self.weights_scale,
+                        self.weights_norm)
+
     def check_device_flag(self):
         check(lib().lmoe_check_device_flag(self.workspace(1).data_ptr(), stream_ptr()))
 
