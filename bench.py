@@ -164,6 +164,65 @@ def run_reference(args, rank, world):
     }))
 
 
+def zipf_bias(n_expert, seed, device):
+    """Selection bias that skews per-expert token counts: Zipf(s=1.1) over a seeded shuffle."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_expert, generator=g)
+    z = 1.0 / (torch.arange(1, n_expert + 1, dtype=torch.float32) ** 1.1)
+    b = torch.empty(n_expert)
+    b[perm] = (z / z.max()) * 0.3 - 0.1
+    return b.to(device)
+
+
+def measure_prefill(dev, rank, world, steps=8, warmup=3):
+    """Prefill of one MoE layer: N=1 -> config 3 (4096 tokens, Zipf-skewed routing, one GPU);
+    N>1 -> config 4 (16384 tokens split over the ranks, experts sharded 256/N per GPU,
+    NCCL all-to-all dispatch / combine), uniform and Zipf.  Returns TFLOP/s figures."""
+    import torch
+    import torch.distributed as dist
+
+    from maxuna_b200.ep import make_gpu_ep_block
+    from maxuna_b200.moe import MoeBlock
+
+    res = {}
+    t_total = 4096 if world == 1 else 16384
+    for name in (("zipf",) if world == 1 else ("uniform", "zipf")):
+        bias = zipf_bias(E, 3, dev) if name == "zipf" else None
+        blk = MoeBlock.random(H, F, E, K, seed=4242, device=dev, bias=bias)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(99 + rank)
+        t_loc = t_total // world
+        x = torch.randn(t_loc, H, generator=gen, device=dev)
+        if world == 1:
+            run = lambda: blk.forward(x)
+        else:
+            ep = make_gpu_ep_block(blk.router, blk.exp_probs_b, blk.shard(rank, world), E, K)
+            run = lambda: ep.forward(x)
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt[0])
+        flops = t_total * (K + 1) * 18874368
+        res[name] = {"tokens": t_total, "ms": ms, "tflops": flops / ms / 1e9, "tok_per_s": t_total / ms * 1e3}
+        del blk
+        torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -172,6 +231,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--layers", type=int, default=8, help="layer copies rotated through (working set >> L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (grouped GEMM) measurement")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -329,6 +389,12 @@ def main():
         cpu = {"value": tok / sec, "unit": "tok/s", "cores": orc.num_threads(), "kind": "port",
                "sample": f"{tok} tokens of the decode sweep on layer 0 (int8-activation k-quant dots, OpenMP)"}
 
+    prefill = None
+    if not args.no_prefill:
+        del layers, ws
+        torch.cuda.empty_cache()
+        prefill = measure_prefill(dev, rank, world)
+
     if rank == 0:
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
@@ -353,6 +419,16 @@ def main():
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if prefill is not None:
+            peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"bf16_tflops": 1590.0}
+            line["prefill"] = {
+                "workload": ("config3: 4096-token prefill of one layer, Zipf-skewed routing, 1 GPU" if world == 1 else
+                             f"config4: 16384-token expert-parallel prefill over {world} GPUs (256/{world} experts per GPU, "
+                             "NCCL all-to-all dispatch and combine)"),
+                "unit": "TFLOP/s", "flops_per_token": (K + 1) * 18874368,
+                "peak_tflops": peaks.get("bf16_tflops"), "results": prefill,
+                "frac_of_peak": {k: v["tflops"] / (peaks.get("bf16_tflops") * world) for k, v in prefill.items()},
+            }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
