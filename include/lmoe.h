@@ -111,6 +111,21 @@ size_t lmoe_route_workspace_bytes(int64_t t, int64_t n_expert);
 lmoe_status lmoe_route(const float *router, const float *bias, const float *x, int64_t t, int64_t hidden,
                        int64_t n_expert, int64_t top_k, float scale, int32_t norm, uint32_t *ids_out,
                        float *weights_out, void *workspace, size_t workspace_bytes, void *stream);
+/* `lmoe_route` for callers that cannot allocate device memory when they route (a host engine
+ * whose pool owns the device, a loop under a fixed memory budget, code inside a stream
+ * capture): same arguments and results, but the logits scratch is a fixed array inside the
+ * library instead of a workspace.  It has no counterpart in the reference.
+ *   - limit: t * n_expert <= 32768 (128 KB of scratch held by every GPU that loads the
+ *     library, until exit); larger requests are rejected with LMOE_ERR_INVALID;
+ *   - the first call on each device looks up the array's device address: make that call once
+ *     before starting any stream capture;
+ *   - all calls share the one array (it keeps the previous call's logits; nothing needs
+ *     clearing because each call overwrites what it reads): calls that overlap on the GPU,
+ *     e.g. on two streams, race.
+ * No cudaMalloc / cudaFree or allocating library routine is called. */
+lmoe_status lmoe_route_noalloc(const float *router, const float *bias, const float *x, int64_t t, int64_t hidden,
+                               int64_t n_expert, int64_t top_k, float scale, int32_t norm, uint32_t *ids_out,
+                               float *weights_out, void *stream);
 /* `route_from_logits` alone, src/moe.rs:94-119 (logits [t, n_expert] f32). */
 lmoe_status lmoe_route_from_logits(const float *logits, const float *bias, int64_t t, int64_t n_expert,
                                    int64_t top_k, float scale, int32_t norm, uint32_t *ids_out,

@@ -28,6 +28,7 @@ PROTOTYPES = {
     "lmoe_dequantize": (c_i32, [c_i32, c_vp, c_i64, c_vp, c_vp]),
     "lmoe_route_workspace_bytes": (c_sz, [c_i64, c_i64]),
     "lmoe_route": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_f32, c_i32, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_route_noalloc": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_f32, c_i32, c_vp, c_vp, c_vp]),
     "lmoe_route_from_logits": (c_i32, [c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_i32, c_vp, c_vp, c_vp]),
     "lmoe_mul_mv_id": (c_i32, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_i64, c_i64, c_vp, c_vp]),
     "lmoe_mul_mv": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_vp, c_i64, c_vp, c_vp]),

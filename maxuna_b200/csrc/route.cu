@@ -166,3 +166,47 @@ cudaError_t launch_route_select(const float *logits, const float *bias, int t, i
                                                              weights);
     return cudaGetLastError();
 }
+
+// ---- routing without any allocation -------------------------------------------------------
+// Some hosts of this library may not allocate device memory at the moment they route: an engine
+// whose buffer pool owns the whole device and hands nothing to plugins, a serving loop running
+// under a frozen memory budget, or code that is between cudaStreamBeginCapture and EndCapture.
+// For them the logits scratch of `lmoe_route` lives in this fixed array instead of a caller
+// workspace.  Every GPU that loads the library carries the array until the process exits.
+#define LMOE_ROUTE_NOALLOC_MAX_LOGITS (64 * 512) /* t * n_expert floats, 128 KB */
+static __device__ __align__(256) float g_route_noalloc_logits[LMOE_ROUTE_NOALLOC_MAX_LOGITS];
+
+extern "C" lmoe_status lmoe_route_noalloc(const float *router, const float *bias, const float *x, int64_t t,
+                                          int64_t hidden, int64_t n_expert, int64_t top_k, float scale, int32_t norm,
+                                          uint32_t *ids_out, float *weights_out, void *stream) {
+    lmoe_clear_error();
+    if (t < 0 || n_expert < 1 || n_expert > 512 || top_k < 1 || top_k > 32 || top_k > n_expert)
+        return lmoe_fail(LMOE_ERR_INVALID, "route_noalloc: t >= 0, n_expert in [1, 512], top_k in [1, min(32, n_expert)] required");
+    if (hidden < 1 || hidden > (1 << 20)) return lmoe_fail(LMOE_ERR_INVALID, "hidden (%lld) out of range", (long long)hidden);
+    if (t * n_expert > LMOE_ROUTE_NOALLOC_MAX_LOGITS)
+        return lmoe_fail(LMOE_ERR_INVALID,
+                         "route_noalloc: t * n_expert = %lld exceeds the built-in scratch of %d logits; use lmoe_route with a workspace",
+                         (long long)(t * n_expert), LMOE_ROUTE_NOALLOC_MAX_LOGITS);
+    if (!router || !x || !ids_out || !weights_out) return lmoe_fail(LMOE_ERR_INVALID, "router/x/ids_out/weights_out is NULL");
+    if (hidden % 4 == 0 && (((uintptr_t)router | (uintptr_t)x) & 15u))
+        return lmoe_fail(LMOE_ERR_INVALID, "router and x must be 16-byte aligned");
+    // In host code the array's name is only a stand-in; the kernels need its device address, which
+    // differs per GPU.  It is looked up once per device, with that device current.
+    static float *dev_ptr[64] = {nullptr};
+    int dev = 0;
+    LMOE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    if (!dev_ptr[dev]) {
+        float *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&p, g_route_noalloc_logits);
+        if (e != cudaSuccess || !p)
+            return lmoe_fail(LMOE_ERR_CUDA, "cudaGetSymbolAddress(route scratch) failed: %s", cudaGetErrorString(e));
+        dev_ptr[dev] = p;
+    }
+    float *logits = dev_ptr[dev];
+    // nothing has to start at zero: every logit a launch reads was written by the same call
+    LMOE_CUDA(launch_route_logits(router, x, (int)t, (int)hidden, (int)n_expert, logits, (cudaStream_t)stream));
+    LMOE_CUDA(launch_route_select(logits, bias, (int)t, (int)n_expert, (int)top_k, scale, norm, ids_out, weights_out,
+                                  (cudaStream_t)stream));
+    return LMOE_OK;
+}
