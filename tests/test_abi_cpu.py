@@ -70,3 +70,21 @@ def test_host_mirror_rejects_cpu_tensors():
         ops.silu_mul(torch.zeros(4), torch.zeros(4))
     with pytest.raises(LmoeError):
         ops.combine(torch.zeros(1, 2, 3), None, torch.zeros(1, 2))
+
+
+def test_cpp_host_mirror_compiles_and_reports_errors(tmp_path):
+    import shutil
+    import subprocess
+
+    from maxuna_b200 import _native
+
+    _native.lib()
+    gxx = shutil.which("g++")
+    assert gxx, "g++ not found"
+    exe = str(tmp_path / "host_errors")
+    libdir = os.path.dirname(_native.lib_path())
+    env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
+    subprocess.run([gxx, "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "host_errors.cpp"), "-o", exe,
+                    "-L" + libdir, "-llmoe", "-Wl,-rpath," + libdir], check=True, env=env)
+    out = subprocess.run([exe], capture_output=True, text=True, env=env)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout + out.stderr
