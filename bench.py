@@ -176,7 +176,7 @@ def zipf_bias(n_expert, seed, device):
     return b.to(device)
 
 
-def measure_prefill(dev, rank, world, steps=8, warmup=3):
+def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None):
     """Prefill of one MoE layer: N=1 -> config 3 (4096 tokens, Zipf-skewed routing, one GPU);
     N>1 -> config 4 (16384 tokens split over the ranks, experts sharded 256/N per GPU,
     NCCL all-to-all dispatch / combine), uniform and Zipf.  Returns TFLOP/s figures."""
@@ -187,7 +187,7 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3):
     from maxuna_b200.moe import MoeBlock
 
     res = {}
-    t_total = 4096 if world == 1 else 16384
+    t_total = tokens if tokens else (4096 if world == 1 else 16384)
     for name in (("zipf",) if world == 1 else ("uniform", "zipf")):
         bias = zipf_bias(E, 3, dev) if name == "zipf" else None
         blk = MoeBlock.random(H, F, E, K, seed=4242, device=dev, bias=bias)
@@ -232,6 +232,8 @@ def main():
     ap.add_argument("--layers", type=int, default=8, help="layer copies rotated through (working set >> L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (grouped GEMM) measurement")
+    ap.add_argument("--prefill-only", action="store_true", help="profiling aid: run only the prefill measurement and print it")
+    ap.add_argument("--prefill-tokens", type=int, default=0, help="profiling aid: token count of the prefill measurement")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -258,6 +260,14 @@ def main():
     from maxuna_b200.moe import MoeBlock
 
     _native.lib()
+    if args.prefill_only:
+        res = measure_prefill(dev, rank, world, steps=max(1, min(args.steps, 8)), warmup=args.warmup,
+                              tokens=args.prefill_tokens or None)
+        if rank == 0:
+            print(json.dumps({"prefill_only": res}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     layers = [MoeBlock.random(H, F, E, K, seed=100 * rank + i, device=dev) for i in range(args.layers)]
     n_x = 64
     gen = torch.Generator(device=dev)
@@ -393,7 +403,7 @@ def main():
     if not args.no_prefill:
         del layers, ws
         torch.cuda.empty_cache()
-        prefill = measure_prefill(dev, rank, world)
+        prefill = measure_prefill(dev, rank, world, tokens=args.prefill_tokens or None)
 
     if rank == 0:
         line = {
