@@ -57,6 +57,8 @@ struct DecodeParams {
     int norm, has_shared;
     uint32_t *ctrl;   // [0..3] flag, [4] grid barrier, [5] exit count, [8192..] optional timing stamps
     float *logits;    // [t][n_expert]
+    uint32_t *ids_ws; // [t][top_k] routing decision, written by the CTA that ranked the token
+    float *w_ws;
     __half *act_hl;   // [t*(top_k+1)][2][ff], k permuted within groups of 8
     float *ypart;     // [t*(top_k+1)][hidden]
 };
@@ -159,7 +161,6 @@ __device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, in
         atomicAdd(&ctrl[4], 1u);
         uint32_t i = 0;
         while (ld_acquire(&ctrl[4]) < target) {
-            __nanosleep(32);
             if (++i > SPIN_LIMIT) {
                 if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
                     ctrl[1] = 0x100u + target;
@@ -522,6 +523,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         // holds may be issued before the routing tables exist (consumers drain the ring
         // only after they have built them).
         unit_range(shared_passes * tiles1, u0, u1);
+        bar_sync(3, DEC_THREADS); // the consumers stage hidden states in the ring while they compute the logits
         if (lane == 0) {
             for (u = u0; u < u1 && u < u0 + NSTAGE; u++) {
                 const int tile = u % tiles1;
@@ -561,11 +563,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     STAMP(0);
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
     if (P.hidden == 128 * 24) {
-        // router row held in registers (all its loads in flight at once); hidden states of
-        // two tokens at a time staged as f32 in the (not yet used) activation cache
+        // router row held in registers (all its loads in flight at once); hidden states staged as
+        // f32, as many tokens at a time as the (not yet used) weight ring + activation cache hold
         constexpr int HB = 24;
         const int H = P.hidden;
-        float *xs32 = reinterpret_cast<float *>(xc);
+        float *xs32 = reinterpret_cast<float *>(ring);
+        const int xt_cap = max(1, (L.o_s - L.o_ring) / (H * 4));
         for (int er = 0; er * G * CW < E; er++) {
             const int e = blockIdx.x + G * (warp + CW * er);
             const bool have = e < E;
@@ -575,8 +578,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
 #pragma unroll
                 for (int j = 0; j < HB; j++) wv[j] = __ldg(wr + 32 * j);
             }
-            for (int t0 = 0; t0 < P.t; t0 += 2) {
-                const int nt = min(2, P.t - t0);
+            for (int t0 = 0; t0 < P.t; t0 += xt_cap) {
+                const int nt = min(xt_cap, P.t - t0);
                 bar_sync(1, CW * 32);
                 for (int i = tid; i < nt * (H / 4); i += CW * 32)
                     reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
@@ -629,27 +632,116 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
         }
     }
+    // selection bias -> shared memory (the expert-count table is not in use yet)
+    float *bias_s = reinterpret_cast<float *>(cnt_s);
+    for (int e = tid; e < E; e += CW * 32) bias_s[e] = P.bias ? __ldg(P.bias + e) : 0.0f;
+    bar_sync(3, DEC_THREADS); // the weight ring is free from here on: the producer may start
     STAMP(1);
     grid_barrier(P.ctrl, (uint32_t)G, tid);
     STAMP(2);
 
-    // ---- phase 0b: selection, redundantly in every CTA ----
-    {
-        for (int tok = warp; tok < P.t; tok += CW) {
-            const float *lrow = P.logits + (size_t)tok * E;
-            lmoe_warp_select_regs([&](int e) { return __ldcg(lrow + e); }, P.bias, E, K, P.scale, P.norm,
-                                  ids_s + tok * K, w_s + tok * K, lane);
+    // ---- phase 0b: selection.  Token i is handled by CTA i: each of the four warps ranks a quarter of
+    //      the experts (register-light, rolled loops: this code runs once), warp 0 merges the 4*K
+    //      candidates; ties always go to the lower expert index, so the result equals a stable
+    //      descending sort.  Results travel through global memory and one more grid barrier. ----
+    if ((int)blockIdx.x < P.t) {
+        const int tok = blockIdx.x;
+        float *probs = reinterpret_cast<float *>(xc);
+        uint32_t *keys = reinterpret_cast<uint32_t *>(probs + E);
+        uint32_t *cand_key = keys + E, *cand_idx = cand_key + CW * 32;
+        const int eq = (E + CW - 1) / CW, lo = warp * eq, hi = min(E, lo + eq);
+        uint32_t best = 0u;
+        int best_i = 0x7fffffff;
+        {
+            float lg[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int e = lo + lane + 32 * i;
+                lg[i] = e < hi ? __ldcg(P.logits + (size_t)tok * E + e) : 0.0f;
+            }
+#pragma unroll 1
+            for (int i = 0; i < 4; i++) {
+                const int e = lo + lane + 32 * i;
+                if (e < hi) {
+                    const float p = lmoe_sigmoid_fixed(lg[i]);
+                    const float sv = __fadd_rn(__fadd_rn(p, bias_s[e]), 0.0f);
+                    const uint32_t u = __float_as_uint(sv);
+                    uint32_t kk = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                    kk = kk == 0u ? 1u : kk;
+                    probs[e] = p;
+                    keys[e] = kk;
+                    if (kk > best) { best = kk; best_i = e; }
+                }
+            }
         }
-        for (int e = tid; e < E; e += CW * 32) cnt_s[e] = 0;
+        __syncwarp();
+#pragma unroll 1
+        for (int k = 0; k < K; k++) {
+            const uint32_t m = __reduce_max_sync(0xffffffffu, best);
+            const uint32_t idx = __reduce_min_sync(0xffffffffu, best == m ? (uint32_t)best_i : 0xffffffffu);
+            if (lane == 0) { cand_key[warp * 32 + k] = m; cand_idx[warp * 32 + k] = idx; }
+            if (m != 0u && (int)idx == best_i && best == m) {
+                keys[idx] = 0u;
+                best = 0u;
+                best_i = 0x7fffffff;
+#pragma unroll 1
+                for (int e = lo + lane; e < hi; e += 32) {
+                    const uint32_t kk = keys[e];
+                    if (kk > best) { best = kk; best_i = e; }
+                }
+            }
+        }
+        bar_sync(1, CW * 32);
+        if (warp == 0) {
+            // lane l owns candidate l of warps 0..3 (K <= 32)
+            uint32_t ck[CW], ci[CW];
+#pragma unroll
+            for (int w = 0; w < CW; w++) {
+                ck[w] = lane < K ? cand_key[w * 32 + lane] : 0u;
+                ci[w] = lane < K ? cand_idx[w * 32 + lane] : 0xffffffffu;
+            }
+            float my_w = 0.0f;
+#pragma unroll 1
+            for (int k = 0; k < K; k++) {
+                uint32_t bk = 0u;
+#pragma unroll
+                for (int w = 0; w < CW; w++) bk = ck[w] > bk ? ck[w] : bk;
+                const uint32_t m = __reduce_max_sync(0xffffffffu, bk);
+                uint32_t bi = 0xffffffffu;
+#pragma unroll
+                for (int w = 0; w < CW; w++) bi = (ck[w] == m && ci[w] < bi) ? ci[w] : bi;
+                const uint32_t idx = __reduce_min_sync(0xffffffffu, bi);
+#pragma unroll
+                for (int w = 0; w < CW; w++) if (ci[w] == idx) ck[w] = 0u;
+                const float pw = probs[idx];
+                if (lane == k) my_w = pw;
+                if (lane == 0) P.ids_ws[tok * K + k] = idx;
+            }
+            if (P.norm) {
+                float sum = 0.0f;
+#pragma unroll 1
+                for (int k = 0; k < K; k++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_w, k));
+                sum = sum < 6.103515625e-5f ? 6.103515625e-5f : sum;
+                my_w = __fdiv_rn(my_w, sum);
+            }
+            if (P.scale != 0.0f && P.scale != 1.0f) my_w = __fmul_rn(my_w, P.scale);
+            if (lane < K) P.w_ws[tok * K + lane] = my_w;
+        }
     }
     STAMP(8);
-    bar_sync(1, CW * 32);
-    if (blockIdx.x == 0) {
-        for (int i = tid; i < P.t * K; i += CW * 32) {
-            if (P.ids_out) P.ids_out[i] = ids_s[i];
-            if (P.w_out) P.w_out[i] = w_s[i];
+    grid_barrier(P.ctrl, (uint32_t)(2 * G), tid);
+    for (int i = tid; i < P.t * K; i += CW * 32) {
+        const uint32_t id = __ldcg(P.ids_ws + i);
+        const float wv = __ldcg(P.w_ws + i);
+        ids_s[i] = id;
+        w_s[i] = wv;
+        if (blockIdx.x == 0) {
+            if (P.ids_out) P.ids_out[i] = id;
+            if (P.w_out) P.w_out[i] = wv;
         }
     }
+    for (int e = tid; e < E; e += CW * 32) cnt_s[e] = 0;
+    bar_sync(1, CW * 32);
     // ---- phase 0c: per-expert token lists ----
     for (int i = tid; i < P.t * K; i += CW * 32) atomicAdd(&cnt_s[ids_s[i]], 1u);
     bar_sync(1, CW * 32);
@@ -731,7 +823,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             unit_range((shared ? shared_passes : T.routed_passes) * tiles, u0, u1);
             for (int u = u0; u < u1; u++) {
                 const Unit U = make_unit(P, T, shared, u, tiles);
-                const int key = (phase << 24) | (shared << 23) | U.qpass;
+                // what the cache holds is identified by the rows staged into it
+                const int key = phase == 1 ? ((1 << 30) | (U.n_tok << 24) | (U.tok[0] << 12) | U.tok[1])
+                                           : ((2 << 30) | (U.n_tok << 24) | (U.pair[0] << 12) | U.pair[1]);
                 if (key != xkey) {
                     bar_sync(1, CW * 32); // everyone is done with the previous contents
                     if (phase == 1) stage_x(P, U, xc, sh, L.xs, L.ss, tid);
@@ -797,7 +891,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
         }
         STAMP(phase == 1 ? 4 : 6);
-        grid_barrier(P.ctrl, (uint32_t)((phase + 1) * G), tid);
+        grid_barrier(P.ctrl, (uint32_t)((phase + 2) * G), tid);
         STAMP(phase == 1 ? 5 : 7);
     }
 
@@ -840,6 +934,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
 size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k) {
     size_t o = 65536; // control words
     o += lmoe_align_up((size_t)t * n_expert * 4, 256);
+    o += 2 * lmoe_align_up((size_t)t * top_k * 4, 256);
     o += lmoe_align_up((size_t)t * (top_k + 1) * 2 * ff * 2, 256);
     o += lmoe_align_up((size_t)t * (top_k + 1) * hidden * 4, 256);
     return o;
@@ -895,6 +990,8 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
     P.ctrl = reinterpret_cast<uint32_t *>(ws);
     size_t o = 65536;
     P.logits = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * E * 4, 256);
+    P.ids_ws = reinterpret_cast<uint32_t *>(ws + o); o += lmoe_align_up((size_t)t * K * 4, 256);
+    P.w_ws = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * K * 4, 256);
     P.act_hl = reinterpret_cast<__half *>(ws + o); o += lmoe_align_up((size_t)t * (K + 1) * 2 * F * 2, 256);
     P.ypart = reinterpret_cast<float *>(ws + o);
     void *args[] = {&P};
