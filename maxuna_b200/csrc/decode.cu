@@ -38,7 +38,9 @@
 namespace {
 
 constexpr int CW = 4;                      // consumer warps
-constexpr int DEC_THREADS = 32 * (CW + 1); // + producer warp
+constexpr int DEC_THREADS = 32 * (CW + 2); // + producer warp + epilogue warp
+constexpr int RING_THREADS = 32 * (CW + 1); // consumers + producer
+constexpr int EPI_THREADS = 32 * (CW + 1);  // consumers + epilogue warp
 constexpr int NSTAGE = 3;
 constexpr int NTOK = 2;         // tokens per pass over an expert's weights
 constexpr int NCOL = 2 * NTOK;  // MMA columns in use: (token, hi/lo)
@@ -85,7 +87,7 @@ struct DecLayout {
         o += (xc_bytes + 15) / 16 * 16;
         o_s = o; o += NCOL * ss * 2;
         o_red = o; o += 2 * CW * 16 * NCOL * 4;
-        o_bar = o; o += 64;
+        o_bar = o; o += 128;
         o_ids = o; o += tk * 4;
         o_w = o; o += tk * 4;
         o_cnt = o; o += n_expert * 4;
@@ -140,6 +142,9 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 __device__ __forceinline__ void bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
+__device__ __forceinline__ void bar_arrive(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -154,9 +159,13 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t *p) {
 
 // Grid-wide barrier among the consumer threads of all CTAs (thread 0 of each
 // CTA arrives).  `target` = arrivals expected so far in this launch.
-__device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, int tid) {
+__device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, int tid, int first_id = 1,
+                                             int first_count = CW * 32) {
     __threadfence();
-    bar_sync(1, CW * 32);
+    bar_sync(first_id, first_count); // phases 1/2: the epilogue warp arrives here once its stores are fenced
+    if (tid == 0) {
+        __threadfence();
+    }
     if (tid == 0) {
         atomicAdd(&ctrl[4], 1u);
         uint32_t i = 0;
@@ -210,11 +219,13 @@ __device__ __forceinline__ int find_active(const uint16_t *ppre, int n_active, i
     return lo;
 }
 
-__device__ __forceinline__ Unit make_unit(const DecodeParams &P, const Tables &T, int shared, int u, int tiles) {
+// Everything about pass `q` (the tokens it serves); the tile index is set by the caller, which walks
+// consecutive tiles of one pass without recomputing this.
+__device__ __forceinline__ Unit make_pass(const DecodeParams &P, const Tables &T, int shared, int q) {
     Unit U;
     U.shared = shared;
-    U.qpass = u / tiles;
-    U.tile = u - U.qpass * tiles;
+    U.qpass = q;
+    U.tile = 0;
     if (shared) {
         U.expert = 0;
         U.n_tok = min(NTOK, P.t - U.qpass * NTOK);
@@ -478,6 +489,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     float *red = reinterpret_cast<float *>(smem + L.o_red);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.o_bar);
     uint64_t *empty = full + NSTAGE;
+    uint64_t *red_full = empty + NSTAGE, *red_free = red_full + 2; // K-split partial buffers: consumers -> epilogue warp
     uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + L.o_ids);
     float *w_s = reinterpret_cast<float *>(smem + L.o_w);
     uint32_t *cnt_s = reinterpret_cast<uint32_t *>(smem + L.o_cnt);
@@ -501,6 +513,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CW);
         }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&red_full[b], CW);
+            mbar_init(&red_free[b], 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -523,7 +539,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         // holds may be issued before the routing tables exist (consumers drain the ring
         // only after they have built them).
         unit_range(shared_passes * tiles1, u0, u1);
-        bar_sync(3, DEC_THREADS); // the consumers stage hidden states in the ring while they compute the logits
+        bar_sync(3, RING_THREADS); // the consumers stage hidden states in the ring while they compute the logits
         if (lane == 0) {
             for (u = u0; u < u1 && u < u0 + NSTAGE; u++) {
                 const int tile = u % tiles1;
@@ -539,20 +555,101 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
             const int n_active = s_n_active, routed_passes = s_routed_passes;
             unit_range(routed_passes * tiles1, u0, u1);
-            for (u = u0; u < u1; u++) {
-                const int q = u / tiles1, tile = u - q * tiles1;
-                const int e = act_s[find_active(ppre_s, n_active, q)];
-                fill(P.gate + e * gexp + (size_t)tile * 8 * row4, P.up + e * gexp + (size_t)tile * 8 * row4, 8 * row4);
+            if (u0 < u1) {
+                int q = u0 / tiles1, tile = u0 - q * tiles1;
+                int e = act_s[find_active(ppre_s, n_active, q)];
+                for (u = u0; u < u1; u++) {
+                    fill(P.gate + e * gexp + (size_t)tile * 8 * row4, P.up + e * gexp + (size_t)tile * 8 * row4, 8 * row4);
+                    if (++tile == tiles1 && u + 1 < u1) {
+                        tile = 0;
+                        e = act_s[find_active(ppre_s, n_active, ++q)];
+                    }
+                }
             }
             // phase 2 (weights do not depend on the grid barrier: keep streaming)
             unit_range(shared_passes * tiles2, u0, u1);
             for (u = u0; u < u1; u++) fill(P.sh_down + (size_t)(u % tiles2) * 16 * row6, nullptr, 16 * row6);
             unit_range(routed_passes * tiles2, u0, u1);
-            for (u = u0; u < u1; u++) {
-                const int q = u / tiles2, tile = u - q * tiles2;
-                const int e = act_s[find_active(ppre_s, n_active, q)];
-                fill(P.down + e * dexp + (size_t)tile * 16 * row6, nullptr, 16 * row6);
+            if (u0 < u1) {
+                int q = u0 / tiles2, tile = u0 - q * tiles2;
+                int e = act_s[find_active(ppre_s, n_active, q)];
+                for (u = u0; u < u1; u++) {
+                    fill(P.down + e * dexp + (size_t)tile * 16 * row6, nullptr, 16 * row6);
+                    if (++tile == tiles2 && u + 1 < u1) {
+                        tile = 0;
+                        e = act_s[find_active(ppre_s, n_active, ++q)];
+                    }
+                }
             }
+        }
+        return;
+    }
+
+    if (warp == CW + 1) {
+        // ===================== epilogue warp =====================
+        // Sums the K-split partials of each unit in a fixed order and writes the SwiGLU activation
+        // (phase 1) or the weighted partial output row (phase 2), off the consumers' critical path.
+        bar_sync(2, DEC_THREADS);
+        const Tables T{ids_s, w_s, off_s, plist_s, act_s, ppre_s, s_n_active, s_routed_passes, shared_passes};
+        uint32_t m = 0;
+        for (int phase = 1; phase <= 2; phase++) {
+            const int tiles = phase == 1 ? tiles1 : tiles2;
+            for (int kind = 0; kind < 2; kind++) {
+                const int shared = kind == 0;
+                int u0, u1;
+                unit_range((shared ? shared_passes : T.routed_passes) * tiles, u0, u1);
+                if (u0 >= u1) continue;
+                int q = u0 / tiles, tile = u0 - q * tiles;
+                Unit U = make_pass(P, T, shared, q);
+                for (int u = u0; u < u1; u++, m++) {
+                    const int buf = m & 1;
+                    mbar_wait(&red_full[buf], (m >> 1) & 1, P.ctrl, 0x30 + phase);
+                    const float *rb = red + buf * (CW * 16 * NCOL);
+                    if (phase == 1) {
+                        // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
+                        const int tk = lane >> 3, r = lane & 7;
+                        if (tk < U.n_tok) {
+                            float gv = 0.f, uv = 0.f;
+#pragma unroll
+                            for (int w = 0; w < CW; w++) {
+                                gv += rb[(w * 16 + r) * NCOL + 2 * tk];
+                                gv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
+                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk];
+                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk + 1];
+                            }
+                            const float sv = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+                            const float av = __fmul_rn(sv, uv);
+                            const __half h = __float2half_rn(av);
+                            __half *dst = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + tile * 8 + perm8(r);
+                            dst[0] = h;
+                            dst[P.ff] = __float2half_rn(av - __half2float(h));
+                        }
+                    } else {
+                        // weighted partial row of this (pair, tile); summed over slots in phase 3
+                        const int tk = lane >> 4, r = lane & 15;
+                        if (tk < U.n_tok) {
+                            float yv = 0.f;
+#pragma unroll
+                            for (int w = 0; w < CW; w++) {
+                                yv += rb[(w * 16 + r) * NCOL + 2 * tk];
+                                yv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
+                            }
+                            const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
+                            if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
+                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + tile * 16 + r, yv);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&red_free[buf]);
+                    if (++tile == tiles && u + 1 < u1) {
+                        tile = 0;
+                        U = make_pass(P, T, shared, ++q);
+                    }
+                }
+            }
+            // this phase's results are complete: join the consumers' grid barrier
+            __threadfence();
+            bar_arrive(4, EPI_THREADS);
         }
         return;
     }
@@ -635,7 +732,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     // selection bias -> shared memory (the expert-count table is not in use yet)
     float *bias_s = reinterpret_cast<float *>(cnt_s);
     for (int e = tid; e < E; e += CW * 32) bias_s[e] = P.bias ? __ldg(P.bias + e) : 0.0f;
-    bar_sync(3, DEC_THREADS); // the weight ring is free from here on: the producer may start
+    bar_sync(3, RING_THREADS); // the weight ring is free from here on: the producer may start
     STAMP(1);
     grid_barrier(P.ctrl, (uint32_t)G, tid);
     STAMP(2);
@@ -812,7 +909,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
 
     uint32_t n = 0; // ring fill counter, same sequence as the producer's
     int xkey = -1;
-    int redbuf = 0;
 
     // ---- phases 1 and 2 ----
     for (int phase = 1; phase <= 2; phase++) {
@@ -821,8 +917,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             const int shared = kind == 0;
             int u0, u1;
             unit_range((shared ? shared_passes : T.routed_passes) * tiles, u0, u1);
+            if (u0 >= u1) continue;
+            int q = u0 / tiles, tile = u0 - q * tiles;
+            Unit U = make_pass(P, T, shared, q);
             for (int u = u0; u < u1; u++) {
-                const Unit U = make_unit(P, T, shared, u, tiles);
                 // what the cache holds is identified by the rows staged into it
                 const int key = phase == 1 ? ((1 << 30) | (U.n_tok << 24) | (U.tok[0] << 12) | U.tok[1])
                                            : ((2 << 30) | (U.n_tok << 24) | (U.pair[0] << 12) | U.pair[1]);
@@ -842,56 +940,26 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 else unit_q6k(stage, row6, nb6, warp, g, t4, xc + g * L.xs, sh + g * L.ss, colv, acc);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
-                n++;
-                // K-split partials -> shared memory
-                float *rb = red + redbuf * (CW * 16 * NCOL);
+                // K-split partials -> shared memory, handed to the epilogue warp (two buffers in flight)
+                const int buf = n & 1;
+                mbar_wait(&red_free[buf], ((n >> 1) & 1) ^ 1, P.ctrl, 0x28 + phase);
+                float *rb = red + buf * (CW * 16 * NCOL);
                 if (t4 < NTOK) {
                     float *r0 = rb + (warp * 16 + g) * NCOL + 2 * t4;
                     r0[0] = acc[0]; r0[1] = acc[1];
                     r0[8 * NCOL] = acc[2]; r0[8 * NCOL + 1] = acc[3];
                 }
-                bar_sync(1, CW * 32);
-                if (warp == (int)(n & (CW - 1))) { // the epilogue rotates over the warps
-                    if (phase == 1) {
-                        // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
-                        const int tk = lane >> 3, r = lane & 7;
-                        if (tk < U.n_tok) {
-                            float gv = 0.f, uv = 0.f;
-#pragma unroll
-                            for (int w = 0; w < CW; w++) {
-                                gv += rb[(w * 16 + r) * NCOL + 2 * tk];
-                                gv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
-                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk];
-                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk + 1];
-                            }
-                            const float sv = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
-                            const float av = __fmul_rn(sv, uv);
-                            const __half h = __float2half_rn(av);
-                            __half *dst = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + U.tile * 8 + perm8(r);
-                            dst[0] = h;
-                            dst[P.ff] = __float2half_rn(av - __half2float(h));
-                        }
-                    } else {
-                        // weighted partial row of this (pair, tile); summed over slots in phase 3
-                        const int tk = lane >> 4, r = lane & 15;
-                        if (tk < U.n_tok) {
-                            float yv = 0.f;
-#pragma unroll
-                            for (int w = 0; w < CW; w++) {
-                                yv += rb[(w * 16 + r) * NCOL + 2 * tk];
-                                yv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
-                            }
-                            const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
-                            if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
-                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + U.tile * 16 + r, yv);
-                        }
-                    }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_full[buf]);
+                n++;
+                if (++tile == tiles && u + 1 < u1) {
+                    tile = 0;
+                    U = make_pass(P, T, shared, ++q);
                 }
-                redbuf ^= 1;
             }
         }
         STAMP(phase == 1 ? 4 : 6);
-        grid_barrier(P.ctrl, (uint32_t)((phase + 2) * G), tid);
+        grid_barrier(P.ctrl, (uint32_t)((phase + 2) * G), tid, 4, EPI_THREADS);
         STAMP(phase == 1 ? 5 : 7);
     }
 
