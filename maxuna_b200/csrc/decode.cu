@@ -37,7 +37,8 @@
 
 namespace {
 
-constexpr int CW = 4;                      // consumer warps
+constexpr int CW = 4;                      // consumer warps (even)
+constexpr int DOWN_ROWS = 32;              // rows of a down-projection unit: two MMA row tiles
 constexpr int DEC_THREADS = 32 * (CW + 2); // + producer warp + epilogue warp
 constexpr int RING_THREADS = 32 * (CW + 1); // consumers + producer
 constexpr int EPI_THREADS = 32 * (CW + 1);  // consumers + epilogue warp
@@ -71,7 +72,7 @@ struct DecLayout {
     int o_ring, o_xc, o_s, o_red, o_bar, o_ids, o_w, o_cnt, o_off, o_plist, o_act, o_ppre, total;
     __host__ __device__ DecLayout(int hidden, int ff, int n_expert, int t, int top_k) {
         const int row4 = hidden / QK_K * Q4K_BYTES, row6 = ff / QK_K * Q6K_BYTES;
-        int sb = 16 * row4 > 16 * row6 ? 16 * row4 : 16 * row6;
+        int sb = 16 * row4 > DOWN_ROWS * row6 ? 16 * row4 : DOWN_ROWS * row6;
         stage_bytes = (sb + 127) / 128 * 128;
         const int kmax = hidden > ff ? hidden : ff;
         xs = kmax + 32; // halfs per column (+64 B so two columns land in different bank halves)
@@ -86,11 +87,14 @@ struct DecLayout {
         if (sel_bytes > xc_bytes) xc_bytes = sel_bytes;
         o += (xc_bytes + 15) / 16 * 16;
         o_s = o; o += NCOL * ss * 2;
-        o_red = o; o += 2 * CW * 16 * NCOL * 4;
+        // the K-split partial buffers (phases 1-2) share their space with two routing tables that are
+        // only alive while the token lists are built: expert counts and the id list
+        int red_bytes = 2 * CW * 16 * NCOL * 4;
+        if (red_bytes < (n_expert + tk) * 4) red_bytes = (n_expert + tk) * 4;
+        o_red = o; o_cnt = o; o_ids = o + n_expert * 4;
+        o += (red_bytes + 15) / 16 * 16;
         o_bar = o; o += 128;
-        o_ids = o; o += tk * 4;
         o_w = o; o += tk * 4;
-        o_cnt = o; o += n_expert * 4;
         o_off = o; o += (n_expert + 2) / 2 * 2 * 2;
         o_plist = o; o += (tk + 1) / 2 * 2 * 2;
         o_act = o; o += (tk + 2) / 2 * 2 * 2;
@@ -124,9 +128,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait: gives up after SPIN_LIMIT polls, records the fact and carries on
 // (results are then invalid, but every loop in the kernel stays finite).
+template <int BACKOFF_NS = 0>
 __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *ctrl, uint32_t where) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; i++)
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
+        // service warps (producer, epilogue) poll slowly so that they do not take issue slots from the math
+        if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
+    }
     if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
         ctrl[1] = where;
         ctrl[2] = blockIdx.x;
@@ -323,12 +331,16 @@ __device__ __forceinline__ float byte_to_float(uint32_t w) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + I)) - 8388608.0f;
 }
 
-// 16 Q4_K rows (8 gate + 8 up) x the blocks of this warp.  acc: rows g / g+8, columns 2t, 2t+1.
+// 16 Q4_K rows (8 gate + 8 up).  Work item of a warp: a super-block (CW <= 4) or half of one (CW is
+// then even, so a warp always works on the same half).  acc: rows g / g+8, columns 2t, 2t+1.
+constexpr int Q4_SPLIT = CW > 4 ? 2 : 1;
 __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
-                                         const __half *xcol, const __half *scol, bool colv, float (&acc)[4]) {
+                                         const __half *xcol, const __half *scol, float (&acc)[4]) {
+    constexpr int HPI = 2 / Q4_SPLIT; // halves per item
     const uint8_t *rg = stage + g * row_bytes;
     const uint8_t *rG = rg + 8 * row_bytes;
-    for (int b = warp; b < nb; b += CW) {
+    for (int it = warp; it < Q4_SPLIT * nb; it += CW) {
+        const int b = it / Q4_SPLIT, h0 = (it % Q4_SPLIT) * HPI;
         const uint8_t *bg = rg + b * Q4K_BYTES, *bG = rG + b * Q4K_BYTES;
         const uint4 hg = *reinterpret_cast<const uint4 *>(bg);
         const uint4 hG = *reinterpret_cast<const uint4 *>(bG);
@@ -336,45 +348,49 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
         const float mg = lmoe_h2f((uint16_t)(hg.x >> 16)) * 16777216.f;
         const float dG = lmoe_h2f((uint16_t)(hG.x & 0xffff)) * 16777216.f;
         const float mG = lmoe_h2f((uint16_t)(hG.x >> 16)) * 16777216.f;
-        uint32_t scg[2], mng[2], scG[2], mnG[2];
+        uint32_t scg[2], mng[2], scG[2], mnG[2]; // (scale, min) pairs, one per byte, per half
         q4k_unpack_scales(hg.y, hg.z, hg.w, scg[0], scg[1], mng[0], mng[1]);
         q4k_unpack_scales(hG.y, hG.z, hG.w, scG[0], scG[1], mnG[0], mnG[1]);
-        // min term: one MMA, A = the 8 six-bit mins of each row, B = 32-wide activation sums
+        // min term: one MMA, A = the six-bit mins of each row (of this item's halves), B = 32-wide activation sums
         float cm[4];
         {
+            const bool mine = Q4_SPLIT == 1 || (t >> 1) == h0;
             const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
-            const uint32_t ma = __byte_perm(t < 2 ? mng[0] : mng[1], 0u, sel);
-            const uint32_t mA = __byte_perm(t < 2 ? mnG[0] : mnG[1], 0u, sel);
-            const uint32_t sb = colv ? *reinterpret_cast<const uint32_t *>(scol + 8 * b + 2 * t) : 0u;
+            const uint32_t ma = mine ? __byte_perm(t < 2 ? mng[0] : mng[1], 0u, sel) : 0u;
+            const uint32_t mA = mine ? __byte_perm(t < 2 ? mnG[0] : mnG[1], 0u, sel) : 0u;
+            const uint32_t sb = *reinterpret_cast<const uint32_t *>(scol + 8 * b + 2 * t);
             mma16816_z(cm, ma, mA, 0u, 0u, sb, 0u);
         }
         // low-nibble and high-nibble sub-blocks accumulate apart (they differ by a factor 16)
         float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint2 wg = *reinterpret_cast<const uint2 *>(bg + 16 + 32 * j + 8 * t);
-            const uint2 wG = *reinterpret_cast<const uint2 *>(bG + 16 + 32 * j + 8 * t);
-            uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = make_uint4(0u, 0u, 0u, 0u);
-            if (colv) {
-                xl = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 8 * t);
-                xh = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
+        for (int hh = 0; hh < HPI; hh++) {
+            const int h = h0 + hh;
+            const uint32_t sg = h ? scg[1] : scg[0], sG = h ? scG[1] : scG[0];
+#pragma unroll
+            for (int jj = 0; jj < 2; jj++) {
+                const int j = 2 * h + jj;
+                const uint2 wg = *reinterpret_cast<const uint2 *>(bg + 16 + 32 * j + 8 * t);
+                const uint2 wG = *reinterpret_cast<const uint2 *>(bG + 16 + 32 * j + 8 * t);
+                const uint4 xl = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 8 * t);
+                const uint4 xh = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
+                const uint32_t sg8 = wg.x >> 8, sG8 = wG.x >> 8, tg8 = wg.y >> 8, tG8 = wG.y >> 8;
+                float fl[4], fh[4];
+                mma16816_z(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, sg8 & 0x000F000Fu, sG8 & 0x000F000Fu, xl.x, xl.y);
+                mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, tg8 & 0x000F000Fu, tG8 & 0x000F000Fu, xl.z, xl.w);
+                mma16816_z(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, sg8 & 0x00F000F0u, sG8 & 0x00F000F0u, xh.x, xh.y);
+                mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, tg8 & 0x00F000F0u, tG8 & 0x00F000F0u, xh.z, xh.w);
+                float s0g, s1g, s0G, s1G;
+                if (jj) {
+                    s0g = byte_to_float<2>(sg); s1g = byte_to_float<3>(sg);
+                    s0G = byte_to_float<2>(sG); s1G = byte_to_float<3>(sG);
+                } else {
+                    s0g = byte_to_float<0>(sg); s1g = byte_to_float<1>(sg);
+                    s0G = byte_to_float<0>(sG); s1G = byte_to_float<1>(sG);
+                }
+                al[0] += s0g * fl[0]; al[1] += s0g * fl[1]; al[2] += s0G * fl[2]; al[3] += s0G * fl[3];
+                ah[0] += s1g * fh[0]; ah[1] += s1g * fh[1]; ah[2] += s1G * fh[2]; ah[3] += s1G * fh[3];
             }
-            const uint32_t sg8 = wg.x >> 8, sG8 = wG.x >> 8, tg8 = wg.y >> 8, tG8 = wG.y >> 8;
-            float fl[4], fh[4];
-            mma16816_z(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, sg8 & 0x000F000Fu, sG8 & 0x000F000Fu, xl.x, xl.y);
-            mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, tg8 & 0x000F000Fu, tG8 & 0x000F000Fu, xl.z, xl.w);
-            mma16816_z(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, sg8 & 0x00F000F0u, sG8 & 0x00F000F0u, xh.x, xh.y);
-            mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, tg8 & 0x00F000F0u, tG8 & 0x00F000F0u, xh.z, xh.w);
-            float s0g, s1g, s0G, s1G;
-            if (j & 1) {
-                s0g = byte_to_float<2>(scg[j >> 1]); s1g = byte_to_float<3>(scg[j >> 1]);
-                s0G = byte_to_float<2>(scG[j >> 1]); s1G = byte_to_float<3>(scG[j >> 1]);
-            } else {
-                s0g = byte_to_float<0>(scg[j >> 1]); s1g = byte_to_float<1>(scg[j >> 1]);
-                s0G = byte_to_float<0>(scG[j >> 1]); s1G = byte_to_float<1>(scG[j >> 1]);
-            }
-            al[0] += s0g * fl[0]; al[1] += s0g * fl[1]; al[2] += s0G * fl[2]; al[3] += s0G * fl[3];
-            ah[0] += s1g * fh[0]; ah[1] += s1g * fh[1]; ah[2] += s1G * fh[2]; ah[3] += s1G * fh[3];
         }
         acc[0] += dg * (al[0] + 0.0625f * ah[0]) - mg * cm[0];
         acc[1] += dg * (al[1] + 0.0625f * ah[1]) - mg * cm[1];
@@ -383,14 +399,19 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
     }
 }
 
-__device__ __forceinline__ uint32_t lds32_a2(const uint8_t *p) {
-    // p is 2-byte aligned; both neighbouring words are inside the staged tile
-    if (reinterpret_cast<uintptr_t>(p) & 2) {
-        const uint32_t lo = *reinterpret_cast<const uint32_t *>(p - 2);
-        const uint32_t hi = *reinterpret_cast<const uint32_t *>(p + 2);
+// Four bytes at p + off.  MODE 0: p is word aligned.  MODE 1: p is 2 (mod 4), the bytes straddle two
+// aligned words.  MODE 2: either, decided per lane (both words are always inside shared memory).
+template <int MODE>
+__device__ __forceinline__ uint32_t lds32(const uint8_t *p, int off) {
+    if (MODE == 0) return *reinterpret_cast<const uint32_t *>(p + off);
+    if (MODE == 1) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t *>(p + off - 2);
+        const uint32_t hi = *reinterpret_cast<const uint32_t *>(p + off + 2);
         return __byte_perm(lo, hi, 0x5432);
     }
-    return *reinterpret_cast<const uint32_t *>(p);
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p + off);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    return __byte_perm(q[0], q[1], (a & 2) ? 0x5432u : 0x3210u);
 }
 
 __device__ __forceinline__ uint32_t sc_pair_half2(const int8_t *p) {
@@ -398,73 +419,81 @@ __device__ __forceinline__ uint32_t sc_pair_half2(const int8_t *p) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// 16 Q6_K rows x the blocks of this warp.
-__device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
-                                         const __half *xcol, const __half *scol, bool colv, float (&acc)[4]) {
-    const uint8_t *rg = stage + g * row_bytes;
-    const uint8_t *rG = rg + 8 * row_bytes;
-    for (int b = warp; b < nb; b += CW) {
-        const uint8_t *bg = rg + b * Q6K_BYTES, *bG = rG + b * Q6K_BYTES;
-        const int8_t *scg = reinterpret_cast<const int8_t *>(bg + 192);
-        const int8_t *scG = reinterpret_cast<const int8_t *>(bG + 192);
-        const float dg = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bg + 208));
-        const float dG = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bG + 208));
-        // "-32" offset: one MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
-        float co[4];
-        {
-            uint32_t s0 = 0u, s1 = 0u;
-            if (colv) {
-                s0 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t);
-                s1 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t + 8);
-            }
-            mma16816_z(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
-                       sc_pair_half2(scG + 2 * t + 8), s0, s1);
-        }
-        float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
+// byte I (0..3) of `w`, which holds int8 + 128, as an exact float
+__device__ __forceinline__ float biased_byte_to_float(uint32_t w, int i) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + i)) - 8388736.0f; // 2^23 + 128
+}
+
+// One Q6_K super-block of rows g (bg) and g+8 (bG), which have the same alignment.
+template <int MIS>
+__device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, int b, int t, const __half *xcol,
+                                          const __half *scol, float (&acc)[4]) {
+    const int8_t *scg = reinterpret_cast<const int8_t *>(bg + 192);
+    const int8_t *scG = reinterpret_cast<const int8_t *>(bG + 192);
+    const float dg = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bg + 208));
+    const float dG = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bG + 208));
+    // "-32" offset: one MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
+    float co[4];
+    {
+        const uint32_t s0 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t);
+        const uint32_t s1 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t + 8);
+        mma16816_z(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
+                   sc_pair_half2(scG + 2 * t + 8), s0, s1);
+    }
+    float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-        for (int n = 0; n < 2; n++) {
-            // the eight scales of this half, biased to unsigned so a byte permute turns them into floats
-            const uint32_t swg0 = lds32_a2(bg + 192 + 8 * n) ^ 0x80808080u, swg1 = lds32_a2(bg + 196 + 8 * n) ^ 0x80808080u;
-            const uint32_t swG0 = lds32_a2(bG + 192 + 8 * n) ^ 0x80808080u, swG1 = lds32_a2(bG + 196 + 8 * n) ^ 0x80808080u;
+    for (int n = 0; n < 2; n++) {
+        // the eight scales of this half, biased to unsigned so a byte permute turns them into floats
+        const uint32_t swg0 = lds32<MIS>(bg, 192 + 8 * n) ^ 0x80808080u, swg1 = lds32<MIS>(bg, 196 + 8 * n) ^ 0x80808080u;
+        const uint32_t swG0 = lds32<MIS>(bG, 192 + 8 * n) ^ 0x80808080u, swG1 = lds32<MIS>(bG, 196 + 8 * n) ^ 0x80808080u;
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                const int l0 = 16 * c + 4 * t;
-                const uint32_t qa_g = lds32_a2(bg + 64 * n + l0), qb_g = lds32_a2(bg + 64 * n + 32 + l0);
-                const uint32_t qh_g = lds32_a2(bg + 128 + 32 * n + l0);
-                const uint32_t qa_G = lds32_a2(bG + 64 * n + l0), qb_G = lds32_a2(bG + 64 * n + 32 + l0);
-                const uint32_t qh_G = lds32_a2(bG + 128 + 32 * n + l0);
-                const __half *xp = xcol + 256 * b + 128 * n + 16 * c + 4 * t;
+        for (int c = 0; c < 2; c++) {
+            const int l0 = 16 * c + 4 * t;
+            const uint32_t qa_g = lds32<MIS>(bg, 64 * n + l0), qb_g = lds32<MIS>(bg, 64 * n + 32 + l0);
+            const uint32_t qh_g = lds32<MIS>(bg, 128 + 32 * n + l0);
+            const uint32_t qa_G = lds32<MIS>(bG, 64 * n + l0), qb_G = lds32<MIS>(bG, 64 * n + 32 + l0);
+            const uint32_t qh_G = lds32<MIS>(bG, 128 + 32 * n + l0);
+            const __half *xp = xcol + 256 * b + 128 * n + 16 * c + 4 * t;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    // group i: q1 (ql lo | qh 0-1), q2 (ql+32 lo | qh 2-3), q3 (ql hi | qh 4-5), q4 (ql+32 hi | qh 6-7)
-                    const uint32_t qg = (i & 1) ? qb_g : qa_g, qG = (i & 1) ? qb_G : qa_G;
-                    const uint32_t hg = (i & 1) ? (qh_g << 2) : (qh_g << 4), hG = (i & 1) ? (qh_G << 2) : (qh_G << 4);
-                    const uint32_t hg8 = (i & 1) ? (qh_g >> 6) : (qh_g >> 4), hG8 = (i & 1) ? (qh_G >> 6) : (qh_G >> 4);
-                    const uint32_t ml = (i & 2) ? 0x00F000F0u : 0x000F000Fu, mh = (i & 2) ? 0x03000300u : 0x00300030u;
-                    const uint32_t a0 = (qg & ml) | (hg & mh), a1 = (qG & ml) | (hG & mh);
-                    const uint32_t a2 = ((qg >> 8) & ml) | (hg8 & mh), a3 = ((qG >> 8) & ml) | (hG8 & mh);
-                    uint2 xv = make_uint2(0u, 0u);
-                    if (colv) xv = *reinterpret_cast<const uint2 *>(xp + 32 * i);
-                    float f[4];
-                    mma16816_z(f, a0, a1, a2, a3, xv.x, xv.y);
-                    // scale index within the half: 2*i + c
-                    float sg, sG;
-                    if (i < 2) {
-                        sg = (c ? byte_to_float<1>(swg0 >> (16 * i)) : byte_to_float<0>(swg0 >> (16 * i))) - 128.f;
-                        sG = (c ? byte_to_float<1>(swG0 >> (16 * i)) : byte_to_float<0>(swG0 >> (16 * i))) - 128.f;
-                        al[0] += sg * f[0]; al[1] += sg * f[1]; al[2] += sG * f[2]; al[3] += sG * f[3];
-                    } else {
-                        sg = (c ? byte_to_float<1>(swg1 >> (16 * (i - 2))) : byte_to_float<0>(swg1 >> (16 * (i - 2)))) - 128.f;
-                        sG = (c ? byte_to_float<1>(swG1 >> (16 * (i - 2))) : byte_to_float<0>(swG1 >> (16 * (i - 2)))) - 128.f;
-                        ah[0] += sg * f[0]; ah[1] += sg * f[1]; ah[2] += sG * f[2]; ah[3] += sG * f[3];
-                    }
+            for (int i = 0; i < 4; i++) {
+                // group i: q1 (ql lo | qh 0-1), q2 (ql+32 lo | qh 2-3), q3 (ql hi | qh 4-5), q4 (ql+32 hi | qh 6-7)
+                const uint32_t qg = (i & 1) ? qb_g : qa_g, qG = (i & 1) ? qb_G : qa_G;
+                const uint32_t hg = (i & 1) ? (qh_g << 2) : (qh_g << 4), hG = (i & 1) ? (qh_G << 2) : (qh_G << 4);
+                const uint32_t hg8 = (i & 1) ? (qh_g >> 6) : (qh_g >> 4), hG8 = (i & 1) ? (qh_G >> 6) : (qh_G >> 4);
+                const uint32_t ml = (i & 2) ? 0x00F000F0u : 0x000F000Fu, mh = (i & 2) ? 0x03000300u : 0x00300030u;
+                const uint32_t a0 = (qg & ml) | (hg & mh), a1 = (qG & ml) | (hG & mh);
+                const uint32_t a2 = ((qg >> 8) & ml) | (hg8 & mh), a3 = ((qG >> 8) & ml) | (hG8 & mh);
+                const uint2 xv = *reinterpret_cast<const uint2 *>(xp + 32 * i);
+                float f[4];
+                mma16816_z(f, a0, a1, a2, a3, xv.x, xv.y);
+                // scale index within the half: 2*i + c -> byte 2*(i & 1) + c of word i >> 1
+                const float sg = biased_byte_to_float(i < 2 ? swg0 : swg1, 2 * (i & 1) + c);
+                const float sG = biased_byte_to_float(i < 2 ? swG0 : swG1, 2 * (i & 1) + c);
+                if (i < 2) {
+                    al[0] += sg * f[0]; al[1] += sg * f[1]; al[2] += sG * f[2]; al[3] += sG * f[3];
+                } else {
+                    ah[0] += sg * f[0]; ah[1] += sg * f[1]; ah[2] += sG * f[2]; ah[3] += sG * f[3];
                 }
             }
         }
-        acc[0] += dg * ((al[0] + 0.0625f * ah[0]) * 16777216.f - 32.f * co[0]);
-        acc[1] += dg * ((al[1] + 0.0625f * ah[1]) * 16777216.f - 32.f * co[1]);
-        acc[2] += dG * ((al[2] + 0.0625f * ah[2]) * 16777216.f - 32.f * co[2]);
-        acc[3] += dG * ((al[3] + 0.0625f * ah[3]) * 16777216.f - 32.f * co[3]);
+    }
+    acc[0] += dg * ((al[0] + 0.0625f * ah[0]) * 16777216.f - 32.f * co[0]);
+    acc[1] += dg * ((al[1] + 0.0625f * ah[1]) * 16777216.f - 32.f * co[1]);
+    acc[2] += dG * ((al[2] + 0.0625f * ah[2]) * 16777216.f - 32.f * co[2]);
+    acc[3] += dG * ((al[3] + 0.0625f * ah[3]) * 16777216.f - 32.f * co[3]);
+}
+
+// 32 Q6_K rows: warp w takes row tile w & 1 (16 rows) and every (CW/2)-th super-block of it.
+// Super-blocks are 210 bytes long, so every other one starts 2 bytes off a word boundary.
+__device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
+                                         const __half *xcol, const __half *scol, float (&acc)[4]) {
+    const uint8_t *rg = stage + ((warp & 1) * 16 + g) * row_bytes;
+    const uint8_t *rG = rg + 8 * row_bytes;
+    for (int b = warp >> 1; b < nb; b += CW / 2) {
+        const uint8_t *bg = rg + b * Q6K_BYTES, *bG = rG + b * Q6K_BYTES;
+        if (row_bytes & 2) q6k_block<2>(bg, bG, b, t, xcol, scol, acc); // odd block count: rows alternate too
+        else if (b & 1) q6k_block<1>(bg, bG, b, t, xcol, scol, acc);
+        else q6k_block<0>(bg, bG, b, t, xcol, scol, acc);
     }
 }
 
@@ -504,7 +533,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     const int K = P.top_k, E = P.n_expert;
     const int nb4 = P.hidden / QK_K, nb6 = P.ff / QK_K;
     const int row4 = nb4 * Q4K_BYTES, row6 = nb6 * Q6K_BYTES;
-    const int tiles1 = P.ff / 8, tiles2 = P.hidden / 16;
+    const int tiles1 = P.ff / 8, tiles2 = P.hidden / DOWN_ROWS;
     const int shared_passes = P.has_shared ? (P.t + NTOK - 1) / NTOK : 0;
     const size_t gexp = (size_t)P.ff * row4, dexp = (size_t)P.hidden * row6;
 
@@ -527,7 +556,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         auto fill = [&](const uint8_t *src0, const uint8_t *src1, uint32_t bytes_each) {
             const int s = n % NSTAGE;
             const uint32_t r = n / NSTAGE;
-            mbar_wait(&empty[s], (r & 1) ^ 1, P.ctrl, 0x10);
+            mbar_wait<200>(&empty[s], (r & 1) ^ 1, P.ctrl, 0x10);
             uint8_t *dst = ring + (size_t)s * L.stage_bytes;
             mbar_expect_tx(&full[s], src1 ? 2 * bytes_each : bytes_each);
             bulk_g2s(dst, src0, bytes_each, &full[s]);
@@ -568,13 +597,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
             // phase 2 (weights do not depend on the grid barrier: keep streaming)
             unit_range(shared_passes * tiles2, u0, u1);
-            for (u = u0; u < u1; u++) fill(P.sh_down + (size_t)(u % tiles2) * 16 * row6, nullptr, 16 * row6);
+            for (u = u0; u < u1; u++) fill(P.sh_down + (size_t)(u % tiles2) * DOWN_ROWS * row6, nullptr, DOWN_ROWS * row6);
             unit_range(routed_passes * tiles2, u0, u1);
             if (u0 < u1) {
                 int q = u0 / tiles2, tile = u0 - q * tiles2;
                 int e = act_s[find_active(ppre_s, n_active, q)];
                 for (u = u0; u < u1; u++) {
-                    fill(P.down + e * dexp + (size_t)tile * 16 * row6, nullptr, 16 * row6);
+                    fill(P.down + e * dexp + (size_t)tile * DOWN_ROWS * row6, nullptr, DOWN_ROWS * row6);
                     if (++tile == tiles2 && u + 1 < u1) {
                         tile = 0;
                         e = act_s[find_active(ppre_s, n_active, ++q)];
@@ -603,7 +632,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 Unit U = make_pass(P, T, shared, q);
                 for (int u = u0; u < u1; u++, m++) {
                     const int buf = m & 1;
-                    mbar_wait(&red_full[buf], (m >> 1) & 1, P.ctrl, 0x30 + phase);
+                    mbar_wait<100>(&red_full[buf], (m >> 1) & 1, P.ctrl, 0x30 + phase);
                     const float *rb = red + buf * (CW * 16 * NCOL);
                     if (phase == 1) {
                         // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
@@ -625,18 +654,19 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                             dst[P.ff] = __float2half_rn(av - __half2float(h));
                         }
                     } else {
-                        // weighted partial row of this (pair, tile); summed over slots in phase 3
-                        const int tk = lane >> 4, r = lane & 15;
-                        if (tk < U.n_tok) {
+                        // weighted partial rows of this (pair, tile); summed over slots in phase 3.
+                        // lane = row of the unit; warps w with w & 1 == row tile hold its K-split partials
+                        const int rt = lane >> 4, r = lane & 15;
+                        for (int tk = 0; tk < U.n_tok; tk++) {
                             float yv = 0.f;
 #pragma unroll
-                            for (int w = 0; w < CW; w++) {
-                                yv += rb[(w * 16 + r) * NCOL + 2 * tk];
-                                yv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
+                            for (int w = 0; w < CW / 2; w++) {
+                                yv += rb[((2 * w + rt) * 16 + r) * NCOL + 2 * tk];
+                                yv += rb[((2 * w + rt) * 16 + r) * NCOL + 2 * tk + 1];
                             }
                             const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
                             if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
-                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + tile * 16 + r, yv);
+                            __stcg(P.ypart + (size_t)U.pair[tk] * P.hidden + tile * DOWN_ROWS + lane, yv);
                         }
                     }
                     __syncwarp();
@@ -660,42 +690,66 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     STAMP(0);
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
     if (P.hidden == 128 * 24) {
-        // router row held in registers (all its loads in flight at once); hidden states staged as
-        // f32, as many tokens at a time as the (not yet used) weight ring + activation cache hold
-        constexpr int HB = 24;
+        // Work item = (expert, group of four tokens), spread over every warp of the grid.  The router row
+        // is held in registers half a row at a time (all loads of a half in flight at once); hidden states
+        // are staged as f32, as many tokens per round as the (not yet used) weight ring + activation cache
+        // hold.  Each of the 128 partial chains still runs over its 24 elements in order.
+        constexpr int HH = 12;
         const int H = P.hidden;
         float *xs32 = reinterpret_cast<float *>(ring);
-        const int xt_cap = max(1, (L.o_s - L.o_ring) / (H * 4));
-        for (int er = 0; er * G * CW < E; er++) {
-            const int e = blockIdx.x + G * (warp + CW * er);
-            const bool have = e < E;
-            float4 wv[HB];
-            if (have) {
-                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
+        const int xt_cap = max(4, (L.o_s - L.o_ring) / (H * 4) / 4 * 4);
+        float4 wv[HH];
+        bool preloaded = false;
+        {
+            // the first item's first half row is requested before the hidden states are staged
+            const int item = blockIdx.x + G * warp;
+            const int ngr = (min(xt_cap, P.t) + 3) / 4;
+            if (item < E * ngr) {
+                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)(item / ngr) * H) + lane;
 #pragma unroll
-                for (int j = 0; j < HB; j++) wv[j] = __ldg(wr + 32 * j);
+                for (int j = 0; j < HH; j++) wv[j] = __ldg(wr + 32 * j);
+                preloaded = true;
             }
-            for (int t0 = 0; t0 < P.t; t0 += xt_cap) {
-                const int nt = min(xt_cap, P.t - t0);
-                bar_sync(1, CW * 32);
-                for (int i = tid; i < nt * (H / 4); i += CW * 32)
-                    reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
-                bar_sync(1, CW * 32);
-                if (have) {
-                    for (int i = 0; i < nt; i++) {
-                        const float4 *xr = reinterpret_cast<const float4 *>(xs32 + i * H) + lane;
-                        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        }
+        for (int t0 = 0; t0 < P.t; t0 += xt_cap) {
+            const int nt = min(xt_cap, P.t - t0);
+            const int ngr = (nt + 3) / 4;
+            bar_sync(1, CW * 32);
+            for (int i = tid; i < nt * (H / 4); i += CW * 32)
+                reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
+            bar_sync(1, CW * 32);
+            for (int item = blockIdx.x + G * warp; item < E * ngr; item += G * CW) {
+                const int e = item / ngr, i0 = (item - e * ngr) * 4;
+                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
+                float a[4][4];
 #pragma unroll
-                        for (int j = 0; j < HB; j++) {
-                            const float4 xv = xr[32 * j];
-                            a0 = __fmaf_rn(xv.x, wv[j].x, a0);
-                            a1 = __fmaf_rn(xv.y, wv[j].y, a1);
-                            a2 = __fmaf_rn(xv.z, wv[j].z, a2);
-                            a3 = __fmaf_rn(xv.w, wv[j].w, a3);
-                        }
-                        const float v = lmoe_router_fold(a0, a1, a2, a3);
-                        if (lane == 0) P.logits[(size_t)(t0 + i) * E + e] = v;
+                for (int i = 0; i < 4; i++) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.f;
+#pragma unroll 1
+                for (int half = 0; half < 2; half++) {
+                    if (!(preloaded && half == 0)) {
+#pragma unroll
+                        for (int j = 0; j < HH; j++) wv[j] = __ldg(wr + 32 * (HH * half + j));
                     }
+                    preloaded = false;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        if (i0 + i < nt) {
+                            const float4 *xr = reinterpret_cast<const float4 *>(xs32 + (i0 + i) * H) + lane + 32 * HH * half;
+#pragma unroll
+                            for (int j = 0; j < HH; j++) {
+                                const float4 xv = xr[32 * j];
+                                a[i][0] = __fmaf_rn(xv.x, wv[j].x, a[i][0]);
+                                a[i][1] = __fmaf_rn(xv.y, wv[j].y, a[i][1]);
+                                a[i][2] = __fmaf_rn(xv.z, wv[j].z, a[i][2]);
+                                a[i][3] = __fmaf_rn(xv.w, wv[j].w, a[i][3]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float v = lmoe_router_fold(a[i][0], a[i][1], a[i][2], a[i][3]);
+                    if (lane == 0 && i0 + i < nt) P.logits[(size_t)(t0 + i0 + i) * E + e] = v;
                 }
             }
         }
@@ -935,9 +989,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 mbar_wait(&full[s], (n / NSTAGE) & 1, P.ctrl, 0x20 + phase);
                 const uint8_t *stage = ring + (size_t)s * L.stage_bytes;
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const bool colv = g < 2 * U.n_tok;
-                if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + g * L.xs, sh + g * L.ss, colv, acc);
-                else unit_q6k(stage, row6, nb6, warp, g, t4, xc + g * L.xs, sh + g * L.ss, colv, acc);
+                // MMA columns beyond the staged ones alias them: their results are never read
+                const int col = g & (NCOL - 1);
+#ifndef DEC_DBG_NOCOMPUTE
+                if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
+                else unit_q6k(stage, row6, nb6, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
+#else
+                acc[0] = stage[lane * 16];
+#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 // K-split partials -> shared memory, handed to the epilogue warp (two buffers in flight)
