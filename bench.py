@@ -37,6 +37,11 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm (rank 0 only) is meant to use
+# every host core, so the variable is reset before the OpenMP runtime of the CPU code starts.
+if os.environ.get("TORCHELASTIC_RUN_ID") is not None and os.environ.get("RANK", "0") == "0":
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+
 H, F, E, K = 3072, 1024, 256, 10
 SWEEP = (1, 2, 4, 8, 16)
 EXPERT_BYTES = 2 * F * (H // 256) * 144 + H * (F // 256) * 210  # 6 119 424
