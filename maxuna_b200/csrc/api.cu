@@ -311,13 +311,24 @@ extern "C" lmoe_status lmoe_layer_create(int64_t hidden, int64_t expert_ff, int6
                     shared_down->dtype == down->dtype,
                 "shared expert dtypes must match the routed experts'");
     }
+    uint32_t *sync = nullptr;
+    LMOE_CUDA(cudaMalloc(&sync, 256));
+    if (cudaMemset(sync, 0, 256) != cudaSuccess) {
+        cudaFree(sync);
+        return lmoe_fail(LMOE_ERR_CUDA, "could not clear the layer's synchronisation words");
+    }
     *out = new (std::nothrow) lmoe_layer{hidden, expert_ff, n_expert, top_k, scale, norm, router, bias, gate, up, down,
-                                         shared_gate, shared_up, shared_down};
+                                         shared_gate, shared_up, shared_down, sync};
+    if (*out == nullptr) cudaFree(sync);
     REQUIRE(*out != nullptr, "out of host memory");
     return LMOE_OK;
 }
 
-extern "C" void lmoe_layer_destroy(lmoe_layer *layer) { delete layer; }
+extern "C" void lmoe_layer_destroy(lmoe_layer *layer) {
+    if (!layer) return;
+    cudaFree(layer->sync);
+    delete layer;
+}
 
 extern "C" lmoe_status lmoe_check_device_flag(void *workspace, void *stream) {
     lmoe_clear_error();

@@ -51,6 +51,9 @@ struct lmoe_layer {
     int32_t norm;
     const float *router, *bias;
     const lmoe_expert_stack *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+    // device words the fused decode kernel synchronises its CTAs through; zero between launches,
+    // so one decode call at a time per layer
+    uint32_t *sync;
 };
 
 static inline int lmoe_type_size(int32_t dtype) {

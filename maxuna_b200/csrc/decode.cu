@@ -58,7 +58,9 @@ struct DecodeParams {
     int t, hidden, ff, n_expert, top_k;
     float scale;
     int norm, has_shared;
-    uint32_t *ctrl;   // [0..3] flag, [4] grid barrier, [5] exit count, [8192..] optional timing stamps
+    uint32_t *ctrl;   // workspace: [0..3] device flag (zeroed by the launch with first_launch set), [8192..] optional timing stamps
+    uint32_t *sync;   // owned by the layer, zero between launches: [0] grid barrier, [1] exit count
+    int first_launch;
     float *logits;    // [t][n_expert]
     uint32_t *ids_ws; // [t][top_k] routing decision, written by the CTA that ranked the token
     float *w_ws;
@@ -167,7 +169,7 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t *p) {
 
 // Grid-wide barrier among the consumer threads of all CTAs (thread 0 of each
 // CTA arrives).  `target` = arrivals expected so far in this launch.
-__device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, int tid, int first_id = 1,
+__device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t *sync, uint32_t target, int tid, int first_id = 1,
                                              int first_count = CW * 32) {
     __threadfence();
     bar_sync(first_id, first_count); // phases 1/2: the epilogue warp arrives here once its stores are fenced
@@ -175,9 +177,9 @@ __device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t target, in
         __threadfence();
     }
     if (tid == 0) {
-        atomicAdd(&ctrl[4], 1u);
+        atomicAdd(&sync[0], 1u);
         uint32_t i = 0;
-        while (ld_acquire(&ctrl[4]) < target) {
+        while (ld_acquire(&sync[0]) < target) {
             if (++i > SPIN_LIMIT) {
                 if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
                     ctrl[1] = 0x100u + target;
@@ -441,7 +443,7 @@ __device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, 
                    sc_pair_half2(scG + 2 * t + 8), s0, s1);
     }
     float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
+#pragma unroll
     for (int n = 0; n < 2; n++) {
         // the eight scales of this half, biased to unsigned so a byte permute turns them into floats
         const uint32_t swg0 = lds32<MIS>(bg, 192 + 8 * n) ^ 0x80808080u, swg1 = lds32<MIS>(bg, 196 + 8 * n) ^ 0x80808080u;
@@ -688,6 +690,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     const int g = lane >> 2, t4 = lane & 3;
 
     STAMP(0);
+    if (P.first_launch && blockIdx.x == 0 && tid < 4) P.ctrl[tid] = 0u; // a fresh device flag for this call
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
     if (P.hidden == 128 * 24) {
         // Work item = (expert, group of four tokens), spread over every warp of the grid.  The router row
@@ -788,7 +791,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     for (int e = tid; e < E; e += CW * 32) bias_s[e] = P.bias ? __ldg(P.bias + e) : 0.0f;
     bar_sync(3, RING_THREADS); // the weight ring is free from here on: the producer may start
     STAMP(1);
-    grid_barrier(P.ctrl, (uint32_t)G, tid);
+    grid_barrier(P.ctrl, P.sync, (uint32_t)G, tid);
     STAMP(2);
 
     // ---- phase 0b: selection.  Token i is handled by CTA i: each of the four warps ranks a quarter of
@@ -880,7 +883,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         }
     }
     STAMP(8);
-    grid_barrier(P.ctrl, (uint32_t)(2 * G), tid);
+    grid_barrier(P.ctrl, P.sync, (uint32_t)(2 * G), tid);
     for (int i = tid; i < P.t * K; i += CW * 32) {
         const uint32_t id = __ldcg(P.ids_ws + i);
         const float wv = __ldcg(P.w_ws + i);
@@ -1018,7 +1021,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             }
         }
         STAMP(phase == 1 ? 4 : 6);
-        grid_barrier(P.ctrl, (uint32_t)((phase + 2) * G), tid, 4, EPI_THREADS);
+        grid_barrier(P.ctrl, P.sync, (uint32_t)((phase + 2) * G), tid, 4, EPI_THREADS);
         STAMP(phase == 1 ? 5 : 7);
     }
 
@@ -1046,10 +1049,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     bar_sync(1, CW * 32);
     if (tid == 0) {
         __threadfence();
-        const uint32_t old = atomicAdd(&P.ctrl[5], 1u);
+        const uint32_t old = atomicAdd(&P.sync[1], 1u);
         if (old == (uint32_t)(G - 1)) {
-            P.ctrl[4] = 0u;
-            P.ctrl[5] = 0u;
+            P.sync[0] = 0u;
+            P.sync[1] = 0u;
             __threadfence();
         }
     }
@@ -1070,7 +1073,7 @@ size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k
 int decode_max_tokens() { return DEC_MAX_T; }
 
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
-                              float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+                              float *w_out, void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream) {
     const int H = (int)Ly->hidden, F = (int)Ly->expert_ff, E = (int)Ly->n_expert, K = (int)Ly->top_k;
     if (Ly->gate->dtype != LMOE_Q4_K || Ly->down->dtype != LMOE_Q6_K)
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the fused decode kernel is built for Q4_K gate/up and Q6_K down stacks");
@@ -1115,6 +1118,8 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
     P.scale = Ly->scale; P.norm = Ly->norm;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     P.ctrl = reinterpret_cast<uint32_t *>(ws);
+    P.sync = Ly->sync;
+    P.first_launch = first_launch;
     size_t o = 65536;
     P.logits = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * E * 4, 256);
     P.ids_ws = reinterpret_cast<uint32_t *>(ws + o); o += lmoe_align_up((size_t)t * K * 4, 256);

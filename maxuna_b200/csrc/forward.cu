@@ -5,7 +5,7 @@
 size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k);
 int decode_max_tokens();
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
-                              float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+                              float *w_out, void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream);
 // prefill.cu
 size_t prefill_workspace_bytes(const lmoe_layer *Ly, int64_t t);
 lmoe_status launch_moe_prefill(const lmoe_layer *Ly, const float *x, int64_t t, float *out, uint32_t *ids_out,
@@ -46,7 +46,7 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
         st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
                                ids_out ? ids_out + t0 * layer->top_k : nullptr,
                                weights_out ? weights_out + t0 * layer->top_k : nullptr, workspace, workspace_bytes,
-                               (cudaStream_t)stream);
+                               t0 == 0, (cudaStream_t)stream);
         if (st) return st;
     }
     return LMOE_OK;
