@@ -78,6 +78,11 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)),
                  "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
 }
+// Ask L2 to fetch a contiguous global range (16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0 || bytes == 0) return; // a hint only: skipped when not aligned
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
 }
@@ -644,6 +649,17 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
                 const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
+                {
+                    // the quantized rows of this CTA's next tile are two contiguous ranges: have L2 fetch them now
+                    const int nt = tile + gridDim.x;
+                    if (nt < n_tiles) {
+                        const int ne = P.tiles[8 * nt], nm0 = P.tiles[8 * nt + 3];
+                        const int nrows = min(MM_M, P.n_out - nm0);
+                        const size_t off = (size_t)ne * P.expert_bytes + (size_t)nm0 * row_bytes;
+                        bulk_prefetch_l2(P.wg + off, (uint32_t)(nrows * row_bytes) & ~15u);
+                        bulk_prefetch_l2(P.wu + off, (uint32_t)(nrows * row_bytes) & ~15u);
+                    }
+                }
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % GU_NS;
                     ok = mb_wait(&b_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 4);
@@ -747,78 +763,155 @@ struct DnParams {
     uint32_t *flag;
 };
 
-// aligned-or-not 32-bit load from a 2-byte aligned global address (uniform branch per super-block)
-template <bool MIS>
-__device__ __forceinline__ uint32_t ldg32_a2(const uint8_t *p) {
-    if (MIS) {
-        const uint32_t lo = __ldg(reinterpret_cast<const uint32_t *>(p - 2)), hi = __ldg(reinterpret_cast<const uint32_t *>(p + 2));
-        return __byte_perm(lo, hi, 0x5432);
-    }
-    return __ldg(reinterpret_cast<const uint32_t *>(p));
+// Predicated global loads that leave 0 in the register when off (no select after the load, so nothing
+// waits for the data until it is really used).
+__device__ __forceinline__ uint32_t ldg32_if(const void *p, bool on) {
+    uint32_t v = 0u;
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q ld.global.nc.u32 %0, [%1];\n\t}" : "+r"(v) : "l"(p), "r"((uint32_t)on));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg16_if(const void *p, bool on) {
+    uint32_t v = 0u;
+    asm volatile("{\n\t.reg .pred q;\n\t.reg .b16 t;\n\tsetp.ne.u32 q, %2, 0;\n\tmov.b16 t, 0;\n\t@q ld.global.nc.u16 t, [%1];\n\tcvt.u32.u16 %0, t;\n\t}"
+                 : "=r"(v) : "l"(p), "r"((uint32_t)on));
+    return v;
 }
 
+// Down-projection dequant, one (super-block b, 128-weight half n) of the tile's 256 rows at a time:
+//   load   eight lanes per row read aligned 32-bit words side by side (coalesced), nothing else;
+//   stage  the words go to a shared-memory row per weight row (32 words, 16-byte chunks XOR-swizzled);
+//   row    one thread per weight row turns its 128 weights into f16 (each sub-block scale serves 16).
+// Super-blocks are 210 bytes, so odd ones start 2 bytes off a word boundary (MIS): their words are loaded
+// from the aligned addresses around them and re-aligned by byte permutes in the row step.
+// Word slots of a staged row:  aligned: 0-7 ql, 8-15 ql+32, 16-23 qh, 24-25 scales, 26 d (low half)
+//                              MIS:     0-16 ql window, 17-25 qh window, 26-28 scales window, 29 d (high half)
+constexpr int DN_RAWP = 128;
+constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP;
+
 struct DnRegs {
-    uint32_t qa[8], qb[8], qh[8], sx[8];
+    uint32_t a[8], b[8], h[8], x[8];
 };
 
-// loads of one (super-block b, half n) for this thread's eight rows
 template <bool MIS>
 __device__ __forceinline__ void dn_load(DnRegs &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int n, int w,
                                         int row0) {
+#ifdef DN_DBG_NOLOAD
+#pragma unroll
+    for (int i = 0; i < 8; i++) { R.a[i] = 0x12345678u + i; R.b[i] = 0x9abcdef0u + w; R.h[i] = 0x55aa55aau; R.x[i] = 0x3c003c00u; }
+    return;
+#endif
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int row = row0 + 32 * i;
-        if (row < rows_valid) {
-            const uint8_t *blk = tile_w + (size_t)row * row_bytes + (size_t)b * Q6K_BYTES;
-            R.qa[i] = ldg32_a2<MIS>(blk + 64 * n + 4 * w);
-            R.qb[i] = ldg32_a2<MIS>(blk + 64 * n + 32 + 4 * w);
-            R.qh[i] = ldg32_a2<MIS>(blk + 128 + 32 * n + 4 * w);
-            // lanes 0,1 of the group fetch the half's eight scales, lane 2 the block scale d
-            R.sx[i] = w < 2 ? ldg32_a2<MIS>(blk + 192 + 8 * n + 4 * w)
-                            : (w == 2 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t *>(blk + 208)) : 0u);
+        const bool on = row < rows_valid;
+        const uint8_t *blk = tile_w + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES - (MIS ? 2 : 0);
+        R.a[i] = ldg32_if(blk + 64 * n + 4 * w, on);
+        R.b[i] = ldg32_if(blk + 64 * n + 32 + 4 * w, on);
+        R.h[i] = ldg32_if(blk + 128 + 32 * n + 4 * w, on);
+        if (MIS) {
+            // lane 0: tail of the ql window, 1: tail of the qh window, 2-4: scales window, 5: word holding d
+            const int off = w == 0 ? 64 * n + 64 : w == 1 ? 128 + 32 * n + 32 : w < 5 ? 192 + 8 * n + 4 * (w - 2) : 208;
+            R.x[i] = ldg32_if(blk + off, on && w < 6);
         } else {
-            R.qa[i] = R.qb[i] = R.qh[i] = R.sx[i] = 0u;
+            // lanes 0, 1: the eight scales of the half, lane 2: d
+            if (w == 2) R.x[i] = ldg16_if(blk + 208, on);
+            else R.x[i] = ldg32_if(blk + 192 + 8 * n + 4 * (w & 1), on && w < 2);
         }
     }
 }
 
-// 16 weights per row (4 l-positions x 4 groups) -> two k-stages of the A tile
-__device__ __forceinline__ void dn_dequant(const DnRegs &R, uint8_t *st_even, uint8_t *st_odd, int w, int row0, int lane) {
-    const int gb = lane & ~7;
-    const __half2 zero = __float2half2_rn(0.f);
+__device__ __forceinline__ uint32_t dn_slot_off(int row, int slot) {
+    return (uint32_t)(row * DN_RAWP + ((((slot >> 2) ^ (row & 7))) << 4) + ((slot & 3) << 2));
+}
+
+template <bool MIS>
+__device__ __forceinline__ void dn_stage(const DnRegs &R, uint8_t *raw, int w, int row0) {
+    const int xslot = MIS ? (w == 0 ? 16 : w == 1 ? 25 : 24 + w) : 24 + w;
+    const bool xon = MIS ? w < 6 : w < 3;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int row = row0 + 32 * i;
-        const uint32_t scw0 = __shfl_sync(0xffffffffu, R.sx[i], gb), scw1 = __shfl_sync(0xffffffffu, R.sx[i], gb + 1);
-        const float d = lmoe_h2f((uint16_t)__shfl_sync(0xffffffffu, R.sx[i], gb + 2));
-        const uint32_t qa = R.qa[i], qb = R.qb[i], hh = R.qh[i];
-        uint8_t *base_e = st_even + (row >> 7) * A_STAGE_BYTES, *base_o = st_odd + (row >> 7) * A_STAGE_BYTES;
-        const int r = row & 127;
+        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, w)) = R.a[i];
+        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, 8 + w)) = R.b[i];
+        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, (MIS ? 17 : 16) + w)) = R.h[i];
+        if (xon) *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, xslot)) = R.x[i];
+    }
+}
+
+// One thread = one weight row: its 128 weights of the half (4 groups x 32 l) -> sixteen 16-byte chunks of
+// two consecutive k-stages (groups 0,1 -> the even stage, groups 2,3 -> the odd one).
+template <bool MIS>
+__device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_even, uint8_t *st_odd, int row) {
+    uint32_t W[32];
 #pragma unroll
-        for (int gi = 0; gi < 4; gi++) {
-            const uint32_t scw = (gi & 2) ? scw1 : scw0;
-            // scale index inside the word: 2*(gi&1) + (l / 16), l / 16 = w >> 2
-            const int sb = (int)(int8_t)((scw >> (8 * (2 * (gi & 1) + (w >> 2)))) & 0xff);
-            const bool hi_nib = gi & 2;
-            const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
-            const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u;
-            const __half2 s = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
-            const uint32_t q = (gi & 1) ? qb : qa;
-            const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
-            const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
-            const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
-            const uint2 o = make_uint2(h2_sub_fma(v02, off, s, zero), h2_sub_fma(v13, off, s, zero));
-            uint8_t *dst = (hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + (w >> 1)) + 8 * (w & 1);
-            *reinterpret_cast<uint2 *>(dst) = o;
+    for (int c = 0; c < (MIS ? 8 : 7); c++) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(raw + row * DN_RAWP + ((c ^ (row & 7)) << 4));
+        W[4 * c] = v.x; W[4 * c + 1] = v.y; W[4 * c + 2] = v.z; W[4 * c + 3] = v.w;
+    }
+    uint32_t QA[8], QB[8], QH[8], S0, S1, dbits;
+    if (MIS) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            QA[j] = __byte_perm(W[j], W[j + 1], 0x5432);
+            QB[j] = __byte_perm(W[8 + j], W[9 + j], 0x5432);
+            QH[j] = __byte_perm(W[17 + j], W[18 + j], 0x5432);
+        }
+        S0 = __byte_perm(W[26], W[27], 0x5432);
+        S1 = __byte_perm(W[27], W[28], 0x5432);
+        dbits = W[29] >> 16;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) { QA[j] = W[j]; QB[j] = W[8 + j]; QH[j] = W[16 + j]; }
+        S0 = W[24]; S1 = W[25];
+        dbits = W[26] & 0xffffu;
+    }
+    const float d = lmoe_h2f((uint16_t)dbits);
+    uint8_t *base_e = st_even + (row >> 7) * A_STAGE_BYTES, *base_o = st_odd + (row >> 7) * A_STAGE_BYTES;
+    const int r = row & 127;
+#pragma unroll
+    for (int gi = 0; gi < 4; gi++) {
+        const bool hi_nib = gi & 2;
+        const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
+        const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u;
+#pragma unroll
+        for (int lh = 0; lh < 2; lh++) {
+            // scale 2*gi + lh of this half
+            const uint32_t scw = (2 * gi + lh) < 4 ? S0 : S1;
+            const int sb = (int)(int8_t)((scw >> (8 * ((2 * gi + lh) & 3))) & 0xff);
+            const __half2 sc = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    const int j = 4 * lh + 2 * m + jj;
+                    const uint32_t q = (gi & 1) ? QB[j] : QA[j], hh = QH[j];
+                    const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
+                    const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
+                    const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
+                    const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
+                    const __half2 d13 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v13), *reinterpret_cast<const __half2 *>(&off)), sc);
+                    o[2 * jj] = *reinterpret_cast<const uint32_t *>(&d02);
+                    o[2 * jj + 1] = *reinterpret_cast<const uint32_t *>(&d13);
+                }
+                *reinterpret_cast<uint4 *>((hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + 2 * lh + m)) =
+                    make_uint4(o[0], o[1], o[2], o[3]);
+            }
         }
     }
 }
 
+#ifdef MM_DBG_STAMP_DN
+#define DSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
+#else
+#define DSTAMP(role, g, i) do { } while (0)
+#endif
 __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_constant__ DnParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *a_st = smem, *b_st = smem + DN_NSA * GU_A_STAGE;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(b_st + DN_NSB * B_STAGE_BYTES);
+    uint8_t *raw = b_st + DN_NSB * B_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + DN_RAW_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 10, *acc_full = bars + 12, *acc_empty = bars + 13;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
 
@@ -854,39 +947,44 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
         const int w = tid & 7, row0 = tid >> 3; // this thread: l = 4w..4w+3 of rows row0, row0+32, ...
         uint32_t g = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        // (after a wait timed out the loops still run to their end, without waiting: every warp must
+        // keep meeting the others at the staging barriers)
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
             const int rows_valid = min(2 * MM_M, P.n_out - m0);
             const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
             const bool mis0 = (reinterpret_cast<uintptr_t>(tw) & 2) != 0; // parity of even blocks (row_bytes % 4 == 0 when n_blk is even)
-            DnRegs RA, RB;
-            if (mis0) dn_load<true>(RA, tw, row_bytes, rows_valid, 0, 0, w, row0);
-            else dn_load<false>(RA, tw, row_bytes, rows_valid, 0, 0, w, row0);
-            for (int b = 0; b < n_blk && ok; b++) {
+            DnRegs R;
+            if (mis0) dn_load<true>(R, tw, row_bytes, rows_valid, 0, 0, w, row0);
+            else dn_load<false>(R, tw, row_bytes, rows_valid, 0, 0, w, row0);
+            for (int it = 0; it < 2 * n_blk; it++, g += 2) {
+                const int b = it >> 1;
                 const bool mis = mis0 != ((b & 1) != 0);
-#pragma unroll
-                for (int n = 0; n < 2; n++, g += 2) {
-                    // prefetch the next half while this one is converted
-                    DnRegs &cur = n ? RB : RA;
-                    DnRegs &nxt = n ? RA : RB;
-                    const int nb = n ? b + 1 : b, nn = n ? 0 : 1;
-                    if (nb < n_blk) {
-                        const bool nmis = mis0 != ((nb & 1) != 0);
-                        if (nmis) dn_load<true>(nxt, tw, row_bytes, rows_valid, nb, nn, w, row0);
-                        else dn_load<false>(nxt, tw, row_bytes, rows_valid, nb, nn, w, row0);
-                    }
-                    const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
-                    ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3) &&
-                         mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
-                    dn_dequant(cur, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, w, row0, lane);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mb_arrive(&a_full[s0]);
-                        mb_arrive(&a_full[s1]);
-                    }
+                if (tid == 0) DSTAMP(0, g >> 1, 0);
+                asm volatile("bar.sync 1, 256;" ::: "memory"); // the staged rows of the previous half are consumed
+                if (mis) dn_stage<true>(R, raw, w, row0);
+                else dn_stage<false>(R, raw, w, row0);
+                // the next half's words are requested now and only touched after this half is converted
+                if (it + 1 < 2 * n_blk) {
+                    const int nb = (it + 1) >> 1, nn = (it + 1) & 1;
+                    if (mis0 != ((nb & 1) != 0)) dn_load<true>(R, tw, row_bytes, rows_valid, nb, nn, w, row0);
+                    else dn_load<false>(R, tw, row_bytes, rows_valid, nb, nn, w, row0);
                 }
-                (void)mis;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (tid == 0) DSTAMP(0, g >> 1, 1);
+                const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
+                ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3) &&
+                     mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
+                if (tid == 0) DSTAMP(0, g >> 1, 2);
+                if (mis) dn_dequant_row<true>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, tid);
+                else dn_dequant_row<false>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, tid);
+                if (tid == 0) DSTAMP(0, g >> 1, 3);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mb_arrive(&a_full[s0]);
+                    mb_arrive(&a_full[s1]);
+                }
             }
         }
     } else if (warp == 8) {
@@ -897,6 +995,16 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
                 const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
+                {
+                    // the quantized rows of this CTA's next tile are one contiguous range: have L2 fetch it
+                    // now, so the dequant warps' small loads find it there
+                    const int nt = tile + gridDim.x;
+                    if (nt < n_tiles) {
+                        const int ne = P.tiles[8 * nt], nm0 = P.tiles[8 * nt + 3];
+                        const int nrows = min(2 * MM_M, P.n_out - nm0);
+                        bulk_prefetch_l2(P.w + (size_t)ne * P.expert_bytes + (size_t)nm0 * row_bytes, (uint32_t)(nrows * row_bytes) & ~15u);
+                    }
+                }
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % DN_NSB;
                     ok = mb_wait(&b_empty[s], ((g / DN_NSB) & 1) ^ 1, P.flag, 4);
@@ -918,7 +1026,11 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % DN_NSA, sb = g % DN_NSB;
-                    ok = mb_wait(&a_full[s], (g / DN_NSA) & 1, P.flag, 6) && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
+                    DSTAMP(1, g, 0);
+                    ok = mb_wait(&a_full[s], (g / DN_NSA) & 1, P.flag, 6);
+                    DSTAMP(1, g, 1);
+                    ok = ok && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
+                    DSTAMP(1, g, 2);
                     tc_fence_after();
                     const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
                     const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
@@ -930,6 +1042,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                     }
                     tc_commit(&a_empty[s]);
                     tc_commit(&b_empty[sb]);
+                    DSTAMP(1, g, 3);
                 }
                 tc_commit(acc_full);
             }
@@ -1099,7 +1212,7 @@ lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const 
     P.w = down->blocks(); P.expert_bytes = down->expert_bytes(); P.n_out = (int)down->n_out; P.k = (int)down->k;
     P.xt = static_cast<const uint8_t *>(xt); P.ids_map = ids_map; P.map_stride = (int)map_stride;
     P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.flag = flag;
-    const int smem = DN_NSA * GU_A_STAGE + DN_NSB * B_STAGE_BYTES + 256 + 1024;
+    const int smem = DN_NSA * GU_A_STAGE + DN_NSB * B_STAGE_BYTES + DN_RAW_BYTES + 256 + 1024;
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));
