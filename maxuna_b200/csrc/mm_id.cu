@@ -195,20 +195,24 @@ __device__ __forceinline__ void dequant_q6k_row32(const uint8_t *blk, int js, in
 }
 
 // ---- tile list -----------------------------------------------------------------------
-// tiles[i] = {expert, first list index, valid rows, first weight row, row-tile slot}; m tiles vary fastest so
+// tiles[i] = {expert, first list index, valid rows, first weight row, row-tile slot, first sorted row};
+// m tiles vary fastest so
 // CTAs running side by side share the same activation rows in L2.
 __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__restrict__ tpe, int n_expert, int n_out,
                                                           int32_t *__restrict__ tiles, int32_t *__restrict__ n_tiles,
                                                           int max_tiles, int m_step) {
-    __shared__ int pre[513];
+    __shared__ int pre[513], rpre[513];
     const int m_tiles = (n_out + m_step - 1) / m_step;
     const int e = threadIdx.x;
     const int cnt = e < n_expert ? (int)((tpe[e] + MM_N - 1) / MM_N) * m_tiles : 0;
     pre[e + 1] = cnt;
-    if (e == 0) pre[0] = 0;
+    rpre[e + 1] = e < n_expert ? (int)tpe[e] : 0;
+    if (e == 0) pre[0] = rpre[0] = 0;
     __syncthreads();
     if (e == 0)
         for (int i = 1; i <= 512; i++) pre[i] += pre[i - 1];
+    if (e == 32)
+        for (int i = 1; i <= 512; i++) rpre[i] += rpre[i - 1];
     __syncthreads();
     if (e < n_expert) {
         int o = pre[e];
@@ -221,6 +225,7 @@ __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__rest
                 tiles[8 * o + 2] = min(MM_N, rows - n0);
                 tiles[8 * o + 3] = m * m_step;
                 tiles[8 * o + 4] = pre[e] / m_tiles + n0 / MM_N;
+                tiles[8 * o + 5] = rpre[e] + n0; // first row of the tile in expert-sorted row order
             }
     }
     if (e == 0) *n_tiles = min(pre[512], max_tiles);
@@ -239,28 +244,41 @@ __device__ __forceinline__ size_t tiled_off(int slot, int k_stages, int ks, int 
 __global__ void __launch_bounds__(256) gather_tiles_kernel(const float *__restrict__ x, int x_per_row, int top_k, int k,
                                                            const uint32_t *__restrict__ tpe, const int32_t *__restrict__ ids_map,
                                                            int map_stride, int n_expert, uint8_t *__restrict__ xt,
-                                                           int32_t *__restrict__ pos) {
-    __shared__ int warp_sum[8];
-    __shared__ int slot0_s;
+                                                           int32_t *__restrict__ pos, int32_t *__restrict__ spos,
+                                                           int32_t *__restrict__ sfid) {
+    __shared__ int warp_sum[8], warp_rows[8];
+    __shared__ int slot0_s, row0_s;
     const int e = blockIdx.x;
-    // slot of this expert's first row tile = number of row tiles of all earlier experts
-    int part = 0;
-    for (int i = threadIdx.x; i < e; i += 256) part += (int)((tpe[i] + MM_N - 1) / MM_N);
-    for (int o = 16; o; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = part;
+    // slot of this expert's first row tile = number of row tiles of all earlier experts; likewise its
+    // first row in expert-sorted order = number of rows of all earlier experts
+    int part = 0, rpart = 0;
+    for (int i = threadIdx.x; i < e; i += 256) {
+        part += (int)((tpe[i] + MM_N - 1) / MM_N);
+        rpart += (int)tpe[i];
+    }
+    for (int o = 16; o; o >>= 1) {
+        part += __shfl_xor_sync(0xffffffffu, part, o);
+        rpart += __shfl_xor_sync(0xffffffffu, rpart, o);
+    }
+    if ((threadIdx.x & 31) == 0) { warp_sum[threadIdx.x >> 5] = part; warp_rows[threadIdx.x >> 5] = rpart; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int t = 0;
-        for (int i = 0; i < 8; i++) t += warp_sum[i];
+        int t = 0, r = 0;
+        for (int i = 0; i < 8; i++) { t += warp_sum[i]; r += warp_rows[i]; }
         slot0_s = t;
+        row0_s = r;
     }
     __syncthreads();
-    const int slot0 = slot0_s, rows = (int)tpe[e], k_stages = k / MM_K, chunks = k / 8;
+    const int slot0 = slot0_s, srow0 = row0_s, rows = (int)tpe[e], k_stages = k / MM_K, chunks = k / 8;
     for (int i = blockIdx.y; i < rows; i += gridDim.y) {
         const int fid = ids_map[(size_t)e * map_stride + i];
         const float *src = x + (size_t)(x_per_row == 1 ? fid / top_k : fid) * k;
         const int slot = slot0 + i / MM_N, rr = i % MM_N;
-        if (pos && threadIdx.x == 0) pos[fid] = slot * MM_N + rr;
+        if (threadIdx.x == 0) {
+            if (pos) pos[fid] = slot * MM_N + rr;
+            if (spos) spos[fid] = srow0 + i;
+            if (sfid) sfid[srow0 + i] = fid;
+        }
         for (int ci = threadIdx.x; ci < chunks; ci += 256) {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci);
             const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci + 1);
@@ -478,15 +496,27 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
             const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
             const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
             const uint32_t buf = it & 1;
+            // destination rows and their scales are fetched while the tile is still being multiplied
+            int fids[MM_N / 32];
+            float scs[MM_N / 32];
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) {
+                const int my = 32 * c + lane;
+                fids[c] = my < nv ? list[my] : 0;
+            }
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) scs[c] = (P.row_scale && 32 * c + lane < nv) ? P.row_scale[fids[c]] : 1.0f;
             ok = mb_wait(&acc_full[buf], (it >> 1) & 1, P.flag, 8);
             tc_fence_after();
             const bool mvalid = m0 + m < P.n_out;
-            for (int cb = 0; cb < nv; cb += 32) {
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) {
+                const int cb = 32 * c;
+                if (cb >= nv) break;
                 uint32_t v[32];
                 tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * 256 + cb, v);
-                const int my = cb + lane;
-                const int myfid = my < nv ? list[my] : 0;
-                const float mysc = (P.row_scale && my < nv) ? P.row_scale[myfid] : 1.0f;
+                const int myfid = fids[c];
+                const float mysc = scs[c];
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int fid = __shfl_sync(0xffffffffu, myfid, j);
@@ -532,6 +562,7 @@ struct GuParams {
     int map_stride;
     const int32_t *tiles, *n_tiles;
     float *act; // [rows, n_out] f32
+    int sorted; // rows of `act` in expert-sorted order (tile table entry 5) instead of by flat id
     uint32_t *flag;
 };
 
@@ -712,21 +743,41 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
             const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
             const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            // destination rows are fetched while the tile is still being multiplied
+            int fids[MM_N / 32];
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) {
+                const int my = 32 * c + lane;
+                fids[c] = my < nv ? list[my] : 0;
+            }
             ok = mb_wait(acc_full, it & 1, P.flag, 8);
             tc_fence_after();
             const bool mvalid = m0 + m < P.n_out;
-            for (int cb = 0; cb < nv; cb += 32) {
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) {
+                const int cb = 32 * c;
+                if (cb >= nv) break;
                 uint32_t vg[32], vu[32];
                 tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + cb, vg);
                 tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + 256 + cb, vu);
-                const int my = cb + lane;
-                const int myfid = my < nv ? list[my] : 0;
+                const int myfid = fids[c];
+                if (P.sorted) {
+                    // rows in expert-sorted order: consecutive tile columns are consecutive rows
+                    float *dst = P.act + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + m0 + m;
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int fid = __shfl_sync(0xffffffffu, myfid, j);
-                    const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
-                    const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
-                    if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
+                    for (int j = 0; j < 32; j++) {
+                        const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
+                        const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                        if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = a;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                        const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
+                        const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                        if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
+                    }
                 }
             }
             tc_fence_before();
@@ -747,7 +798,8 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 // words side by side; each lane turns its 4 l-positions of the four 32-weight groups into
 // f16 and writes 8-byte pieces of the swizzled A stages of TWO consecutive k-stages.
 //   warps 0-7 dequant    warp 8 B loader    warp 9 MMA issuer    warps 10-13 epilogue
-constexpr int DN_THREADS = 14 * 32;
+constexpr int DN_DQ_WARPS = 16;                       // dequant warps
+constexpr int DN_THREADS = (DN_DQ_WARPS + 6) * 32;    // + B loader, MMA issuer, four epilogue warps
 constexpr int DN_NSA = 4, DN_NSB = 2;
 
 struct DnParams {
@@ -760,6 +812,7 @@ struct DnParams {
     const int32_t *tiles, *n_tiles;
     const float *row_scale;
     float *out; // [rows, n_out]
+    int sorted; // rows of `out` in expert-sorted order, unscaled, instead of scaled rows by flat id
     uint32_t *flag;
 };
 
@@ -788,8 +841,9 @@ __device__ __forceinline__ uint32_t ldg16_if(const void *p, bool on) {
 constexpr int DN_RAWP = 128;
 constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP;
 
+constexpr int DN_RPT = 2 * MM_M / (DN_DQ_WARPS * 4); // rows per thread in the load / stage steps
 struct DnRegs {
-    uint32_t a[8], b[8], h[8], x[8];
+    uint32_t a[DN_RPT], b[DN_RPT], h[DN_RPT], x[DN_RPT];
 };
 
 template <bool MIS>
@@ -797,12 +851,12 @@ __device__ __forceinline__ void dn_load(DnRegs &R, const uint8_t *tile_w, int ro
                                         int row0) {
 #ifdef DN_DBG_NOLOAD
 #pragma unroll
-    for (int i = 0; i < 8; i++) { R.a[i] = 0x12345678u + i; R.b[i] = 0x9abcdef0u + w; R.h[i] = 0x55aa55aau; R.x[i] = 0x3c003c00u; }
+    for (int i = 0; i < DN_RPT; i++) { R.a[i] = 0x12345678u + i; R.b[i] = 0x9abcdef0u + w; R.h[i] = 0x55aa55aau; R.x[i] = 0x3c003c00u; }
     return;
 #endif
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int row = row0 + 32 * i;
+    for (int i = 0; i < DN_RPT; i++) {
+        const int row = row0 + DN_DQ_WARPS * 4 * i;
         const bool on = row < rows_valid;
         const uint8_t *blk = tile_w + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES - (MIS ? 2 : 0);
         R.a[i] = ldg32_if(blk + 64 * n + 4 * w, on);
@@ -829,8 +883,8 @@ __device__ __forceinline__ void dn_stage(const DnRegs &R, uint8_t *raw, int w, i
     const int xslot = MIS ? (w == 0 ? 16 : w == 1 ? 25 : 24 + w) : 24 + w;
     const bool xon = MIS ? w < 6 : w < 3;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int row = row0 + 32 * i;
+    for (int i = 0; i < DN_RPT; i++) {
+        const int row = row0 + DN_DQ_WARPS * 4 * i;
         *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, w)) = R.a[i];
         *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, 8 + w)) = R.b[i];
         *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, (MIS ? 17 : 16) + w)) = R.h[i];
@@ -838,32 +892,35 @@ __device__ __forceinline__ void dn_stage(const DnRegs &R, uint8_t *raw, int w, i
     }
 }
 
-// One thread = one weight row: its 128 weights of the half (4 groups x 32 l) -> sixteen 16-byte chunks of
-// two consecutive k-stages (groups 0,1 -> the even stage, groups 2,3 -> the odd one).
+// One thread = (weight row, half lh of the l range): 64 weights (4 groups x 16 l, one sub-block scale each)
+// -> eight 16-byte chunks of two consecutive k-stages (groups 0,1 -> the even stage, 2,3 -> the odd one).
 template <bool MIS>
-__device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_even, uint8_t *st_odd, int row) {
-    uint32_t W[32];
-#pragma unroll
-    for (int c = 0; c < (MIS ? 8 : 7); c++) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(raw + row * DN_RAWP + ((c ^ (row & 7)) << 4));
-        W[4 * c] = v.x; W[4 * c + 1] = v.y; W[4 * c + 2] = v.z; W[4 * c + 3] = v.w;
-    }
-    uint32_t QA[8], QB[8], QH[8], S0, S1, dbits;
+__device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_even, uint8_t *st_odd, int row, int lh) {
+    const uint8_t *rr = raw + row * DN_RAWP;
+    const int sw = row & 7;
+    auto chunk = [&](int c) { return *reinterpret_cast<const uint4 *>(rr + ((c ^ sw) << 4)); };
+    uint32_t QA[4], QB[4], QH[4], S0, S1, dbits;
     if (MIS) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            QA[j] = __byte_perm(W[j], W[j + 1], 0x5432);
-            QB[j] = __byte_perm(W[8 + j], W[9 + j], 0x5432);
-            QH[j] = __byte_perm(W[17 + j], W[18 + j], 0x5432);
-        }
-        S0 = __byte_perm(W[26], W[27], 0x5432);
-        S1 = __byte_perm(W[27], W[28], 0x5432);
-        dbits = W[29] >> 16;
+        // ql window words 4lh .. 4lh+4 and 8+4lh .. 12+4lh, qh window words 17+4lh .. 21+4lh
+        const uint4 a = chunk(lh), a2 = chunk(lh + 1), b = chunk(2 + lh), b2 = chunk(3 + lh);
+        QA[0] = __byte_perm(a.x, a.y, 0x5432); QA[1] = __byte_perm(a.y, a.z, 0x5432);
+        QA[2] = __byte_perm(a.z, a.w, 0x5432); QA[3] = __byte_perm(a.w, a2.x, 0x5432);
+        QB[0] = __byte_perm(b.x, b.y, 0x5432); QB[1] = __byte_perm(b.y, b.z, 0x5432);
+        QB[2] = __byte_perm(b.z, b.w, 0x5432); QB[3] = __byte_perm(b.w, b2.x, 0x5432);
+        const uint4 h = chunk(4 + lh), h2 = chunk(5 + lh), t6 = chunk(6), t7 = chunk(7);
+        // words 17+4lh..: lh = 0 -> h.y h.z h.w h2.x h2.y ; lh = 1 -> h.y .. of chunks 5, 6
+        QH[0] = __byte_perm(h.y, h.z, 0x5432); QH[1] = __byte_perm(h.z, h.w, 0x5432);
+        QH[2] = __byte_perm(h.w, h2.x, 0x5432); QH[3] = __byte_perm(h2.x, h2.y, 0x5432);
+        S0 = __byte_perm(t6.z, t6.w, 0x5432); // words 26, 27
+        S1 = __byte_perm(t6.w, t7.x, 0x5432); // words 27, 28
+        dbits = t7.y >> 16;                   // word 29
     } else {
-#pragma unroll
-        for (int j = 0; j < 8; j++) { QA[j] = W[j]; QB[j] = W[8 + j]; QH[j] = W[16 + j]; }
-        S0 = W[24]; S1 = W[25];
-        dbits = W[26] & 0xffffu;
+        const uint4 a = chunk(lh), b = chunk(2 + lh), h = chunk(4 + lh), t6 = chunk(6);
+        QA[0] = a.x; QA[1] = a.y; QA[2] = a.z; QA[3] = a.w;
+        QB[0] = b.x; QB[1] = b.y; QB[2] = b.z; QB[3] = b.w;
+        QH[0] = h.x; QH[1] = h.y; QH[2] = h.z; QH[3] = h.w;
+        S0 = t6.x; S1 = t6.y;
+        dbits = t6.z & 0xffffu;
     }
     const float d = lmoe_h2f((uint16_t)dbits);
     uint8_t *base_e = st_even + (row >> 7) * A_STAGE_BYTES, *base_o = st_odd + (row >> 7) * A_STAGE_BYTES;
@@ -873,30 +930,27 @@ __device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_e
         const bool hi_nib = gi & 2;
         const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
         const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u;
+        // scale 2*gi + lh of this half: byte (2*gi + lh) & 3 of word (2*gi + lh) >> 2
+        const uint32_t scw = gi < 2 ? S0 : S1;
+        const int sb = (int)(int8_t)((scw >> (8 * (2 * (gi & 1) + lh))) & 0xff);
+        const __half2 sc = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
 #pragma unroll
-        for (int lh = 0; lh < 2; lh++) {
-            // scale 2*gi + lh of this half
-            const uint32_t scw = (2 * gi + lh) < 4 ? S0 : S1;
-            const int sb = (int)(int8_t)((scw >> (8 * ((2 * gi + lh) & 3))) & 0xff);
-            const __half2 sc = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
+        for (int m = 0; m < 2; m++) {
+            uint32_t o[4];
 #pragma unroll
-            for (int m = 0; m < 2; m++) {
-                uint32_t o[4];
-#pragma unroll
-                for (int jj = 0; jj < 2; jj++) {
-                    const int j = 4 * lh + 2 * m + jj;
-                    const uint32_t q = (gi & 1) ? QB[j] : QA[j], hh = QH[j];
-                    const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
-                    const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
-                    const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
-                    const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
-                    const __half2 d13 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v13), *reinterpret_cast<const __half2 *>(&off)), sc);
-                    o[2 * jj] = *reinterpret_cast<const uint32_t *>(&d02);
-                    o[2 * jj + 1] = *reinterpret_cast<const uint32_t *>(&d13);
-                }
-                *reinterpret_cast<uint4 *>((hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + 2 * lh + m)) =
-                    make_uint4(o[0], o[1], o[2], o[3]);
+            for (int jj = 0; jj < 2; jj++) {
+                const int j = 2 * m + jj;
+                const uint32_t q = (gi & 1) ? QB[j] : QA[j], hh = QH[j];
+                const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
+                const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
+                const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
+                const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
+                const __half2 d13 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v13), *reinterpret_cast<const __half2 *>(&off)), sc);
+                o[2 * jj] = *reinterpret_cast<const uint32_t *>(&d02);
+                o[2 * jj + 1] = *reinterpret_cast<const uint32_t *>(&d13);
             }
+            *reinterpret_cast<uint4 *>((hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + 2 * lh + m)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
@@ -922,7 +976,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
 
     if (tid == 0) {
         for (int s = 0; s < DN_NSA; s++) {
-            mb_init(&a_full[s], 8);
+            mb_init(&a_full[s], DN_DQ_WARPS);
             mb_init(&a_empty[s], 1);
         }
         for (int s = 0; s < DN_NSB; s++) {
@@ -933,7 +987,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
         mb_init(acc_empty, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == DN_DQ_WARPS + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -942,9 +996,10 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 8) {
+    if (warp < DN_DQ_WARPS) {
         // ---------------- dequant ----------------
-        const int w = tid & 7, row0 = tid >> 3; // this thread: l = 4w..4w+3 of rows row0, row0+32, ...
+        const int w = tid & 7, row0 = tid >> 3; // load / stage steps: word w of rows row0, row0 + 64, ...
+        const int drow = tid & (2 * MM_M - 1), dlh = tid / (2 * MM_M); // convert step: (row, l half)
         uint32_t g = 0;
         bool ok = true;
         // (after a wait timed out the loops still run to their end, without waiting: every warp must
@@ -954,30 +1009,30 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             const int rows_valid = min(2 * MM_M, P.n_out - m0);
             const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
             const bool mis0 = (reinterpret_cast<uintptr_t>(tw) & 2) != 0; // parity of even blocks (row_bytes % 4 == 0 when n_blk is even)
-            DnRegs R;
-            if (mis0) dn_load<true>(R, tw, row_bytes, rows_valid, 0, 0, w, row0);
-            else dn_load<false>(R, tw, row_bytes, rows_valid, 0, 0, w, row0);
-            for (int it = 0; it < 2 * n_blk; it++, g += 2) {
+            // loads run two halves ahead of their use, in two register sets
+            DnRegs R0, R1;
+            auto load = [&](DnRegs &R, int it) {
+                if (it >= 2 * n_blk) return;
+                const int b = it >> 1, n = it & 1;
+                if (mis0 != ((b & 1) != 0)) dn_load<true>(R, tw, row_bytes, rows_valid, b, n, w, row0);
+                else dn_load<false>(R, tw, row_bytes, rows_valid, b, n, w, row0);
+            };
+            auto half = [&](DnRegs &R, int it) {
                 const int b = it >> 1;
                 const bool mis = mis0 != ((b & 1) != 0);
                 if (tid == 0) DSTAMP(0, g >> 1, 0);
-                asm volatile("bar.sync 1, 256;" ::: "memory"); // the staged rows of the previous half are consumed
+                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the staged rows of the previous half are consumed
                 if (mis) dn_stage<true>(R, raw, w, row0);
                 else dn_stage<false>(R, raw, w, row0);
-                // the next half's words are requested now and only touched after this half is converted
-                if (it + 1 < 2 * n_blk) {
-                    const int nb = (it + 1) >> 1, nn = (it + 1) & 1;
-                    if (mis0 != ((nb & 1) != 0)) dn_load<true>(R, tw, row_bytes, rows_valid, nb, nn, w, row0);
-                    else dn_load<false>(R, tw, row_bytes, rows_valid, nb, nn, w, row0);
-                }
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                load(R, it + 2);
+                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory");
                 if (tid == 0) DSTAMP(0, g >> 1, 1);
                 const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
                 ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3) &&
                      mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
                 if (tid == 0) DSTAMP(0, g >> 1, 2);
-                if (mis) dn_dequant_row<true>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, tid);
-                else dn_dequant_row<false>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, tid);
+                if (mis) dn_dequant_row<true>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
+                else dn_dequant_row<false>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
                 if (tid == 0) DSTAMP(0, g >> 1, 3);
                 fence_async_smem();
                 __syncwarp();
@@ -985,9 +1040,16 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                     mb_arrive(&a_full[s0]);
                     mb_arrive(&a_full[s1]);
                 }
+                g += 2;
+            };
+            load(R0, 0);
+            load(R1, 1);
+            for (int it = 0; it < 2 * n_blk; it += 2) {
+                half(R0, it);
+                half(R1, it + 1);
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == DN_DQ_WARPS) {
         // ---------------- B loader ----------------
         if (lane == 0) {
             uint32_t g = 0;
@@ -1013,7 +1075,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == DN_DQ_WARPS + 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t g = 0, it = 0;
@@ -1057,33 +1119,56 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
             const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
             const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            // destination rows and their scales are fetched while the tile is still being multiplied
+            int fids[MM_N / 32];
+            float scs[MM_N / 32];
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) {
+                const int my = 32 * c + lane;
+                fids[c] = my < nv ? list[my] : 0;
+            }
+#pragma unroll
+            for (int c = 0; c < MM_N / 32; c++) scs[c] = (P.row_scale && 32 * c + lane < nv) ? P.row_scale[fids[c]] : 1.0f;
+            if (q == 0 && lane == 0) DSTAMP(2, it, 0);
             ok = mb_wait(acc_full, it & 1, P.flag, 8);
             tc_fence_after();
+            if (q == 0 && lane == 0) DSTAMP(2, it, 1);
             for (int sub = 0; sub < 2; sub++) {
                 const int mrow = m0 + sub * MM_M + m;
                 const bool mvalid = mrow < P.n_out;
-                for (int cb = 0; cb < nv; cb += 32) {
+#pragma unroll
+                for (int c = 0; c < MM_N / 32; c++) {
+                    const int cb = 32 * c;
+                    if (cb >= nv) break;
                     uint32_t v[32];
                     tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + sub * 256 + cb, v);
-                    const int my = cb + lane;
-                    const int myfid = my < nv ? list[my] : 0;
-                    const float mysc = (P.row_scale && my < nv) ? P.row_scale[myfid] : 1.0f;
+                    const int myfid = fids[c];
+                    const float mysc = scs[c];
+                    if (P.sorted) {
+                        // rows in expert-sorted order, unscaled: consecutive tile columns are consecutive rows
+                        float *dst = P.out + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + mrow;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int fid = __shfl_sync(0xffffffffu, myfid, j);
-                        const float sc = __shfl_sync(0xffffffffu, mysc, j);
-                        if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + mrow] = __uint_as_float(v[j]) * sc;
+                        for (int j = 0; j < 32; j++)
+                            if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                            const float sc = __shfl_sync(0xffffffffu, mysc, j);
+                            if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + mrow] = __uint_as_float(v[j]) * sc;
+                        }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
+            if (q == 0 && lane == 0) DSTAMP(2, it, 2);
             if (lane == 0) mb_arrive(acc_empty);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (warp == DN_DQ_WARPS + 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
 } // namespace
@@ -1124,11 +1209,11 @@ size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k) {
 
 cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
                                 const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
-                                cudaStream_t s) {
+                                int32_t *spos, int32_t *sfid, cudaStream_t s) {
     // enough blocks per expert to cover the device even when one expert holds all the rows
     const int gy = n_expert >= 64 ? 16 : (n_expert >= 8 ? 128 : 1024);
     gather_tiles_kernel<<<dim3(n_expert, gy), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
-                                                           static_cast<uint8_t *>(xt), pos);
+                                                           static_cast<uint8_t *>(xt), pos, spos, sfid);
     return cudaGetLastError();
 }
 
@@ -1169,7 +1254,7 @@ lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint
 // gate and up of one expert block in one kernel, SwiGLU applied: act[rows, ff] (f32).
 lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
                              const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
-                             float *act, void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
+                             float *act, int sorted, void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
     if (gate->dtype != LMOE_Q4_K || up->dtype != LMOE_Q4_K)
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the fused gate/up kernel is built for Q4_K stacks");
     if (gate->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
@@ -1181,7 +1266,7 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     GuParams P;
     P.wg = gate->blocks(); P.wu = up->blocks(); P.expert_bytes = gate->expert_bytes();
     P.n_out = (int)gate->n_out; P.k = (int)gate->k; P.xt = static_cast<const uint8_t *>(xt);
-    P.ids_map = ids_map; P.map_stride = (int)map_stride; P.tiles = tiles; P.n_tiles = n_tiles; P.act = act; P.flag = flag;
+    P.ids_map = ids_map; P.map_stride = (int)map_stride; P.tiles = tiles; P.n_tiles = n_tiles; P.act = act; P.sorted = sorted; P.flag = flag;
     const int smem = GU_NS * (GU_A_STAGE + B_STAGE_BYTES) + 256 + 1024;
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;
@@ -1198,8 +1283,8 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
 
 // The down projection: 256 Q6_K weight rows per CTA, optional per-row scale in the epilogue.
 lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
-                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
-                           uint32_t *flag, cudaStream_t stream) {
+                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, int sorted,
+                           void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
     if (down->dtype != LMOE_Q6_K || (down->k / QK_K) % 2 != 0 || (down->n_out & 1))
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the 256-row down kernel needs a Q6_K stack with k %% 512 == 0 and even n_out");
     if (down->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
@@ -1211,7 +1296,7 @@ lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const 
     DnParams P;
     P.w = down->blocks(); P.expert_bytes = down->expert_bytes(); P.n_out = (int)down->n_out; P.k = (int)down->k;
     P.xt = static_cast<const uint8_t *>(xt); P.ids_map = ids_map; P.map_stride = (int)map_stride;
-    P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.flag = flag;
+    P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.sorted = sorted; P.flag = flag;
     const int smem = DN_NSA * GU_A_STAGE + DN_NSB * B_STAGE_BYTES + DN_RAW_BYTES + 256 + 1024;
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;

@@ -11,13 +11,13 @@ size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out);
 size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k);
 cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
                                 const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
-                                cudaStream_t s);
+                                int32_t *spos, int32_t *sfid, cudaStream_t s);
 lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
                              const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
-                             float *act, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
+                             float *act, int sorted, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
 lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
-                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
-                           uint32_t *flag, cudaStream_t stream);
+                           int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, int sorted,
+                           void *tiles_ws, uint32_t *flag, cudaStream_t stream);
 lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
                          int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, void *tiles_ws,
                          uint32_t *flag, cudaStream_t stream);
@@ -73,12 +73,15 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restric
 }
 
 // Same range guard for an activation that is already silu(g)*u (f32): l2, rescale, f16, tile order.
+// With `sfid` the rows of `a` (and of `scale`) are in expert-sorted order and sfid[row] is the flat id.
 __global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restrict__ a, const float *__restrict__ w,
-                                                           const int32_t *__restrict__ pos, int64_t rows, int ff,
-                                                           uint8_t *__restrict__ act, float *__restrict__ scale) {
+                                                           const int32_t *__restrict__ pos, const int32_t *__restrict__ sfid,
+                                                           int64_t rows, int ff, uint8_t *__restrict__ act,
+                                                           float *__restrict__ scale) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
+    const int64_t fid = sfid ? sfid[row] : row;
     const float *ar = a + row * ff;
     float ss = 0.f;
     for (int i = lane * 8; i < ff; i += 256) {
@@ -89,7 +92,7 @@ __global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restri
     for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float l2 = fminf(fmaxf(sqrtf(ss), 1e-8f), 1e30f);
     const float k = 32768.0f / l2;
-    const int p = pos[row];
+    const int p = pos[fid];
     for (int i = lane * 8; i < ff; i += 256) {
         const float4 a0 = *reinterpret_cast<const float4 *>(ar + i), a1 = *reinterpret_cast<const float4 *>(ar + i + 4);
         __align__(16) __half2 h[4] = {__floats2half2_rn(a0.x * k, a0.z * k), __floats2half2_rn(a0.y * k, a0.w * k),
@@ -99,7 +102,7 @@ __global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restri
                            ((size_t)((ci & 7) ^ (p & 7)) << 4);
         *reinterpret_cast<uint4 *>(act + off) = *reinterpret_cast<const uint4 *>(h);
     }
-    if (lane == 0) scale[row] = l2 * 0x1p-15f * (w ? w[row] : 1.0f);
+    if (lane == 0) scale[row] = l2 * 0x1p-15f * (w ? w[fid] : 1.0f);
 }
 
 // out[t, c] = sum over slots (in slot order) of y[t, s, c], then + shared[t, c].
@@ -117,6 +120,33 @@ __global__ void sum_slots_kernel(const float *__restrict__ y, const float *__res
     if (shared) {
         const float4 v = reinterpret_cast<const float4 *>(shared)[i];
         s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+    }
+    reinterpret_cast<float4 *>(out)[i] = s;
+}
+
+// Same sum when the partial rows are unscaled and in expert-sorted order: row spos[flat id] of `y`
+// times scale[that row]; likewise for the shared expert's rows.
+__global__ void sum_sorted_kernel(const float *__restrict__ y, const float *__restrict__ scale,
+                                  const int32_t *__restrict__ spos, const float *__restrict__ shared,
+                                  const float *__restrict__ sh_scale, const int32_t *__restrict__ sh_spos, int64_t t,
+                                  int top_k, int n4, float *__restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= t * n4) return;
+    const int64_t tok = i / n4, c = i - tok * n4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top_k; k++) {
+        const int64_t r = spos[tok * top_k + k];
+        const float sc = scale[r];
+        const float4 v = reinterpret_cast<const float4 *>(y)[r * n4 + c];
+        s.x = __fadd_rn(s.x, __fmul_rn(v.x, sc)); s.y = __fadd_rn(s.y, __fmul_rn(v.y, sc));
+        s.z = __fadd_rn(s.z, __fmul_rn(v.z, sc)); s.w = __fadd_rn(s.w, __fmul_rn(v.w, sc));
+    }
+    if (shared) {
+        const int64_t r = sh_spos[tok];
+        const float sc = sh_scale[r];
+        const float4 v = reinterpret_cast<const float4 *>(shared)[r * n4 + c];
+        s.x = __fadd_rn(s.x, __fmul_rn(v.x, sc)); s.y = __fadd_rn(s.y, __fmul_rn(v.y, sc));
+        s.z = __fadd_rn(s.z, __fmul_rn(v.z, sc)); s.w = __fadd_rn(s.w, __fmul_rn(v.w, sc));
     }
     reinterpret_cast<float4 *>(out)[i] = s;
 }
@@ -147,16 +177,21 @@ size_t ffn_bytes(int64_t rows, int64_t hidden, int64_t ff, int64_t n_expert) {
     o += 2 * lmoe_align_up((size_t)rows * ff * 4, 256);      // gate, up
     o += mm_tiled_bytes(rows, n_expert, ff);                 // f16 activation in tile order
     o += lmoe_align_up((size_t)rows * 4, 256);               // row scale
+    o += lmoe_align_up((size_t)rows * 4, 256);               // flat id of every sorted row
     const size_t t1 = mm_tiles_bytes(rows, n_expert, ff), t2 = mm_tiles_bytes(rows, n_expert, hidden);
     o += t1 > t2 ? t1 : t2;
     return o;
 }
 
 // y[rows, hidden] = row_weight * FFN_{expert of row}(x[row / top_k]); lists as produced by map0.
+// With `spos` / `scale_out` (both [rows], caller-owned) and the fused kernels available, y instead holds the
+// UNSCALED rows in expert-sorted order: row spos[flat id], to be multiplied by scale_out[that row]; the
+// tensor-core epilogues then store whole tile columns side by side instead of scattering by flat id.
+// *sorted_used tells which form was produced.
 lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const lmoe_expert_stack *down,
                         const float *x, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
                         int64_t map_stride, const float *row_w, float *y, uint8_t *ws, uint32_t *flag,
-                        cudaStream_t s) {
+                        cudaStream_t s, int32_t *spos = nullptr, float *scale_out = nullptr, bool *sorted_used = nullptr) {
     const int64_t rows = t * top_k, ff = gate->n_out, hidden = gate->k, ne = gate->n_expert;
     Carver c{ws, 0};
     uint8_t *xt = c.take<uint8_t>(mm_tiled_bytes(rows, ne, hidden));
@@ -164,13 +199,20 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
     float *g = c.take<float>((size_t)rows * ff), *u = c.take<float>((size_t)rows * ff);
     uint8_t *act = c.take<uint8_t>(mm_tiled_bytes(rows, ne, ff));
     float *rs = c.take<float>((size_t)rows);
+    int32_t *sfid = c.take<int32_t>((size_t)rows);
     void *tiles = ws + c.off;
     lmoe_status st;
-    LMOE_CUDA(launch_gather_tiles(x, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos, s));
-    if (gate->dtype == LMOE_Q4_K && up->dtype == LMOE_Q4_K) {
+    const bool fused_gu = gate->dtype == LMOE_Q4_K && up->dtype == LMOE_Q4_K;
+    const bool fused_dn = down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0;
+    const bool sorted = spos && scale_out && fused_gu && fused_dn;
+    if (sorted_used) *sorted_used = sorted;
+    LMOE_CUDA(launch_gather_tiles(x, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos,
+                                  sorted ? spos : nullptr, sorted ? sfid : nullptr, s));
+    if (fused_gu) {
         // both projections in one pass over the activations, SwiGLU in the epilogue
-        if ((st = launch_mm_gateup(gate, up, xt, tpe, ids_map, map_stride, rows, g, tiles, flag, s))) return st;
-        rescale_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, row_w, pos, rows, (int)ff, act, rs);
+        if ((st = launch_mm_gateup(gate, up, xt, tpe, ids_map, map_stride, rows, g, sorted, tiles, flag, s))) return st;
+        rescale_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, row_w, pos, sorted ? sfid : nullptr, rows, (int)ff,
+                                                                       act, sorted ? scale_out : rs);
         LMOE_LAUNCH_CHECK("rescale_rows_kernel");
     } else {
         if ((st = launch_mm_id(gate, xt, tpe, ids_map, map_stride, rows, nullptr, g, tiles, flag, s))) return st;
@@ -178,8 +220,8 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
         swiglu_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(g, u, row_w, pos, rows, (int)ff, act, rs);
         LMOE_LAUNCH_CHECK("swiglu_rows_kernel");
     }
-    if (down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0)
-        st = launch_mm_down(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s);
+    if (fused_dn)
+        st = launch_mm_down(down, act, tpe, ids_map, map_stride, rows, sorted ? nullptr : rs, y, sorted, tiles, flag, s);
     else
         st = launch_mm_id(down, act, tpe, ids_map, map_stride, rows, rs, y, tiles, flag, s);
     return st;
@@ -203,6 +245,8 @@ size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
     o += lmoe_align_up((size_t)rows * L->hidden * 4, 256);           // routed partial rows
     o += lmoe_align_up((size_t)t * L->hidden * 4, 256);              // shared expert rows
     o += lmoe_align_up((size_t)(t + 64) * 4, 256);                   // identity list
+    o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // sorted position and scale of every routed row
+    o += 2 * lmoe_align_up((size_t)t * 4, 256);                      // the same for the shared expert's rows
     o += ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
     return o;
 }
@@ -224,6 +268,10 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     float *y = c.take<float>((size_t)rows * H);
     float *ysh = c.take<float>((size_t)t * H);
     uint32_t *sh_list = c.take<uint32_t>((size_t)t + 64);
+    int32_t *spos = c.take<int32_t>((size_t)rows);
+    float *rscale = c.take<float>((size_t)rows);
+    int32_t *sh_spos = c.take<int32_t>((size_t)t);
+    float *sh_scale = c.take<float>((size_t)t);
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
 
     LMOE_CUDA(launch_route_logits(L->router, x, (int)t, (int)H, (int)L->n_expert, logits, s));
@@ -231,19 +279,26 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
     LMOE_CUDA(launch_map0(ids, (int)t, (int)L->top_k, (int)L->n_expert, tpe, ids_map, s));
-    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s);
+    bool sorted = false, sh_sorted = false;
+    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s, spos,
+                                 rscale, &sorted);
     if (st) return st;
     const float *shared = nullptr;
     if (L->sh_gate) {
         iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64));
         LMOE_LAUNCH_CHECK("iota_list_kernel");
+        // the shared expert's rows take the same form as the routed ones, so one kernel sums both
         st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
-                         nullptr, ysh, ffn_ws, flag, s);
+                         nullptr, ysh, ffn_ws, flag, s, sorted ? sh_spos : nullptr, sorted ? sh_scale : nullptr, &sh_sorted);
         if (st) return st;
         shared = ysh;
     }
     const int64_t n = t * (H / 4);
-    sum_slots_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, shared, t, (int)L->top_k, (int)(H / 4), out);
+    if (sorted && (!shared || sh_sorted))
+        sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, rscale, spos, shared, sh_scale, sh_spos, t,
+                                                                      (int)L->top_k, (int)(H / 4), out);
+    else
+        sum_slots_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, shared, t, (int)L->top_k, (int)(H / 4), out);
     LMOE_LAUNCH_CHECK("sum_slots_kernel");
     if (ids_out) LMOE_CUDA(cudaMemcpyAsync(ids_out, ids, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
     if (w_out) LMOE_CUDA(cudaMemcpyAsync(w_out, w, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
@@ -281,7 +336,7 @@ static lmoe_status mm_id_run(const lmoe_expert_stack *stack, const float *x, int
     const uint32_t *tpe = static_cast<const uint32_t *>(map0);
     const int32_t *ids_map = reinterpret_cast<const int32_t *>(static_cast<const uint8_t *>(map0) + stack->n_expert * 4);
     LMOE_CUDA(launch_gather_tiles(x, (int)x_per_row, (int)top_k, (int)k, tpe, ids_map, (int)t, (int)stack->n_expert, xt,
-                                  nullptr, s));
+                                  nullptr, nullptr, nullptr, s));
     return launch_mm_id(stack, xt, tpe, ids_map, t, t * top_k, nullptr, out, tiles, flag, s);
 }
 

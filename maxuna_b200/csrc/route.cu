@@ -76,10 +76,10 @@ route_logits_kernel(const float *__restrict__ router, const float *__restrict__ 
 }
 
 // Prefill-sized variant for hidden = 128*HB: a block stages TTB tokens in shared memory; each of
-// its 8 warps walks experts warp, warp+8, ... with the router row in registers (all of its loads
+// its 8 warps walks pairs of experts with both router rows in registers (all of their loads
 // in flight together) and runs the same per-lane fmaf chains, so the logits are bit-identical.
 template <int HB, int TTB>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+__global__ void __launch_bounds__(ROUTE_WARPS * 32, 1)
 route_logits_tiled_kernel(const float *__restrict__ router, const float *__restrict__ x, int t, int n_expert,
                           float *__restrict__ logits) {
     extern __shared__ float xs[];
@@ -90,24 +90,38 @@ route_logits_tiled_kernel(const float *__restrict__ router, const float *__restr
     for (int i = threadIdx.x; i < nt * (H / 4); i += ROUTE_WARPS * 32)
         reinterpret_cast<float4 *>(xs)[i] = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t0 * H) + i);
     __syncthreads();
-    for (int e = warp; e < n_expert; e += ROUTE_WARPS) {
-        float4 wv[HB];
+    // two router rows per pass: every hidden-state value read from shared memory feeds two chains
+    for (int e = 2 * warp; e < n_expert; e += 2 * ROUTE_WARPS) {
+        const bool two = e + 1 < n_expert;
+        float4 wa[HB], wb[HB];
         const float4 *wr = reinterpret_cast<const float4 *>(router + (size_t)e * H) + lane;
+        const float4 *wq = reinterpret_cast<const float4 *>(router + (size_t)(two ? e + 1 : e) * H) + lane;
 #pragma unroll
-        for (int j = 0; j < HB; j++) wv[j] = __ldg(wr + 32 * j);
+        for (int j = 0; j < HB; j++) {
+            wa[j] = __ldg(wr + 32 * j);
+            wb[j] = __ldg(wq + 32 * j);
+        }
         for (int i = 0; i < nt; i++) {
             const float4 *xr = reinterpret_cast<const float4 *>(xs + i * H) + lane;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
 #pragma unroll
             for (int j = 0; j < HB; j++) {
                 const float4 xv = xr[32 * j];
-                a0 = __fmaf_rn(xv.x, wv[j].x, a0);
-                a1 = __fmaf_rn(xv.y, wv[j].y, a1);
-                a2 = __fmaf_rn(xv.z, wv[j].z, a2);
-                a3 = __fmaf_rn(xv.w, wv[j].w, a3);
+                a0 = __fmaf_rn(xv.x, wa[j].x, a0);
+                a1 = __fmaf_rn(xv.y, wa[j].y, a1);
+                a2 = __fmaf_rn(xv.z, wa[j].z, a2);
+                a3 = __fmaf_rn(xv.w, wa[j].w, a3);
+                b0 = __fmaf_rn(xv.x, wb[j].x, b0);
+                b1 = __fmaf_rn(xv.y, wb[j].y, b1);
+                b2 = __fmaf_rn(xv.z, wb[j].z, b2);
+                b3 = __fmaf_rn(xv.w, wb[j].w, b3);
             }
-            const float v = lmoe_router_fold(a0, a1, a2, a3);
-            if (lane == 0) logits[(size_t)(t0 + i) * n_expert + e] = v;
+            const float va = lmoe_router_fold(a0, a1, a2, a3);
+            const float vb = lmoe_router_fold(b0, b1, b2, b3);
+            if (lane == 0) {
+                logits[(size_t)(t0 + i) * n_expert + e] = va;
+                if (two) logits[(size_t)(t0 + i) * n_expert + e + 1] = vb;
+            }
         }
     }
 }
@@ -143,14 +157,22 @@ cudaError_t launch_route_logits(const float *router, const float *x, int t, int 
     } else if (t <= 64) {
         route_logits_kernel<4><<<dim3(gx, (t + 3) / 4), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
     } else if (hidden == 128 * 24) {
-        constexpr int TTB = 8;
-        const size_t smem = (size_t)TTB * hidden * sizeof(float);
+        // 16 tokens per block halve the router re-reads; smaller inputs use 8 to cover more SMs
+        const bool wide = t >= 2048;
+        const int ttb = wide ? 16 : 8;
+        const size_t smem = (size_t)ttb * hidden * sizeof(float);
         static bool attr_set = false;
         if (!attr_set) {
-            cudaFuncSetAttribute(route_logits_tiled_kernel<24, TTB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(route_logits_tiled_kernel<24, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(16 * hidden * sizeof(float)));
+            cudaFuncSetAttribute(route_logits_tiled_kernel<24, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(8 * hidden * sizeof(float)));
             attr_set = true;
         }
-        route_logits_tiled_kernel<24, TTB><<<(t + TTB - 1) / TTB, ROUTE_WARPS * 32, smem, s>>>(router, x, t, n_expert, logits);
+        if (wide)
+            route_logits_tiled_kernel<24, 16><<<(t + 15) / 16, ROUTE_WARPS * 32, smem, s>>>(router, x, t, n_expert, logits);
+        else
+            route_logits_tiled_kernel<24, 8><<<(t + 7) / 8, ROUTE_WARPS * 32, smem, s>>>(router, x, t, n_expert, logits);
     } else {
         route_logits_kernel<8><<<dim3(gx, (t + 7) / 8), ROUTE_WARPS * 32, 0, s>>>(router, x, t, hidden, n_expert, logits);
     }
