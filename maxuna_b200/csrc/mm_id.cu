@@ -596,7 +596,8 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *a_st = smem, *b_st = smem + GU_NS * GU_A_STAGE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(b_st + GU_NS * B_STAGE_BYTES);
-    uint64_t *a_full = bars, *b_full = bars + 4, *a_empty = bars + 8, *b_empty = bars + 12, *acc_full = bars + 16, *acc_empty = bars + 17;
+    // full[s]: eight dequant warps + the B loader's expect_tx arrival; empty[s]: one tcgen05.commit
+    uint64_t *full = bars, *empty = bars + 4, *acc_full = bars + 16, *acc_empty = bars + 17;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -606,10 +607,8 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 
     if (tid == 0) {
         for (int s = 0; s < GU_NS; s++) {
-            mb_init(&a_full[s], 8);
-            mb_init(&b_full[s], 1);
-            mb_init(&a_empty[s], 1);
-            mb_init(&b_empty[s], 1);
+            mb_init(&full[s], 9);
+            mb_init(&empty[s], 1);
         }
         mb_init(acc_full, 1);
         mb_init(acc_empty, 4);
@@ -653,7 +652,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                     for (int j = 0; j < 4; j++, g++) {
                         const int s = g % GU_NS;
                         if (tid == 0) GSTAMP(0, g, 0);
-                        ok = ok && mb_wait(&a_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
+                        ok = ok && mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
                         if (tid == 0) GSTAMP(0, g, 1);
                         uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
                         if (rvalid) {
@@ -666,7 +665,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                         if (tid == 0) GSTAMP(0, g, 2);
                         fence_async_smem();
                         __syncwarp();
-                        if (lane == 0) mb_arrive(&a_full[s]);
+                        if (lane == 0) mb_arrive(&full[s]);
                         if (tid == 0) GSTAMP(0, g, 3);
                     }
                 }
@@ -693,16 +692,26 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 }
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % GU_NS;
-                    ok = mb_wait(&b_empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 4);
-                    mb_expect_tx(&b_full[s], (uint32_t)nv * 128u);
-                    bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &b_full[s]);
+                    ok = mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 4);
+                    mb_expect_tx(&full[s], (uint32_t)nv * 128u);
+                    bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &full[s]);
                 }
             }
         }
     } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t g = 0, it = 0;
+            // The issuing thread runs a dependent chain of scalar instructions, so everything it can
+            // know ahead is precomputed: operand descriptors per ring slot, slot and phase as counters.
+            uint64_t ad0[GU_NS], ad1[GU_NS], bd[GU_NS];
+#pragma unroll
+            for (int s = 0; s < GU_NS; s++) {
+                ad0[s] = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
+                ad1[s] = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
+                bd[s] = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
+            }
+            uint32_t it = 0, ph = 0;
+            int s = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
                 const int nv = P.tiles[8 * tile + 2];
@@ -710,25 +719,20 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
                 ok = mb_wait(acc_empty, (it & 1) ^ 1, P.flag, 5);
                 tc_fence_after();
-                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                    const int s = g % GU_NS;
-                    GSTAMP(1, g, 0);
-                    ok = mb_wait(&a_full[s], (g / GU_NS) & 1, P.flag, 6);
-                    GSTAMP(1, g, 1);
-                    ok = ok && mb_wait(&b_full[s], (g / GU_NS) & 1, P.flag, 7);
-                    GSTAMP(1, g, 2);
+                for (int ks = 0; ks < k_stages && ok; ks++) {
+                    ok = mb_wait(&full[s], ph, P.flag, 6);
                     tc_fence_after();
-                    const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
-                    const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
-                    const uint64_t bd = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
+                    // slot-indexed descriptors without dynamic register indexing
+                    const uint64_t a0 = s == 0 ? ad0[0] : s == 1 ? ad0[1] : ad0[2];
+                    const uint64_t a1 = s == 0 ? ad1[0] : s == 1 ? ad1[1] : ad1[2];
+                    const uint64_t b0 = s == 0 ? bd[0] : s == 1 ? bd[1] : bd[2];
 #pragma unroll
                     for (int kk = 0; kk < MM_K / 16; kk++) {
-                        tc_mma_f16(tmem_base, ad0 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                        tc_mma_f16(tmem_base + 256, ad1 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16(tmem_base, a0 + 2 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16(tmem_base + 256, a1 + 2 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
-                    tc_commit(&a_empty[s]);
-                    tc_commit(&b_empty[s]);
-                    GSTAMP(1, g, 3);
+                    tc_commit(&empty[s]);
+                    if (++s == GU_NS) { s = 0; ph ^= 1; }
                 }
                 tc_commit(acc_full);
             }
