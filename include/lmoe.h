@@ -251,6 +251,12 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
 lmoe_status lmoe_experts_forward_rows(const lmoe_layer *layer, const float *x, const uint32_t *local_ids,
                                       const float *row_weights, int64_t rows, float *out, void *workspace,
                                       size_t workspace_bytes, void *stream);
+/* The same with x [rows, hidden] in IEEE half precision (16-byte aligned): the wire format of the token
+ * dispatch.  The grouped GEMM rounds its activation operand to half anyway, so results are identical to
+ * passing the same values as f32. */
+lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *layer, const void *x_f16, const uint32_t *local_ids,
+                                          const float *row_weights, int64_t rows, float *out, void *workspace,
+                                          size_t workspace_bytes, void *stream);
 /* Bytes of scratch `lmoe_experts_forward_rows` / `lmoe_shared_forward` need for `rows` rows. */
 size_t lmoe_rows_workspace_bytes(const lmoe_layer *layer, int64_t rows);
 /* The shared expert alone: out [t, hidden] = FFN_shared(x [t, hidden]). */

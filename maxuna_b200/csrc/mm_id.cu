@@ -241,7 +241,8 @@ __device__ __forceinline__ size_t tiled_off(int slot, int k_stages, int ks, int 
     return (((size_t)slot * k_stages + ks) * MM_N + rr) * 128 + ((size_t)(c ^ (rr & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(256) gather_tiles_kernel(const float *__restrict__ x, int x_per_row, int top_k, int k,
+template <bool XF16>
+__global__ void __launch_bounds__(256) gather_tiles_kernel(const void *__restrict__ xv, int x_per_row, int top_k, int k,
                                                            const uint32_t *__restrict__ tpe, const int32_t *__restrict__ ids_map,
                                                            int map_stride, int n_expert, uint8_t *__restrict__ xt,
                                                            int32_t *__restrict__ pos, int32_t *__restrict__ spos,
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(256) gather_tiles_kernel(const float *__restri
     const int slot0 = slot0_s, srow0 = row0_s, rows = (int)tpe[e], k_stages = k / MM_K, chunks = k / 8;
     for (int i = blockIdx.y; i < rows; i += gridDim.y) {
         const int fid = ids_map[(size_t)e * map_stride + i];
-        const float *src = x + (size_t)(x_per_row == 1 ? fid / top_k : fid) * k;
+        const size_t srow = (size_t)(x_per_row == 1 ? fid / top_k : fid) * k;
         const int slot = slot0 + i / MM_N, rr = i % MM_N;
         if (threadIdx.x == 0) {
             if (pos) pos[fid] = slot * MM_N + rr;
@@ -280,11 +281,21 @@ __global__ void __launch_bounds__(256) gather_tiles_kernel(const float *__restri
             if (sfid) sfid[srow0 + i] = fid;
         }
         for (int ci = threadIdx.x; ci < chunks; ci += 256) {
-            const float4 a = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci);
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci + 1);
-            __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.z), __floats2half2_rn(a.y, a.w),
-                                          __floats2half2_rn(b.x, b.z), __floats2half2_rn(b.y, b.w)};
-            *reinterpret_cast<uint4 *>(xt + tiled_off(slot, k_stages, ci >> 3, rr, ci & 7)) = *reinterpret_cast<const uint4 *>(h);
+            uint4 o;
+            if (XF16) {
+                // rows already in f16 (the expert-parallel wire format): only the order inside the chunk changes
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(xv) + srow) + ci);
+                o = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632), __byte_perm(v.z, v.w, 0x5410),
+                               __byte_perm(v.z, v.w, 0x7632));
+            } else {
+                const float *src = static_cast<const float *>(xv) + srow;
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci);
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci + 1);
+                __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.z), __floats2half2_rn(a.y, a.w),
+                                              __floats2half2_rn(b.x, b.z), __floats2half2_rn(b.y, b.w)};
+                o = *reinterpret_cast<const uint4 *>(h);
+            }
+            *reinterpret_cast<uint4 *>(xt + tiled_off(slot, k_stages, ci >> 3, rr, ci & 7)) = o;
         }
     }
 }
@@ -1211,13 +1222,17 @@ size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k) {
     return lmoe_align_up((size_t)((rows + MM_N - 1) / MM_N + n_expert) * (size_t)(k / MM_K) * B_STAGE_BYTES, 256);
 }
 
-cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
+cudaError_t launch_gather_tiles(const void *x, int x_f16, int x_per_row, int top_k, int k, const uint32_t *tpe,
                                 const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
                                 int32_t *spos, int32_t *sfid, cudaStream_t s) {
     // enough blocks per expert to cover the device even when one expert holds all the rows
     const int gy = n_expert >= 64 ? 16 : (n_expert >= 8 ? 128 : 1024);
-    gather_tiles_kernel<<<dim3(n_expert, gy), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
-                                                           static_cast<uint8_t *>(xt), pos, spos, sfid);
+    if (x_f16)
+        gather_tiles_kernel<true><<<dim3(n_expert, gy), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
+                                                                     static_cast<uint8_t *>(xt), pos, spos, sfid);
+    else
+        gather_tiles_kernel<false><<<dim3(n_expert, gy), 256, 0, s>>>(x, x_per_row, top_k, k, tpe, ids_map, map_stride, n_expert,
+                                                                      static_cast<uint8_t *>(xt), pos, spos, sfid);
     return cudaGetLastError();
 }
 

@@ -9,7 +9,7 @@ int64_t mm_max_tiles(int64_t rows, int64_t n_expert, int64_t n_out);
 bool mm_id_kernel_available(int dtype, int64_t n_out, int64_t k);
 size_t mm_tiles_bytes(int64_t rows, int64_t n_expert, int64_t n_out);
 size_t mm_tiled_bytes(int64_t rows, int64_t n_expert, int64_t k);
-cudaError_t launch_gather_tiles(const float *x, int x_per_row, int top_k, int k, const uint32_t *tpe,
+cudaError_t launch_gather_tiles(const void *x, int x_f16, int x_per_row, int top_k, int k, const uint32_t *tpe,
                                 const int32_t *ids_map, int map_stride, int n_expert, void *xt, int32_t *pos,
                                 int32_t *spos, int32_t *sfid, cudaStream_t s);
 lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
@@ -189,9 +189,10 @@ size_t ffn_bytes(int64_t rows, int64_t hidden, int64_t ff, int64_t n_expert) {
 // tensor-core epilogues then store whole tile columns side by side instead of scattering by flat id.
 // *sorted_used tells which form was produced.
 lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const lmoe_expert_stack *down,
-                        const float *x, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
+                        const void *x, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
                         int64_t map_stride, const float *row_w, float *y, uint8_t *ws, uint32_t *flag,
-                        cudaStream_t s, int32_t *spos = nullptr, float *scale_out = nullptr, bool *sorted_used = nullptr) {
+                        cudaStream_t s, int32_t *spos = nullptr, float *scale_out = nullptr, bool *sorted_used = nullptr,
+                        int x_f16 = 0) {
     const int64_t rows = t * top_k, ff = gate->n_out, hidden = gate->k, ne = gate->n_expert;
     Carver c{ws, 0};
     uint8_t *xt = c.take<uint8_t>(mm_tiled_bytes(rows, ne, hidden));
@@ -206,7 +207,7 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
     const bool fused_dn = down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0;
     const bool sorted = spos && scale_out && fused_gu && fused_dn;
     if (sorted_used) *sorted_used = sorted;
-    LMOE_CUDA(launch_gather_tiles(x, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos,
+    LMOE_CUDA(launch_gather_tiles(x, x_f16, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos,
                                   sorted ? spos : nullptr, sorted ? sfid : nullptr, s));
     if (fused_gu) {
         // both projections in one pass over the activations, SwiGLU in the epilogue
@@ -335,7 +336,7 @@ static lmoe_status mm_id_run(const lmoe_expert_stack *stack, const float *x, int
     LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
     const uint32_t *tpe = static_cast<const uint32_t *>(map0);
     const int32_t *ids_map = reinterpret_cast<const int32_t *>(static_cast<const uint8_t *>(map0) + stack->n_expert * 4);
-    LMOE_CUDA(launch_gather_tiles(x, (int)x_per_row, (int)top_k, (int)k, tpe, ids_map, (int)t, (int)stack->n_expert, xt,
+    LMOE_CUDA(launch_gather_tiles(x, 0, (int)x_per_row, (int)top_k, (int)k, tpe, ids_map, (int)t, (int)stack->n_expert, xt,
                                   nullptr, nullptr, nullptr, s));
     return launch_mm_id(stack, xt, tpe, ids_map, t, t * top_k, nullptr, out, tiles, flag, s);
 }
@@ -381,13 +382,14 @@ static size_t rows_ws_bytes(const lmoe_layer *L, int64_t rows) {
            ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
 }
 
-extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *L, const float *x, const uint32_t *local_ids,
-                                                 const float *row_weights, int64_t rows, float *out, void *workspace,
-                                                 size_t workspace_bytes, void *stream) {
+static lmoe_status experts_rows_run(const lmoe_layer *L, const void *x, int x_f16, const uint32_t *local_ids,
+                                    const float *row_weights, int64_t rows, float *out, void *workspace,
+                                    size_t workspace_bytes, void *stream) {
     lmoe_clear_error();
     if (!L || !x || !local_ids || !out) return lmoe_fail(LMOE_ERR_INVALID, "layer/x/local_ids/out is NULL");
     if (rows < 0 || rows > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "rows out of range");
     if (rows == 0) return LMOE_OK;
+    if (reinterpret_cast<uintptr_t>(x) & 15u) return lmoe_fail(LMOE_ERR_INVALID, "x must be 16-byte aligned");
     if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
     if (!workspace || workspace_bytes < rows_ws_bytes(L, rows))
         return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", rows_ws_bytes(L, rows), workspace_bytes);
@@ -399,7 +401,20 @@ extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *L, const floa
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
     LMOE_CUDA(launch_map0(local_ids, (int)rows, 1, (int)L->n_expert, tpe, ids_map, s));
-    return ffn_grouped(L->gate, L->up, L->down, x, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s);
+    return ffn_grouped(L->gate, L->up, L->down, x, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s, nullptr,
+                       nullptr, nullptr, x_f16);
+}
+
+extern "C" lmoe_status lmoe_experts_forward_rows(const lmoe_layer *L, const float *x, const uint32_t *local_ids,
+                                                 const float *row_weights, int64_t rows, float *out, void *workspace,
+                                                 size_t workspace_bytes, void *stream) {
+    return experts_rows_run(L, x, 0, local_ids, row_weights, rows, out, workspace, workspace_bytes, stream);
+}
+
+extern "C" lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *L, const void *x_f16, const uint32_t *local_ids,
+                                                     const float *row_weights, int64_t rows, float *out, void *workspace,
+                                                     size_t workspace_bytes, void *stream) {
+    return experts_rows_run(L, x_f16, 1, local_ids, row_weights, rows, out, workspace, workspace_bytes, stream);
 }
 
 extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, int64_t t, float *out, void *workspace,

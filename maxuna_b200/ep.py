@@ -11,8 +11,10 @@ order and adds the shared expert, exactly like the single-GPU path.
 
 The expert math is supplied as two callables so that the host logic can be
 exercised on CPU ranks:
-  rows_fn(x_rows[f32 R,H], local_ids[i32 R], row_w[f32 R]) -> y[f32 R,H]
+  rows_fn(x_rows[payload dtype R,H], local_ids[i32 R], row_w[f32 R]) -> y[f32 R,H]
   shared_fn(x[f32 T,H]) -> y[f32 T,H]  (or None)
+  combine_fn(y[f32 T,K,H]) -> out[f32 T,H], the slot-order sum (optional; a plain loop otherwise)
+On GPUs the shared expert runs on a side stream while the dispatch is in flight.
 """
 from __future__ import annotations
 
@@ -22,8 +24,10 @@ import torch.distributed as dist
 
 class ExpertParallelMoe:
     def __init__(self, route_fn, rows_fn, shared_fn, n_expert: int, top_k: int, group=None,
-                 payload_dtype=torch.float16):
+                 payload_dtype=torch.float16, combine_fn=None):
         self.route_fn, self.rows_fn, self.shared_fn = route_fn, rows_fn, shared_fn
+        self.combine_fn = combine_fn
+        self._side = None
         self.n_expert, self.top_k = n_expert, top_k
         self.group = group
         self.world = dist.get_world_size(group)
@@ -32,6 +36,68 @@ class ExpertParallelMoe:
             raise ValueError(f"n_expert ({n_expert}) must divide over {self.world} ranks")
         self.e_local = n_expert // self.world
         self.payload_dtype = payload_dtype
+        self.last_stats = {}
+
+    # -- the exchange plan (pure index arithmetic; covered by the CPU tests) --------
+    def plan(self, ids: torch.Tensor):
+        """ids [T,K] -> (order, send_counts): rows sorted by destination rank, stably."""
+        flat = ids.reshape(-1).to(torch.int64)
+        dest = flat // self.e_local
+        order = torch.sort(dest, stable=True).indices
+        send_counts = torch.bincount(dest, minlength=self.world)
+        return order, send_counts
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        t, h = x.shape
+        k = self.top_k
+        ids, w = self.route_fn(x)                       # [T,K] int32 (u32 bits), [T,K] f32
+        order, send_counts = self.plan(ids)
+        dev = x.device
+        # counts exchange (G x G int64)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        n_send, n_recv = sum(sc), sum(rc)
+        tok = order // k
+        # the shared expert needs nothing from the exchange: on GPUs it runs beside it
+        shared = None
+        if self.shared_fn is not None and x.is_cuda:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=dev)
+            self._side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(self._side):
+                shared = self.shared_fn(x)
+        # dispatch payloads: activations (f16 on the wire: the grouped GEMM consumes f16 operands
+        # rounded the same way), local expert id, routing weight
+        xs = x.to(self.payload_dtype).index_select(0, tok)
+        meta_ids = (ids.reshape(-1).to(torch.int64).index_select(0, order) % self.e_local).to(torch.int32)
+        meta_w = w.reshape(-1).index_select(0, order).contiguous()
+        xr = torch.empty(n_recv, h, dtype=self.payload_dtype, device=dev)
+        ir = torch.empty(n_recv, dtype=torch.int32, device=dev)
+        wr = torch.empty(n_recv, dtype=torch.float32, device=dev)
+        dist.all_to_all_single(xr, xs, rc, sc, group=self.group)
+        dist.all_to_all_single(ir, meta_ids, rc, sc, group=self.group)
+        dist.all_to_all_single(wr, meta_w, rc, sc, group=self.group)
+        # local experts on the received rows
+        yr = self.rows_fn(xr, ir, wr) if n_recv else torch.empty(0, h, dtype=torch.float32, device=dev)
+        # combine exchange: rows go back to where they came from, in the order they were sent
+        ys = torch.empty(n_send, h, dtype=torch.float32, device=dev)
+        dist.all_to_all_single(ys, yr.contiguous(), sc, rc, group=self.group)
+        y = torch.empty(t * k, h, dtype=torch.float32, device=dev)
+        y.index_copy_(0, order, ys)
+        y3 = y.view(t, k, h)
+        if self.combine_fn is not None:
+            out = self.combine_fn(y3)
+        else:
+            out = torch.zeros(t, h, dtype=torch.float32, device=dev)
+            for s_ in range(k):                         # fixed slot order, like the single-GPU combine
+                out += y3[:, s_]
+        if self.shared_fn is not None:
+            if shared is None:
+                shared = self.shared_fn(x)
+            else:
+                torch.cuda.current_stream(dev).wait_stream(self._side)
+            out += shared
         self.last_stats = {}
 
     # -- the exchange plan (pure index arithmetic; covered by the CPU tests) --------
@@ -91,6 +157,10 @@ def make_gpu_ep_block(full_router, bias, local_block, n_expert, top_k, scale=2.5
     def route_fn(x):
         return ops.route(full_router, bias, x, top_k, scale, norm)
 
+    def combine_fn(y3):
+        # the fused slot-order sum with unit weights (multiplying by 1.0 changes nothing)
+        return ops.combine(y3, None, torch.ones(y3.shape[0], y3.shape[1], dtype=torch.float32, device=y3.device))
+
     return ExpertParallelMoe(route_fn, local_block.experts_forward_rows,
                              local_block.shared_forward if local_block.shared is not None else None,
-                             n_expert, top_k, group)
+                             n_expert, top_k, group, combine_fn=combine_fn)

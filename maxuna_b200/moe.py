@@ -204,14 +204,15 @@ class MoeBlock:
         return self._rws
 
     def experts_forward_rows(self, x: torch.Tensor, local_ids: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
-        """`lmoe_experts_forward_rows`: y[r] = row_w[r] * FFN_{local_ids[r]}(x[r])."""
-        x = x.to(torch.float32).contiguous()
+        """`lmoe_experts_forward_rows` (`_f16` for half-precision rows): y[r] = row_w[r] * FFN_{local_ids[r]}(x[r])."""
+        f16 = x.dtype == torch.float16
+        x = (x if f16 else x.to(torch.float32)).contiguous()
         rows = x.shape[0]
         out = torch.empty(rows, self.hidden, dtype=torch.float32, device=x.device)
         ws = self._rows_ws(rows)
-        check(lib().lmoe_experts_forward_rows(self._h, x.data_ptr(), local_ids.contiguous().data_ptr(),
-                                              row_w.contiguous().data_ptr(), rows, out.data_ptr(), ws.data_ptr(),
-                                              ws.numel(), stream_ptr()))
+        fn = lib().lmoe_experts_forward_rows_f16 if f16 else lib().lmoe_experts_forward_rows
+        check(fn(self._h, x.data_ptr(), local_ids.contiguous().data_ptr(), row_w.contiguous().data_ptr(), rows,
+                 out.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
         return out
 
     def shared_forward(self, x: torch.Tensor) -> torch.Tensor:
