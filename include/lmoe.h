@@ -257,6 +257,21 @@ lmoe_status lmoe_experts_forward_rows(const lmoe_layer *layer, const float *x, c
 lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *layer, const void *x_f16, const uint32_t *local_ids,
                                           const float *row_weights, int64_t rows, float *out, void *workspace,
                                           size_t workspace_bytes, void *stream);
+/* Token dispatch of the expert-parallel path, packed on the device: rank r owns experts
+ * [r * n_expert / world, (r + 1) * n_expert / world).  From x [t, hidden] f32 and the routing decision
+ * ids / weights [t, top_k], writes the t * top_k routed rows grouped by destination rank (by expert inside a
+ * rank): rows_f16 [t*top_k, hidden] half, local_ids [t*top_k] (expert id relative to the destination's first
+ * expert), row_weights [t*top_k], row_pos [t*top_k] = position of flat id (token * top_k + slot) in that order,
+ * and send_counts [world] (int64, device).  Workspace: lmoe_ep_pack_workspace_bytes(n_expert, t). */
+size_t lmoe_ep_pack_workspace_bytes(int64_t n_expert, int64_t t);
+lmoe_status lmoe_ep_pack(const float *x, const uint32_t *ids, const float *weights, int64_t t, int64_t hidden,
+                         int64_t top_k, int64_t n_expert, int64_t world, void *rows_f16, uint32_t *local_ids,
+                         float *row_weights, int32_t *row_pos, int64_t *send_counts, void *workspace,
+                         size_t workspace_bytes, void *stream);
+/* The return leg: out [t, hidden] = sum over slots, in slot order, of rows[row_pos[token * top_k + slot]]
+ * (the weighted expert outputs, back in the order they were sent), then + shared [t, hidden] when non-NULL. */
+lmoe_status lmoe_ep_combine(const float *rows, const int32_t *row_pos, const float *shared, int64_t t,
+                            int64_t top_k, int64_t hidden, float *out, void *stream);
 /* Bytes of scratch `lmoe_experts_forward_rows` / `lmoe_shared_forward` need for `rows` rows. */
 size_t lmoe_rows_workspace_bytes(const lmoe_layer *layer, int64_t rows);
 /* The shared expert alone: out [t, hidden] = FFN_shared(x [t, hidden]). */

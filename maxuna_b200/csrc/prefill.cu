@@ -136,19 +136,71 @@ __global__ void sum_sorted_kernel(const float *__restrict__ y, const float *__re
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top_k; k++) {
         const int64_t r = spos[tok * top_k + k];
-        const float sc = scale[r];
+        const float sc = scale ? scale[r] : 1.0f;
         const float4 v = reinterpret_cast<const float4 *>(y)[r * n4 + c];
         s.x = __fadd_rn(s.x, __fmul_rn(v.x, sc)); s.y = __fadd_rn(s.y, __fmul_rn(v.y, sc));
         s.z = __fadd_rn(s.z, __fmul_rn(v.z, sc)); s.w = __fadd_rn(s.w, __fmul_rn(v.w, sc));
     }
     if (shared) {
-        const int64_t r = sh_spos[tok];
-        const float sc = sh_scale[r];
+        const int64_t r = sh_spos ? sh_spos[tok] : tok;
+        const float sc = sh_scale ? sh_scale[r] : 1.0f;
         const float4 v = reinterpret_cast<const float4 *>(shared)[r * n4 + c];
         s.x = __fadd_rn(s.x, __fmul_rn(v.x, sc)); s.y = __fadd_rn(s.y, __fmul_rn(v.y, sc));
         s.z = __fadd_rn(s.z, __fmul_rn(v.z, sc)); s.w = __fadd_rn(s.w, __fmul_rn(v.w, sc));
     }
     reinterpret_cast<float4 *>(out)[i] = s;
+}
+
+// Expert-parallel dispatch packing: the routed rows of expert e (list `ids_map[e]`) go to positions
+// [prefix(e), prefix(e) + tpe[e]) of the send buffers, as f16; experts are contiguous per destination rank,
+// so the buffer is grouped by rank.  row_pos[flat id] remembers where each row went.
+__global__ void __launch_bounds__(256) ep_pack_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                      const uint32_t *__restrict__ tpe, const int32_t *__restrict__ ids_map,
+                                                      int map_stride, int top_k, int hidden, int e_local,
+                                                      __half *__restrict__ rows, uint32_t *__restrict__ local_ids,
+                                                      float *__restrict__ row_w, int32_t *__restrict__ row_pos) {
+    __shared__ int warp_rows[8];
+    __shared__ int row0_s;
+    const int e = blockIdx.x;
+    int rpart = 0;
+    for (int i = threadIdx.x; i < e; i += 256) rpart += (int)tpe[i];
+    for (int o = 16; o; o >>= 1) rpart += __shfl_xor_sync(0xffffffffu, rpart, o);
+    if ((threadIdx.x & 31) == 0) warp_rows[threadIdx.x >> 5] = rpart;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int r = 0;
+        for (int i = 0; i < 8; i++) r += warp_rows[i];
+        row0_s = r;
+    }
+    __syncthreads();
+    const int row0 = row0_s, n = (int)tpe[e], chunks = hidden / 8;
+    for (int i = blockIdx.y; i < n; i += gridDim.y) {
+        const int fid = ids_map[(size_t)e * map_stride + i];
+        const int p = row0 + i;
+        const float *src = x + (size_t)(fid / top_k) * hidden;
+        __half *dst = rows + (size_t)p * hidden;
+        for (int ci = threadIdx.x; ci < chunks; ci += 256) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 2 * ci + 1);
+            __align__(16) __half2 h[4] = {__floats2half2_rn(a.x, a.y), __floats2half2_rn(a.z, a.w),
+                                          __floats2half2_rn(b.x, b.y), __floats2half2_rn(b.z, b.w)};
+            reinterpret_cast<uint4 *>(dst)[ci] = *reinterpret_cast<const uint4 *>(h);
+        }
+        if (threadIdx.x == 0) {
+            local_ids[p] = (uint32_t)(e % e_local);
+            row_w[p] = w[fid];
+            row_pos[fid] = p;
+        }
+    }
+}
+
+// send_counts[r] = rows routed to the experts of rank r
+__global__ void ep_counts_kernel(const uint32_t *__restrict__ tpe, int n_expert, int e_local, long long *__restrict__ counts) {
+    const int r = blockIdx.x;
+    int c = 0;
+    for (int e = r * e_local + threadIdx.x; e < (r + 1) * e_local && e < n_expert; e += 32) c += (int)tpe[e];
+    for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (threadIdx.x == 0) counts[r] = c;
 }
 
 // identity row list for a one-expert stack: tpe[0] = t, ids_map[i] = i
@@ -440,4 +492,53 @@ extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, 
 
 extern "C" size_t lmoe_rows_workspace_bytes(const lmoe_layer *L, int64_t rows) {
     return L ? rows_ws_bytes(L, rows < 1 ? 1 : rows) : 0;
+}
+
+// Expert-parallel exchange helpers (no counterpart in the single-GPU reference).
+extern "C" size_t lmoe_ep_pack_workspace_bytes(int64_t n_expert, int64_t t) { return lmoe_map0_scratch_bytes(n_expert, t); }
+
+extern "C" lmoe_status lmoe_ep_pack(const float *x, const uint32_t *ids, const float *weights, int64_t t, int64_t hidden,
+                                    int64_t top_k, int64_t n_expert, int64_t world, void *rows_f16, uint32_t *local_ids,
+                                    float *row_weights, int32_t *row_pos, int64_t *send_counts, void *workspace,
+                                    size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!x || !ids || !weights || !rows_f16 || !local_ids || !row_weights || !row_pos || !send_counts)
+        return lmoe_fail(LMOE_ERR_INVALID, "ep_pack: a buffer is NULL");
+    if (t < 0 || top_k < 1 || n_expert < 1 || world < 1 || n_expert % world || hidden < 8 || hidden % 8)
+        return lmoe_fail(LMOE_ERR_INVALID, "ep_pack: t >= 0, top_k >= 1, n_expert divisible by world, hidden a multiple of 8 required");
+    if (t * top_k > INT32_MAX / 2 || n_expert > 65535) return lmoe_fail(LMOE_ERR_INVALID, "ep_pack: problem too large");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(rows_f16)) & 15u)
+        return lmoe_fail(LMOE_ERR_INVALID, "ep_pack: x and rows_f16 must be 16-byte aligned");
+    if (!workspace || workspace_bytes < lmoe_map0_scratch_bytes(n_expert, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "ep_pack workspace needs %zu bytes, got %zu", lmoe_map0_scratch_bytes(n_expert, t),
+                         workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *tpe = static_cast<uint32_t *>(workspace);
+    int32_t *ids_map = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(workspace) + n_expert * 4);
+    LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)n_expert, tpe, ids_map, s));
+    const int e_local = (int)(n_expert / world);
+    ep_counts_kernel<<<(unsigned)world, 32, 0, s>>>(tpe, (int)n_expert, e_local, reinterpret_cast<long long *>(send_counts));
+    LMOE_LAUNCH_CHECK("ep_counts_kernel");
+    if (t > 0) {
+        const int gy = n_expert >= 64 ? 16 : (n_expert >= 8 ? 128 : 1024);
+        ep_pack_kernel<<<dim3((unsigned)n_expert, gy), 256, 0, s>>>(x, weights, tpe, ids_map, (int)t, (int)top_k, (int)hidden, e_local,
+                                                                static_cast<__half *>(rows_f16), local_ids, row_weights, row_pos);
+        LMOE_LAUNCH_CHECK("ep_pack_kernel");
+    }
+    return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_ep_combine(const float *rows, const int32_t *row_pos, const float *shared, int64_t t,
+                                       int64_t top_k, int64_t hidden, float *out, void *stream) {
+    lmoe_clear_error();
+    if (!rows || !row_pos || !out) return lmoe_fail(LMOE_ERR_INVALID, "ep_combine: rows/row_pos/out is NULL");
+    if (t < 0 || top_k < 1 || hidden < 4 || hidden % 4) return lmoe_fail(LMOE_ERR_INVALID, "ep_combine: bad dimensions");
+    if ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(shared)) & 15u)
+        return lmoe_fail(LMOE_ERR_INVALID, "ep_combine: rows, shared and out must be 16-byte aligned");
+    if (t == 0) return LMOE_OK;
+    const int64_t n = t * (hidden / 4);
+    sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rows, nullptr, row_pos, shared, nullptr, nullptr,
+                                                                               t, (int)top_k, (int)(hidden / 4), out);
+    LMOE_LAUNCH_CHECK("sum_sorted_kernel");
+    return LMOE_OK;
 }
