@@ -83,11 +83,13 @@ class ExpertParallelMoe:
             meta_ids = (ids.reshape(-1).to(torch.int64).index_select(0, order) % self.e_local).to(torch.int32)
             meta_w = w.reshape(-1).index_select(0, order).contiguous()
         xr = torch.empty(n_recv, h, dtype=xs.dtype, device=dev)
-        ir = torch.empty(n_recv, dtype=torch.int32, device=dev)
-        wr = torch.empty(n_recv, dtype=torch.float32, device=dev)
         dist.all_to_all_single(xr, xs, rc, sc, group=self.group)
-        dist.all_to_all_single(ir, meta_ids, rc, sc, group=self.group)
-        dist.all_to_all_single(wr, meta_w, rc, sc, group=self.group)
+        # expert id and routing weight travel together: one [rows, 2] array of 32-bit words
+        meta = torch.stack([meta_ids.view(torch.int32), meta_w.view(torch.int32)], dim=1)
+        meta_r = torch.empty(n_recv, 2, dtype=torch.int32, device=dev)
+        dist.all_to_all_single(meta_r, meta, rc, sc, group=self.group)
+        ir = meta_r[:, 0].contiguous()
+        wr = meta_r[:, 1].contiguous().view(torch.float32)
         # local experts on the received rows
         yr = self.rows_fn(xr, ir, wr) if n_recv else torch.empty(0, h, dtype=torch.float32, device=dev)
         # combine exchange: rows go back to where they came from, in the order they were sent
