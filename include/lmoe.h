@@ -220,7 +220,10 @@ size_t lmoe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens);
  * src/moe.rs:221-323 fused: route, stream each DISTINCT selected expert and the
  * shared expert once, SwiGLU and the weighted combine in the same kernels.
  *   x [t, hidden] f32 -> out [t, hidden] f32; ids_out [t, top_k] / weights_out
- * [t, top_k] receive the routing decision when non-NULL. */
+ * [t, top_k] receive the routing decision when non-NULL.
+ * The workspace needs no initialisation.  The kernel's CTAs synchronise through
+ * device words owned by `layer`: at most one decode call in flight per layer
+ * handle (create a second handle over the same stacks for a second stream). */
 lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
                                     uint32_t *ids_out, float *weights_out, void *workspace,
                                     size_t workspace_bytes, void *stream);
