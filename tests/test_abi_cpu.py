@@ -61,6 +61,26 @@ def test_argument_errors_without_cuda():
     assert lib.lmoe_map0_scratch_bytes(256, 512) >= 256 * 4 + 256 * 512 * 4
 
 
+def test_expert_parallel_argument_errors_without_cuda():
+    from maxuna_b200 import _native
+
+    lib = _native.lib()
+    fake = C.c_void_p(4096)
+    # n_expert must divide over the ranks, hidden a multiple of 8, buffers non-NULL and aligned
+    assert lib.lmoe_ep_pack(fake, fake, fake, 4, 128, 2, 8, 3, fake, fake, fake, fake, fake, fake, 1 << 20, None) == -1
+    assert b"divisible" in lib.lmoe_last_error()
+    assert lib.lmoe_ep_pack(fake, fake, fake, 4, 100, 2, 8, 2, fake, fake, fake, fake, fake, fake, 1 << 20, None) == -1
+    assert lib.lmoe_ep_pack(fake, fake, fake, 4, 128, 2, 8, 2, None, fake, fake, fake, fake, fake, 1 << 20, None) == -1
+    assert lib.lmoe_ep_pack(C.c_void_p(4100), fake, fake, 4, 128, 2, 8, 2, fake, fake, fake, fake, fake, fake, 1 << 20, None) == -1
+    assert b"aligned" in lib.lmoe_last_error()
+    assert lib.lmoe_ep_pack(fake, fake, fake, 4, 128, 2, 8, 2, fake, fake, fake, fake, fake, fake, 16, None) == -4
+    assert lib.lmoe_ep_pack_workspace_bytes(8, 4) >= 8 * 4 + 8 * 4 * 4
+    assert lib.lmoe_ep_combine(None, fake, None, 4, 2, 128, fake, None) == -1
+    assert lib.lmoe_ep_combine(fake, fake, None, 4, 0, 128, fake, None) == -1
+    assert lib.lmoe_ep_combine(fake, fake, None, 0, 2, 128, fake, None) == 0
+    assert lib.lmoe_experts_forward_rows_f16(None, fake, fake, fake, 4, fake, fake, 1 << 20, None) == -1
+
+
 def test_host_mirror_rejects_cpu_tensors():
     import torch
 

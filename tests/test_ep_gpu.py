@@ -36,6 +36,73 @@ def test_rows_entry_points_single_gpu(orc):
     torch.cuda.synchronize()
 
 
+def test_rows_f16_equals_f32_rows(orc):
+    """The half-precision wire format gives the same result as the same values passed as f32."""
+    from maxuna_b200.moe import MoeBlock
+
+    dev = torch.device("cuda:0")
+    blk = MoeBlock.random(256, 512, 8, 2, seed=43, device=dev, weight_std=0.25)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    rows = 130
+    x16 = torch.randn(rows, 256, generator=gen, device=dev).to(torch.float16)
+    ids = torch.randint(0, 8, (rows,), generator=gen, device=dev, dtype=torch.int32)
+    w = torch.rand(rows, generator=gen, device=dev)
+    a = blk.experts_forward_rows(x16, ids, w)
+    b = blk.experts_forward_rows(x16.to(torch.float32), ids, w)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_pack_and_combine_match_the_index_arithmetic(world):
+    """lmoe_ep_pack / lmoe_ep_combine against the torch plan they replace (one device, any world size)."""
+    from maxuna_b200._native import check, lib
+    from maxuna_b200.gguf import stream_ptr
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    t, h, k, ne = 37, 128, 3, 8
+    x = torch.randn(t, h, generator=gen, device=dev)
+    # distinct experts per token, arbitrary order
+    ids = torch.stack([torch.randperm(ne, generator=gen, device=dev)[:k] for _ in range(t)]).to(torch.int32)
+    w = torch.rand(t, k, generator=gen, device=dev)
+    n = t * k
+    rows = torch.empty(n, h, dtype=torch.float16, device=dev)
+    lids = torch.empty(n, dtype=torch.int32, device=dev)
+    rw = torch.empty(n, dtype=torch.float32, device=dev)
+    pos = torch.empty(n, dtype=torch.int32, device=dev)
+    counts = torch.empty(world, dtype=torch.int64, device=dev)
+    ws = torch.empty(lib().lmoe_ep_pack_workspace_bytes(ne, t), dtype=torch.uint8, device=dev)
+    check(lib().lmoe_ep_pack(x.data_ptr(), ids.data_ptr(), w.data_ptr(), t, h, k, ne, world, rows.data_ptr(), lids.data_ptr(),
+                             rw.data_ptr(), pos.data_ptr(), counts.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
+    torch.cuda.synchronize()
+    e_local = ne // world
+    flat = ids.reshape(-1).to(torch.int64)
+    assert counts.tolist() == torch.bincount(flat // e_local, minlength=world).tolist()
+    p = pos.to(torch.int64)
+    assert sorted(p.tolist()) == list(range(n))                      # a permutation
+    dest_sorted = torch.empty(n, dtype=torch.int64, device=dev)
+    dest_sorted[p] = flat // e_local
+    assert bool(torch.all(dest_sorted[1:] >= dest_sorted[:-1]))      # grouped by destination rank
+    assert torch.equal(rows[p], x.to(torch.float16).repeat_interleave(k, dim=0))
+    assert torch.equal(lids.to(torch.int64)[p], flat % e_local)
+    assert torch.equal(rw[p], w.reshape(-1))
+    # return leg: rows come back in the order they were sent
+    back = torch.randn(n, h, generator=gen, device=dev)
+    shared = torch.randn(t, h, generator=gen, device=dev)
+    out = torch.empty(t, h, device=dev)
+    check(lib().lmoe_ep_combine(back.data_ptr(), pos.data_ptr(), shared.data_ptr(), t, k, h, out.data_ptr(), stream_ptr()))
+    torch.cuda.synchronize()
+    want = torch.zeros(t, h, device=dev)
+    y3 = back[p].view(t, k, h)
+    for s_ in range(k):
+        want += y3[:, s_]
+    want += shared
+    assert torch.equal(out, want)
+
+
 def _ep_worker(rank, world, port, q):
     import sys
 
