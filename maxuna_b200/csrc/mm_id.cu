@@ -815,7 +815,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 //   warps 0-7 dequant    warp 8 B loader    warp 9 MMA issuer    warps 10-13 epilogue
 constexpr int DN_DQ_WARPS = 16;                       // dequant warps
 constexpr int DN_THREADS = (DN_DQ_WARPS + 6) * 32;    // + B loader, MMA issuer, four epilogue warps
-constexpr int DN_NSA = 4, DN_NSB = 2;
+constexpr int DN_NSA = 3, DN_NSB = 2;
 
 struct DnParams {
     const uint8_t *w; // down stack (Q6_K)
@@ -831,132 +831,111 @@ struct DnParams {
     uint32_t *flag;
 };
 
-// Predicated global loads that leave 0 in the register when off (no select after the load, so nothing
-// waits for the data until it is really used).
-__device__ __forceinline__ uint32_t ldg32_if(const void *p, bool on) {
-    uint32_t v = 0u;
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q ld.global.nc.u32 %0, [%1];\n\t}" : "+r"(v) : "l"(p), "r"((uint32_t)on));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg16_if(const void *p, bool on) {
-    uint32_t v = 0u;
-    asm volatile("{\n\t.reg .pred q;\n\t.reg .b16 t;\n\tsetp.ne.u32 q, %2, 0;\n\tmov.b16 t, 0;\n\t@q ld.global.nc.u16 t, [%1];\n\tcvt.u32.u16 %0, t;\n\t}"
-                 : "=r"(v) : "l"(p), "r"((uint32_t)on));
+// Predicated 16-byte global load that leaves zeros when off (no select after the load, so nothing waits
+// for the data until it is really used).
+__device__ __forceinline__ uint4 ldg128_if(const void *p, bool on) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t@q ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+                 : "l"(p), "r"((uint32_t)on));
     return v;
 }
 
-// Down-projection dequant, one (super-block b, 128-weight half n) of the tile's 256 rows at a time:
-//   load   eight lanes per row read aligned 32-bit words side by side (coalesced), nothing else;
-//   stage  the words go to a shared-memory row per weight row (32 words, 16-byte chunks XOR-swizzled);
-//   row    one thread per weight row turns its 128 weights into f16 (each sub-block scale serves 16).
-// Super-blocks are 210 bytes, so odd ones start 2 bytes off a word boundary (MIS): their words are loaded
-// from the aligned addresses around them and re-aligned by byte permutes in the row step.
-// Word slots of a staged row:  aligned: 0-7 ql, 8-15 ql+32, 16-23 qh, 24-25 scales, 26 d (low half)
-//                              MIS:     0-16 ql window, 17-25 qh window, 26-28 scales window, 29 d (high half)
-constexpr int DN_RAWP = 128;
-constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP;
+// Down-projection dequant, one super-block column b of the tile's 256 rows at a time:
+//   load   the 210 bytes of (row, b) lie inside a 16-byte aligned window of 224 bytes; 14 lanes read one
+//          window with 16-byte loads (two rows per warp instruction: whole cache lines per request);
+//   stage  the windows go to shared memory, one row of 228 bytes per weight row (an odd number of words,
+//          so the per-row reads below spread over the banks);
+//   row    for each 128-weight half, one thread per (row, 16-wide l range) picks its ql / qh / scale
+//          bytes out of the window - at the byte offset the block has inside it, re-aligned with funnel
+//          shifts - and converts 64 weights with one scale each.
+constexpr int DN_WIN = 224;                         // window bytes per (row, super-block)
+constexpr int DN_RAWP = 228;                        // shared-memory pitch of a staged window
+constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP + 64; // + slack: a re-aligning read may touch 16 bytes past a window
+constexpr int DN_LPT = 2 * MM_M / (DN_DQ_WARPS * 2); // window loads per thread (two rows per warp instruction)
 
-constexpr int DN_RPT = 2 * MM_M / (DN_DQ_WARPS * 4); // rows per thread in the load / stage steps
-struct DnRegs {
-    uint32_t a[DN_RPT], b[DN_RPT], h[DN_RPT], x[DN_RPT];
+struct DnWin {
+    uint4 v[DN_LPT];
 };
 
-template <bool MIS>
-__device__ __forceinline__ void dn_load(DnRegs &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int n, int w,
-                                        int row0) {
-#ifdef DN_DBG_NOLOAD
+__device__ __forceinline__ void dn_load(DnWin &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int warp, int lane) {
+    const int sub = lane / 14, piece = lane - 14 * sub; // lanes 28-31 idle
 #pragma unroll
-    for (int i = 0; i < DN_RPT; i++) { R.a[i] = 0x12345678u + i; R.b[i] = 0x9abcdef0u + w; R.h[i] = 0x55aa55aau; R.x[i] = 0x3c003c00u; }
-    return;
-#endif
-#pragma unroll
-    for (int i = 0; i < DN_RPT; i++) {
-        const int row = row0 + DN_DQ_WARPS * 4 * i;
-        const bool on = row < rows_valid;
-        const uint8_t *blk = tile_w + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES - (MIS ? 2 : 0);
-        R.a[i] = ldg32_if(blk + 64 * n + 4 * w, on);
-        R.b[i] = ldg32_if(blk + 64 * n + 32 + 4 * w, on);
-        R.h[i] = ldg32_if(blk + 128 + 32 * n + 4 * w, on);
-        if (MIS) {
-            // lane 0: tail of the ql window, 1: tail of the qh window, 2-4: scales window, 5: word holding d
-            const int off = w == 0 ? 64 * n + 64 : w == 1 ? 128 + 32 * n + 32 : w < 5 ? 192 + 8 * n + 4 * (w - 2) : 208;
-            R.x[i] = ldg32_if(blk + off, on && w < 6);
-        } else {
-            // lanes 0, 1: the eight scales of the half, lane 2: d
-            if (w == 2) R.x[i] = ldg16_if(blk + 208, on);
-            else R.x[i] = ldg32_if(blk + 192 + 8 * n + 4 * (w & 1), on && w < 2);
-        }
+    for (int i = 0; i < DN_LPT; i++) {
+        const int row = 2 * warp + sub + 2 * DN_DQ_WARPS * i;
+        const bool on = lane < 28 && row < rows_valid;
+        const uintptr_t blk = reinterpret_cast<uintptr_t>(tile_w) + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES;
+        R.v[i] = ldg128_if(reinterpret_cast<const void *>((blk & ~(uintptr_t)15) + 16 * piece), on);
     }
 }
 
-__device__ __forceinline__ uint32_t dn_slot_off(int row, int slot) {
-    return (uint32_t)(row * DN_RAWP + ((((slot >> 2) ^ (row & 7))) << 4) + ((slot & 3) << 2));
-}
-
-template <bool MIS>
-__device__ __forceinline__ void dn_stage(const DnRegs &R, uint8_t *raw, int w, int row0) {
-    const int xslot = MIS ? (w == 0 ? 16 : w == 1 ? 25 : 24 + w) : 24 + w;
-    const bool xon = MIS ? w < 6 : w < 3;
+__device__ __forceinline__ void dn_stage(const DnWin &R, uint8_t *raw, int warp, int lane) {
+    const int sub = lane / 14, piece = lane - 14 * sub;
+    if (lane >= 28) return;
 #pragma unroll
-    for (int i = 0; i < DN_RPT; i++) {
-        const int row = row0 + DN_DQ_WARPS * 4 * i;
-        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, w)) = R.a[i];
-        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, 8 + w)) = R.b[i];
-        *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, (MIS ? 17 : 16) + w)) = R.h[i];
-        if (xon) *reinterpret_cast<uint32_t *>(raw + dn_slot_off(row, xslot)) = R.x[i];
+    for (int i = 0; i < DN_LPT; i++) {
+        const int row = 2 * warp + sub + 2 * DN_DQ_WARPS * i;
+        uint32_t *dst = reinterpret_cast<uint32_t *>(raw + row * DN_RAWP + 16 * piece);
+        dst[0] = R.v[i].x; dst[1] = R.v[i].y; dst[2] = R.v[i].z; dst[3] = R.v[i].w;
     }
 }
 
-// One thread = (weight row, half lh of the l range): 64 weights (4 groups x 16 l, one sub-block scale each)
-// -> eight 16-byte chunks of two consecutive k-stages (groups 0,1 -> the even stage, 2,3 -> the odd one).
-template <bool MIS>
-__device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_even, uint8_t *st_odd, int row, int lh) {
-    const uint8_t *rr = raw + row * DN_RAWP;
-    const int sw = row & 7;
-    auto chunk = [&](int c) { return *reinterpret_cast<const uint4 *>(rr + ((c ^ sw) << 4)); };
-    uint32_t QA[4], QB[4], QH[4], S0, S1, dbits;
-    if (MIS) {
-        // ql window words 4lh .. 4lh+4 and 8+4lh .. 12+4lh, qh window words 17+4lh .. 21+4lh
-        const uint4 a = chunk(lh), a2 = chunk(lh + 1), b = chunk(2 + lh), b2 = chunk(3 + lh);
-        QA[0] = __byte_perm(a.x, a.y, 0x5432); QA[1] = __byte_perm(a.y, a.z, 0x5432);
-        QA[2] = __byte_perm(a.z, a.w, 0x5432); QA[3] = __byte_perm(a.w, a2.x, 0x5432);
-        QB[0] = __byte_perm(b.x, b.y, 0x5432); QB[1] = __byte_perm(b.y, b.z, 0x5432);
-        QB[2] = __byte_perm(b.z, b.w, 0x5432); QB[3] = __byte_perm(b.w, b2.x, 0x5432);
-        const uint4 h = chunk(4 + lh), h2 = chunk(5 + lh), t6 = chunk(6), t7 = chunk(7);
-        // words 17+4lh..: lh = 0 -> h.y h.z h.w h2.x h2.y ; lh = 1 -> h.y .. of chunks 5, 6
-        QH[0] = __byte_perm(h.y, h.z, 0x5432); QH[1] = __byte_perm(h.z, h.w, 0x5432);
-        QH[2] = __byte_perm(h.w, h2.x, 0x5432); QH[3] = __byte_perm(h2.x, h2.y, 0x5432);
-        S0 = __byte_perm(t6.z, t6.w, 0x5432); // words 26, 27
-        S1 = __byte_perm(t6.w, t7.x, 0x5432); // words 27, 28
-        dbits = t7.y >> 16;                   // word 29
-    } else {
-        const uint4 a = chunk(lh), b = chunk(2 + lh), h = chunk(4 + lh), t6 = chunk(6);
-        QA[0] = a.x; QA[1] = a.y; QA[2] = a.z; QA[3] = a.w;
-        QB[0] = b.x; QB[1] = b.y; QB[2] = b.z; QB[3] = b.w;
-        QH[0] = h.x; QH[1] = h.y; QH[2] = h.z; QH[3] = h.w;
-        S0 = t6.x; S1 = t6.y;
-        dbits = t6.z & 0xffffu;
+// 16 bytes at byte offset `o` (even) of a staged window, as four words
+__device__ __forceinline__ void dn_read16(const uint8_t *rowp, int o, uint32_t (&out)[4]) {
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(rowp) + (o >> 2);
+    const uint32_t sh = (uint32_t)(o & 3) * 8u;
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+    out[0] = __funnelshift_r(w0, w1, sh);
+    out[1] = __funnelshift_r(w1, w2, sh);
+    out[2] = __funnelshift_r(w2, w3, sh);
+    out[3] = __funnelshift_r(w3, w4, sh);
+}
+
+// The fields of (row, half n, l range lh) out of the staged window whose block starts at byte `sh`.
+struct DnFields {
+    uint32_t qa[4], qb[4], qh[4], s0, s1;
+    float d;
+};
+__device__ __forceinline__ void dn_fields(const uint8_t *rowp, int sh, int n, int lh, DnFields &F) {
+    dn_read16(rowp, sh + 64 * n + 16 * lh, F.qa);
+    dn_read16(rowp, sh + 64 * n + 32 + 16 * lh, F.qb);
+    dn_read16(rowp, sh + 128 + 32 * n + 16 * lh, F.qh);
+    {
+        const int o = sh + 192 + 8 * n;
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(rowp) + (o >> 2);
+        const uint32_t s = (uint32_t)(o & 3) * 8u;
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+        F.s0 = __funnelshift_r(w0, w1, s);
+        F.s1 = __funnelshift_r(w1, w2, s);
     }
-    const float d = lmoe_h2f((uint16_t)dbits);
-    uint8_t *base_e = st_even + (row >> 7) * A_STAGE_BYTES, *base_o = st_odd + (row >> 7) * A_STAGE_BYTES;
+    {
+        const int o = sh + 208;
+        const uint32_t w = reinterpret_cast<const uint32_t *>(rowp)[o >> 2];
+        F.d = lmoe_h2f((uint16_t)((w >> ((o & 2) * 8)) & 0xffffu));
+    }
+}
+
+// Groups 2*hn and 2*hn+1 (low nibbles: hn = 0, the even k-stage; high nibbles: hn = 1, the odd one) of
+// one (row, l range): 32 weights -> four 16-byte chunks of the stage.
+__device__ __forceinline__ void dn_dequant_stage(const DnFields &F, int hn, uint8_t *stage, int row, int lh) {
+    uint8_t *base = stage + (row >> 7) * A_STAGE_BYTES;
     const int r = row & 127;
+    const uint32_t ml = hn ? 0x00F000F0u : 0x000F000Fu, mh = hn ? 0x03000300u : 0x00300030u;
+    const uint32_t off = hn ? 0x66006600u : 0x64206420u;
+    const uint32_t scw = hn ? F.s1 : F.s0;
 #pragma unroll
-    for (int gi = 0; gi < 4; gi++) {
-        const bool hi_nib = gi & 2;
-        const uint32_t ml = hi_nib ? 0x00F000F0u : 0x000F000Fu, mh = hi_nib ? 0x03000300u : 0x00300030u;
-        const uint32_t off = hi_nib ? 0x66006600u : 0x64206420u;
-        // scale 2*gi + lh of this half: byte (2*gi + lh) & 3 of word (2*gi + lh) >> 2
-        const uint32_t scw = gi < 2 ? S0 : S1;
-        const int sb = (int)(int8_t)((scw >> (8 * (2 * (gi & 1) + lh))) & 0xff);
-        const __half2 sc = __float2half2_rn(d * (float)sb * (hi_nib ? 0.0625f : 1.0f));
+    for (int g1 = 0; g1 < 2; g1++) { // gi = 2*hn + g1
+        // scale 2*gi + lh of this half: byte 2*g1 + lh of the word
+        const int sb = (int)(int8_t)((scw >> (8 * (2 * g1 + lh))) & 0xff);
+        const __half2 sc = __float2half2_rn(F.d * (float)sb * (hn ? 0.0625f : 1.0f));
 #pragma unroll
         for (int m = 0; m < 2; m++) {
             uint32_t o[4];
 #pragma unroll
             for (int jj = 0; jj < 2; jj++) {
                 const int j = 2 * m + jj;
-                const uint32_t q = (gi & 1) ? QB[j] : QA[j], hh = QH[j];
-                const uint32_t h02 = (gi & 1) ? (hh << 2) : (hh << 4), h13 = (gi & 1) ? (hh >> 6) : (hh >> 4);
+                const uint32_t q = g1 ? F.qb[j] : F.qa[j], hh = F.qh[j];
+                const uint32_t h02 = g1 ? (hh << 2) : (hh << 4), h13 = g1 ? (hh >> 6) : (hh >> 4);
                 const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
                 const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
                 const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
@@ -964,8 +943,7 @@ __device__ __forceinline__ void dn_dequant_row(const uint8_t *raw, uint8_t *st_e
                 o[2 * jj] = *reinterpret_cast<const uint32_t *>(&d02);
                 o[2 * jj + 1] = *reinterpret_cast<const uint32_t *>(&d13);
             }
-            *reinterpret_cast<uint4 *>((hi_nib ? base_o : base_e) + swz_off(r, 4 * (gi & 1) + 2 * lh + m)) =
-                make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4 *>(base + swz_off(r, 4 * g1 + 2 * lh + m)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
@@ -1013,7 +991,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
 
     if (warp < DN_DQ_WARPS) {
         // ---------------- dequant ----------------
-        const int w = tid & 7, row0 = tid >> 3; // load / stage steps: word w of rows row0, row0 + 64, ...
         const int drow = tid & (2 * MM_M - 1), dlh = tid / (2 * MM_M); // convert step: (row, l half)
         uint32_t g = 0;
         bool ok = true;
@@ -1023,45 +1000,37 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
             const int rows_valid = min(2 * MM_M, P.n_out - m0);
             const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
-            const bool mis0 = (reinterpret_cast<uintptr_t>(tw) & 2) != 0; // parity of even blocks (row_bytes % 4 == 0 when n_blk is even)
-            // loads run two halves ahead of their use, in two register sets
-            DnRegs R0, R1;
-            auto load = [&](DnRegs &R, int it) {
-                if (it >= 2 * n_blk) return;
-                const int b = it >> 1, n = it & 1;
-                if (mis0 != ((b & 1) != 0)) dn_load<true>(R, tw, row_bytes, rows_valid, b, n, w, row0);
-                else dn_load<false>(R, tw, row_bytes, rows_valid, b, n, w, row0);
-            };
-            auto half = [&](DnRegs &R, int it) {
-                const int b = it >> 1;
-                const bool mis = mis0 != ((b & 1) != 0);
+            const uint8_t *rowp = raw + drow * DN_RAWP;
+            DnWin R;
+            dn_load(R, tw, row_bytes, rows_valid, 0, warp, lane);
+            for (int b = 0; b < n_blk; b++) {
                 if (tid == 0) DSTAMP(0, g >> 1, 0);
-                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the staged rows of the previous half are consumed
-                if (mis) dn_stage<true>(R, raw, w, row0);
-                else dn_stage<false>(R, raw, w, row0);
-                load(R, it + 2);
+                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the previous column's windows are consumed
+                dn_stage(R, raw, warp, lane);
+                // the next column is requested now and only touched after this one is converted
+                if (b + 1 < n_blk) dn_load(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
                 asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory");
                 if (tid == 0) DSTAMP(0, g >> 1, 1);
-                const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
-                ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3) &&
-                     mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
-                if (tid == 0) DSTAMP(0, g >> 1, 2);
-                if (mis) dn_dequant_row<true>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
-                else dn_dequant_row<false>(raw, a_st + (size_t)s0 * GU_A_STAGE, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
-                if (tid == 0) DSTAMP(0, g >> 1, 3);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    mb_arrive(&a_full[s0]);
-                    mb_arrive(&a_full[s1]);
+                // byte offset of this row's block inside its window
+                const int sh = (int)((reinterpret_cast<uintptr_t>(tw) + (size_t)drow * row_bytes + (size_t)b * Q6K_BYTES) & 15u);
+#pragma unroll 1
+                for (int n = 0; n < 2; n++, g += 2) {
+                    DnFields F;
+                    dn_fields(rowp, sh, n, dlh, F);
+                    const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
+                    ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3);
+                    if (tid == 0) DSTAMP(0, g >> 1, 2);
+                    dn_dequant_stage(F, 0, a_st + (size_t)s0 * GU_A_STAGE, drow, dlh);
+                    ok = ok && mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
+                    dn_dequant_stage(F, 1, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
+                    if (tid == 0) DSTAMP(0, g >> 1, 3);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mb_arrive(&a_full[s0]);
+                        mb_arrive(&a_full[s1]);
+                    }
                 }
-                g += 2;
-            };
-            load(R0, 0);
-            load(R1, 1);
-            for (int it = 0; it < 2 * n_blk; it += 2) {
-                half(R0, it);
-                half(R1, it + 1);
             }
         }
     } else if (warp == DN_DQ_WARPS) {
