@@ -43,6 +43,7 @@ constexpr int DEC_THREADS = 32 * (CW + 2); // + producer warp + epilogue warp
 constexpr int RING_THREADS = 32 * (CW + 1); // consumers + producer
 constexpr int EPI_THREADS = 32 * (CW + 1);  // consumers + epilogue warp
 constexpr int NSTAGE = 3;
+constexpr int NRED = 3;          // K-split partial buffers between the consumers and the epilogue warp
 constexpr int NTOK = 2;         // tokens per pass over an expert's weights
 constexpr int NCOL = 2 * NTOK;  // MMA columns in use: (token, hi/lo)
 constexpr int DEC_MAX_T = 16;
@@ -91,7 +92,7 @@ struct DecLayout {
         o_s = o; o += NCOL * ss * 2;
         // the K-split partial buffers (phases 1-2) share their space with two routing tables that are
         // only alive while the token lists are built: expert counts and the id list
-        int red_bytes = 2 * CW * 16 * NCOL * 4;
+        int red_bytes = NRED * CW * 16 * NCOL * 4;
         if (red_bytes < (n_expert + tk) * 4) red_bytes = (n_expert + tk) * 4;
         o_red = o; o_cnt = o; o_ids = o + n_expert * 4;
         o += (red_bytes + 15) / 16 * 16;
@@ -520,7 +521,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     float *red = reinterpret_cast<float *>(smem + L.o_red);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.o_bar);
     uint64_t *empty = full + NSTAGE;
-    uint64_t *red_full = empty + NSTAGE, *red_free = red_full + 2; // K-split partial buffers: consumers -> epilogue warp
+    uint64_t *red_full = empty + NSTAGE, *red_free = red_full + NRED; // K-split partial buffers: consumers -> epilogue warp
     uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + L.o_ids);
     float *w_s = reinterpret_cast<float *>(smem + L.o_w);
     uint32_t *cnt_s = reinterpret_cast<uint32_t *>(smem + L.o_cnt);
@@ -544,7 +545,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CW);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < NRED; b++) {
             mbar_init(&red_full[b], CW);
             mbar_init(&red_free[b], 1);
         }
@@ -633,8 +634,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 int q = u0 / tiles, tile = u0 - q * tiles;
                 Unit U = make_pass(P, T, shared, q);
                 for (int u = u0; u < u1; u++, m++) {
-                    const int buf = m & 1;
-                    mbar_wait<100>(&red_full[buf], (m >> 1) & 1, P.ctrl, 0x30 + phase);
+                    const int buf = m % NRED;
+                    mbar_wait<100>(&red_full[buf], (m / NRED) & 1, P.ctrl, 0x30 + phase);
                     const float *rb = red + buf * (CW * 16 * NCOL);
                     if (phase == 1) {
                         // SwiGLU: rows 0-7 gate, 8-15 up; lane = tok*8 + row
@@ -693,67 +694,64 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     if (P.first_launch && blockIdx.x == 0 && tid < 4) P.ctrl[tid] = 0u; // a fresh device flag for this call
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
     if (P.hidden == 128 * 24) {
-        // Work item = (expert, group of four tokens), spread over every warp of the grid.  The router row
-        // is held in registers half a row at a time (all loads of a half in flight at once); hidden states
-        // are staged as f32, as many tokens per round as the (not yet used) weight ring + activation cache
-        // hold.  Each of the 128 partial chains still runs over its 24 elements in order.
+        // Work item = (expert, group of four tokens).  A CTA serves ONE token group (CTA c: group c mod
+        // #groups), so it stages only those four hidden states (as f32, in the not yet used weight ring);
+        // the CTAs of a group share out the experts, one per warp.  The router row is held in registers
+        // half a row at a time (all loads of a half in flight at once).  Each of the 128 partial chains
+        // still runs over its 24 elements in order.
         constexpr int HH = 12;
         const int H = P.hidden;
         float *xs32 = reinterpret_cast<float *>(ring);
-        const int xt_cap = max(4, (L.o_s - L.o_ring) / (H * 4) / 4 * 4);
+        const int ngr = (P.t + 3) / 4;
+        const int cg = blockIdx.x % ngr, ci = blockIdx.x / ngr;
+        const int n_cta = (G - cg + ngr - 1) / ngr; // CTAs serving this group
+        const int t0 = 4 * cg, nt = min(4, P.t - t0);
         float4 wv[HH];
         bool preloaded = false;
         {
             // the first item's first half row is requested before the hidden states are staged
-            const int item = blockIdx.x + G * warp;
-            const int ngr = (min(xt_cap, P.t) + 3) / 4;
-            if (item < E * ngr) {
-                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)(item / ngr) * H) + lane;
+            const int e = ci + n_cta * warp;
+            if (e < E) {
+                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
 #pragma unroll
                 for (int j = 0; j < HH; j++) wv[j] = __ldg(wr + 32 * j);
                 preloaded = true;
             }
         }
-        for (int t0 = 0; t0 < P.t; t0 += xt_cap) {
-            const int nt = min(xt_cap, P.t - t0);
-            const int ngr = (nt + 3) / 4;
-            bar_sync(1, CW * 32);
-            for (int i = tid; i < nt * (H / 4); i += CW * 32)
-                reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
-            bar_sync(1, CW * 32);
-            for (int item = blockIdx.x + G * warp; item < E * ngr; item += G * CW) {
-                const int e = item / ngr, i0 = (item - e * ngr) * 4;
-                const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
-                float a[4][4];
+        for (int i = tid; i < nt * (H / 4); i += CW * 32)
+            reinterpret_cast<float4 *>(xs32)[i] = __ldg(reinterpret_cast<const float4 *>(P.x + (size_t)t0 * H) + i);
+        bar_sync(1, CW * 32);
+        for (int e = ci + n_cta * warp; e < E; e += n_cta * CW) {
+            const float4 *wr = reinterpret_cast<const float4 *>(P.router + (size_t)e * H) + lane;
+            float a[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.f;
+            for (int i = 0; i < 4; i++) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.f;
 #pragma unroll 1
-                for (int half = 0; half < 2; half++) {
-                    if (!(preloaded && half == 0)) {
+            for (int half = 0; half < 2; half++) {
+                if (!(preloaded && half == 0)) {
 #pragma unroll
-                        for (int j = 0; j < HH; j++) wv[j] = __ldg(wr + 32 * (HH * half + j));
-                    }
-                    preloaded = false;
+                    for (int j = 0; j < HH; j++) wv[j] = __ldg(wr + 32 * (HH * half + j));
+                }
+                preloaded = false;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        if (i0 + i < nt) {
-                            const float4 *xr = reinterpret_cast<const float4 *>(xs32 + (i0 + i) * H) + lane + 32 * HH * half;
+                for (int i = 0; i < 4; i++) {
+                    if (i < nt) {
+                        const float4 *xr = reinterpret_cast<const float4 *>(xs32 + i * H) + lane + 32 * HH * half;
 #pragma unroll
-                            for (int j = 0; j < HH; j++) {
-                                const float4 xv = xr[32 * j];
-                                a[i][0] = __fmaf_rn(xv.x, wv[j].x, a[i][0]);
-                                a[i][1] = __fmaf_rn(xv.y, wv[j].y, a[i][1]);
-                                a[i][2] = __fmaf_rn(xv.z, wv[j].z, a[i][2]);
-                                a[i][3] = __fmaf_rn(xv.w, wv[j].w, a[i][3]);
-                            }
+                        for (int j = 0; j < HH; j++) {
+                            const float4 xv = xr[32 * j];
+                            a[i][0] = __fmaf_rn(xv.x, wv[j].x, a[i][0]);
+                            a[i][1] = __fmaf_rn(xv.y, wv[j].y, a[i][1]);
+                            a[i][2] = __fmaf_rn(xv.z, wv[j].z, a[i][2]);
+                            a[i][3] = __fmaf_rn(xv.w, wv[j].w, a[i][3]);
                         }
                     }
                 }
+            }
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float v = lmoe_router_fold(a[i][0], a[i][1], a[i][2], a[i][3]);
-                    if (lane == 0 && i0 + i < nt) P.logits[(size_t)(t0 + i0 + i) * E + e] = v;
-                }
+            for (int i = 0; i < 4; i++) {
+                const float v = lmoe_router_fold(a[i][0], a[i][1], a[i][2], a[i][3]);
+                if (lane == 0 && i < nt) P.logits[(size_t)(t0 + i) * E + e] = v;
             }
         }
     } else {
@@ -1003,8 +1001,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 // K-split partials -> shared memory, handed to the epilogue warp (two buffers in flight)
-                const int buf = n & 1;
-                mbar_wait(&red_free[buf], ((n >> 1) & 1) ^ 1, P.ctrl, 0x28 + phase);
+                const int buf = n % NRED;
+                mbar_wait(&red_free[buf], ((n / NRED) & 1) ^ 1, P.ctrl, 0x28 + phase);
                 float *rb = red + buf * (CW * 16 * NCOL);
                 if (t4 < NTOK) {
                     float *r0 = rb + (warp * 16 + g) * NCOL + 2 * t4;

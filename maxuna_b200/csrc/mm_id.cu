@@ -858,10 +858,12 @@ struct DnWin {
     uint4 v[DN_LPT];
 };
 
+// (issued in two halves, PART = 0 / 1, so that the requests of a column do not all queue at once)
+template <int PART>
 __device__ __forceinline__ void dn_load(DnWin &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int warp, int lane) {
     const int sub = lane / 14, piece = lane - 14 * sub; // lanes 28-31 idle
 #pragma unroll
-    for (int i = 0; i < DN_LPT; i++) {
+    for (int i = PART * (DN_LPT / 2); i < (PART + 1) * (DN_LPT / 2); i++) {
         const int row = 2 * warp + sub + 2 * DN_DQ_WARPS * i;
         const bool on = lane < 28 && row < rows_valid;
         const uintptr_t blk = reinterpret_cast<uintptr_t>(tile_w) + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES;
@@ -1002,13 +1004,15 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
             const uint8_t *rowp = raw + drow * DN_RAWP;
             DnWin R;
-            dn_load(R, tw, row_bytes, rows_valid, 0, warp, lane);
+            dn_load<0>(R, tw, row_bytes, rows_valid, 0, warp, lane);
+            dn_load<1>(R, tw, row_bytes, rows_valid, 0, warp, lane);
             for (int b = 0; b < n_blk; b++) {
                 if (tid == 0) DSTAMP(0, g >> 1, 0);
                 asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the previous column's windows are consumed
                 dn_stage(R, raw, warp, lane);
-                // the next column is requested now and only touched after this one is converted
-                if (b + 1 < n_blk) dn_load(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
+                // the next column is requested now (first half) and between the two conversions (second half),
+                // and only touched after this one is converted
+                if (b + 1 < n_blk) dn_load<0>(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
                 asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory");
                 if (tid == 0) DSTAMP(0, g >> 1, 1);
                 // byte offset of this row's block inside its window
@@ -1030,6 +1034,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                         mb_arrive(&a_full[s0]);
                         mb_arrive(&a_full[s1]);
                     }
+                    if (n == 0 && b + 1 < n_blk) dn_load<1>(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
                 }
             }
         }
