@@ -9,6 +9,8 @@
 #include <new>
 
 #include "common.cuh"
+
+size_t decode_sync_bytes(); // decode.cu
 #include "fused.cuh"
 
 // ---------------------------------------------------------------- errors ----
@@ -312,8 +314,8 @@ extern "C" lmoe_status lmoe_layer_create(int64_t hidden, int64_t expert_ff, int6
                 "shared expert dtypes must match the routed experts'");
     }
     uint32_t *sync = nullptr;
-    LMOE_CUDA(cudaMalloc(&sync, 256));
-    if (cudaMemset(sync, 0, 256) != cudaSuccess) {
+    LMOE_CUDA(cudaMalloc(&sync, decode_sync_bytes()));
+    if (cudaMemset(sync, 0, decode_sync_bytes()) != cudaSuccess) {
         cudaFree(sync);
         return lmoe_fail(LMOE_ERR_CUDA, "could not clear the layer's synchronisation words");
     }

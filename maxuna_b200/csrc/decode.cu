@@ -44,6 +44,8 @@ constexpr int RING_THREADS = 32 * (CW + 1); // consumers + producer
 constexpr int EPI_THREADS = 32 * (CW + 1);  // consumers + epilogue warp
 constexpr int NSTAGE = 3;
 constexpr int NRED = 3;          // K-split partial buffers between the consumers and the epilogue warp
+constexpr int SYNC_PASS0 = 32;   // layer sync words: [0] grid barrier, [1] exit count, [32 + pass] phase-1 units done
+constexpr int SYNC_WORDS = SYNC_PASS0 + 1024;
 constexpr int NTOK = 2;         // tokens per pass over an expert's weights
 constexpr int NCOL = 2 * NTOK;  // MMA columns in use: (token, hi/lo)
 constexpr int DEC_MAX_T = 16;
@@ -60,7 +62,7 @@ struct DecodeParams {
     float scale;
     int norm, has_shared;
     uint32_t *ctrl;   // workspace: [0..3] device flag (zeroed by the launch with first_launch set), [8192..] optional timing stamps
-    uint32_t *sync;   // owned by the layer, zero between launches: [0] grid barrier, [1] exit count
+    uint32_t *sync;   // owned by the layer, zero between launches: [0] grid barrier, [1] exit count, [32..] per-pass counts
     int first_launch;
     float *logits;    // [t][n_expert]
     uint32_t *ids_ws; // [t][top_k] routing decision, written by the CTA that ranked the token
@@ -511,6 +513,25 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define STAMP(i) do { } while (0)
 #endif
 
+// Per-pass hand-over between phases 1 and 2 (small batches).  Out of line on purpose: they run once per
+// pass and must not disturb the register allocation of the unit loops.
+__device__ __noinline__ void dec_publish_pass(uint32_t *cnt, uint32_t add) {
+    __threadfence();
+    atomicAdd(cnt, add);
+}
+__device__ __noinline__ void dec_wait_pass(const uint32_t *cnt, uint32_t need, uint32_t *ctrl, uint32_t where) {
+    uint32_t i = 0;
+    while (ld_acquire(cnt) < need) {
+        if (++i > SPIN_LIMIT) {
+            if (atomicCAS(ctrl, 0u, (uint32_t)LMOE_FLAG_WAIT_TIMEOUT) == 0u) {
+                ctrl[1] = where;
+                ctrl[2] = blockIdx.x;
+            }
+            break;
+        }
+    }
+}
+
 // ---- the kernel ---------------------------------------------------------------------
 __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid_constant__ DecodeParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -539,6 +560,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     const int tiles1 = P.ff / 8, tiles2 = P.hidden / DOWN_ROWS;
     const int shared_passes = P.has_shared ? (P.t + NTOK - 1) / NTOK : 0;
     const size_t gexp = (size_t)P.ff * row4, dexp = (size_t)P.hidden * row6;
+    // Between phases 1 and 2: per-pass completion counters for small batches (latency-bound: no grid barrier,
+    // early passes start early), a grid barrier for larger ones (throughput-bound: the SMs are busy anyway).
+    const bool pass_flags = P.t <= 2;
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; s++) {
@@ -633,6 +657,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 if (u0 >= u1) continue;
                 int q = u0 / tiles, tile = u0 - q * tiles;
                 Unit U = make_pass(P, T, shared, q);
+                // Phase 2 of a pass may start, on any CTA, once all its phase-1 units are done: this CTA adds
+                // the number it finished to the pass's counter whenever it leaves a pass.
+                int done_in_pass = 0;
+                auto publish = [&](int qq) {
+                    if (pass_flags && phase == 1 && done_in_pass > 0) {
+                        __syncwarp();
+                        if (lane == 0) dec_publish_pass(P.sync + SYNC_PASS0 + (shared ? qq : shared_passes + qq), (uint32_t)done_in_pass);
+                        __syncwarp();
+                    }
+                    done_in_pass = 0;
+                };
                 for (int u = u0; u < u1; u++, m++) {
                     const int buf = m % NRED;
                     mbar_wait<100>(&red_full[buf], (m / NRED) & 1, P.ctrl, 0x30 + phase);
@@ -674,15 +709,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&red_free[buf]);
+                    done_in_pass++;
                     if (++tile == tiles && u + 1 < u1) {
                         tile = 0;
+                        publish(q);
                         U = make_pass(P, T, shared, ++q);
                     }
                 }
+                publish(q);
             }
-            // this phase's results are complete: join the consumers' grid barrier
-            __threadfence();
-            bar_arrive(4, EPI_THREADS);
+            // the phase's results are complete: join the consumers' grid barrier (none after phase 1 when the
+            // per-pass counters are in use)
+            if (phase == 2 || !pass_flags) {
+                __threadfence();
+                bar_arrive(4, EPI_THREADS);
+            }
         }
         return;
     }
@@ -975,6 +1016,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             if (u0 >= u1) continue;
             int q = u0 / tiles, tile = u0 - q * tiles;
             Unit U = make_pass(P, T, shared, q);
+            // phase 2 of a pass needs every SwiGLU activation of the pass: wait (bounded) until the pass's
+            // counter shows all its phase-1 units done, on whichever CTAs they ran
+            auto wait_pass = [&](int qq) {
+                if (phase != 2 || !pass_flags) return;
+                if (tid == 0)
+                    dec_wait_pass(P.sync + SYNC_PASS0 + (shared ? qq : shared_passes + qq), (uint32_t)tiles1, P.ctrl, 0x200u + qq);
+                bar_sync(1, CW * 32);
+            };
+            wait_pass(q);
             for (int u = u0; u < u1; u++) {
                 // what the cache holds is identified by the rows staged into it
                 const int key = phase == 1 ? ((1 << 30) | (U.n_tok << 24) | (U.tok[0] << 12) | U.tok[1])
@@ -1015,12 +1065,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 if (++tile == tiles && u + 1 < u1) {
                     tile = 0;
                     U = make_pass(P, T, shared, ++q);
+                    wait_pass(q);
                 }
             }
         }
         STAMP(phase == 1 ? 4 : 6);
-        grid_barrier(P.ctrl, P.sync, (uint32_t)((phase + 2) * G), tid, 4, EPI_THREADS);
-        STAMP(phase == 1 ? 5 : 7);
+        if (phase == 2 || !pass_flags) {
+            grid_barrier(P.ctrl, P.sync, (uint32_t)((pass_flags ? 3 : phase + 2) * G), tid, 4, EPI_THREADS);
+            STAMP(phase == 1 ? 5 : 7);
+        }
     }
 
     // ---- phase 3: out[t, :] = sum over slots (then the shared expert) of the weighted partial rows,
@@ -1051,6 +1104,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         if (old == (uint32_t)(G - 1)) {
             P.sync[0] = 0u;
             P.sync[1] = 0u;
+            const int n_pass = shared_passes + T.routed_passes;
+            if (pass_flags)
+                for (int i = 0; i < n_pass && i < SYNC_WORDS - SYNC_PASS0; i++) P.sync[SYNC_PASS0 + i] = 0u;
             __threadfence();
         }
     }
@@ -1069,6 +1125,7 @@ size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k
 }
 
 int decode_max_tokens() { return DEC_MAX_T; }
+size_t decode_sync_bytes() { return (size_t)SYNC_WORDS * 4; }
 
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
                               float *w_out, void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream) {
@@ -1078,7 +1135,8 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
     if (t < 1 || t > DEC_MAX_T) return lmoe_fail(LMOE_ERR_INVALID, "decode launch takes 1..%d tokens, got %d", DEC_MAX_T, t);
     if (H % 128 || F % 16 || 16 + t * (H / 16) > 16384)
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "fused decode needs hidden %% 128 == 0, expert_ff %% 16 == 0 and t*hidden/16 <= 16368");
-    if (t * K > 65535) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "t*top_k too large");
+    if (t * K > 65535 || (t + NTOK - 1) / NTOK + t * K > SYNC_WORDS - SYNC_PASS0)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "t*top_k too large");
     const DecLayout L(H, F, E, t, K);
     // device facts and the kernel's shared-memory opt-in are looked up once per (device, size)
     static thread_local int c_dev = -1, c_sms = 0, c_max_smem = 0, c_total = -1, c_occ = 0;
