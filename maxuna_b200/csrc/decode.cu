@@ -10,7 +10,7 @@
 //
 // Structure (the path is HBM-bound: 70.5 MB per token at the production shape)
 //   * grid = every SM x 2 CTAs, launched cooperatively so all CTAs are resident;
-//     CTA = 1 producer warp + 4 consumer warps.
+//     CTA = 4 consumer warps + 1 producer warp + 1 epilogue warp.
 //   * The producer streams raw super-blocks global -> shared with 1-D bulk
 //     copies (cp.async.bulk + mbarrier) through a 3-stage ring: each DISTINCT
 //     selected expert (and the shared expert) is read from HBM exactly once per
@@ -23,11 +23,16 @@
 //     scales are applied to the f32 accumulator fragments; the Q4_K "min" term
 //     and the Q6_K "-32" offset are one extra MMA per super-block against
 //     per-sub-block activation sums.
-//   * Work units (8 gate+8 up rows, or 16 down rows, of one expert) are split
+//   * Work units (8 gate+8 up rows, or 32 down rows, of one expert) are split
 //     contiguously over CTAs; the K dimension of a unit is split over the four
-//     consumer warps and reduced in shared memory in a fixed order.
-//   * Phases are separated by bounded grid barriers; the producer runs ahead of
-//     them (weights do not depend on them), which keeps HBM busy across phases.
+//     consumer warps, whose partial sums go through mbarrier-guarded shared-memory
+//     buffers to the epilogue warp: it adds them in a fixed order and writes the
+//     SwiGLU activations / weighted partial rows, so the consumer warps never wait
+//     for one another inside a phase.
+//   * Phases are separated by bounded grid barriers (for one or two tokens the one
+//     between the two projections is replaced by per-pass completion counters);
+//     the producer runs ahead of them (weights do not depend on them), which keeps
+//     HBM busy across phases.
 //   * The down projection writes weighted partial rows; a last phase sums the
 //     K+1 partials of every output element in slot order, so the result is
 //     deterministic without float atomics.
@@ -1042,12 +1047,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 // MMA columns beyond the staged ones alias them: their results are never read
                 const int col = g & (NCOL - 1);
-#ifndef DEC_DBG_NOCOMPUTE
                 if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
                 else unit_q6k(stage, row6, nb6, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
-#else
-                acc[0] = stage[lane * 16];
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 // K-split partials -> shared memory, handed to the epilogue warp (two buffers in flight)

@@ -83,9 +83,6 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes
     if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0 || bytes == 0) return; // a hint only: skipped when not aligned
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
-}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -214,19 +211,23 @@ __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__rest
     if (e == 32)
         for (int i = 1; i <= 512; i++) rpre[i] += rpre[i - 1];
     __syncthreads();
-    if (e < n_expert) {
-        int o = pre[e];
-        const int rows = (int)tpe[e];
-        for (int n0 = 0; n0 < rows; n0 += MM_N)
-            for (int m = 0; m < m_tiles; m++, o++) {
-                if (o >= max_tiles) break;
-                tiles[8 * o + 0] = e;
-                tiles[8 * o + 1] = n0;
-                tiles[8 * o + 2] = min(MM_N, rows - n0);
-                tiles[8 * o + 3] = m * m_step;
-                tiles[8 * o + 4] = pre[e] / m_tiles + n0 / MM_N;
-                tiles[8 * o + 5] = rpre[e] + n0; // first row of the tile in expert-sorted row order
-            }
+    // every thread takes tiles idx, idx + 512, ...; the expert of a tile is found in the prefix table
+    const int total = min(pre[512], max_tiles);
+    for (int o = threadIdx.x; o < total; o += 512) {
+        int lo = 0, hi = n_expert - 1;
+        while (lo < hi) { // last expert whose first tile is <= o
+            const int mid = (lo + hi + 1) >> 1;
+            if (pre[mid] <= o) lo = mid; else hi = mid - 1;
+        }
+        const int ex = lo, rel = o - pre[ex];
+        const int nt = rel / m_tiles, m = rel - nt * m_tiles, n0 = nt * MM_N;
+        const int rows = (int)tpe[ex];
+        tiles[8 * o + 0] = ex;
+        tiles[8 * o + 1] = n0;
+        tiles[8 * o + 2] = min(MM_N, rows - n0);
+        tiles[8 * o + 3] = m * m_step;
+        tiles[8 * o + 4] = pre[ex] / m_tiles + nt;
+        tiles[8 * o + 5] = rpre[ex] + n0; // first row of the tile in expert-sorted row order
     }
     if (e == 0) *n_tiles = min(pre[512], max_tiles);
 }
@@ -382,12 +383,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                     if (lane == 0) mb_expect_tx(&raw_full[slot], (uint32_t)vrows * Q4K_BYTES);
                     __syncwarp();
                     uint8_t *dst = raw + (size_t)slot * raw_slot_stride;
-#ifdef MM_DBG_NORAW
-                    if (lane == 0) bulk_g2s(dst, wt, (uint32_t)vrows * Q4K_BYTES, &raw_full[slot]);
-                    for (int r = lane; r < 0; r += 32)
-#else
                     for (int r = lane; r < vrows; r += 32)
-#endif
                         bulk_g2s(dst + r * Q4K_BYTES, wt + (size_t)r * row_bytes + (size_t)sb * Q4K_BYTES, Q4K_BYTES,
                                  &raw_full[slot]);
                 }
@@ -423,11 +419,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 if (tid == 32) MSTAMP(0, g, 2);
                 uint8_t *ast = a_st + (size_t)s * A_STAGE_BYTES;
                 const uint8_t *rs = raw + (size_t)slot * raw_slot_stride;
-#ifdef MM_DBG_NODEQ
-                if (false) {
-#else
                 if (rvalid) {
-#endif
                     if (DT == LMOE_Q4_K) dequant_q4k_row32(rs + r * Q4K_BYTES, ks & 3, half, ast, r);
                     else dequant_q6k_row32(rs + (size_t)r * row_bytes + (ks >> 2) * Q6K_BYTES, ks & 3, half, ast, r);
                 } else {
@@ -435,9 +427,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                     for (int c = 0; c < 4; c++)
                         *reinterpret_cast<uint4 *>(ast + swz_off(r, c + 4 * half)) = make_uint4(0u, 0u, 0u, 0u);
                 }
-#ifndef MM_DBG_NOFENCE
                 fence_async_smem();
-#endif
                 __syncwarp();
                 if (tid == 32) MSTAMP(0, g, 3);
                 if (lane == 0) {
@@ -808,11 +798,10 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 
 // ================= down projection (Q6_K), 256 weight rows per CTA ===========================
 // Two 128-row sub-tiles of the same stack share every activation stage (two accumulators of
-// 256 TMEM columns).  The quantized rows are read straight from global memory, coalesced:
-// eight consecutive lanes own one (row, 128-weight half of a super-block) and read its ql / qh
-// words side by side; each lane turns its 4 l-positions of the four 32-weight groups into
-// f16 and writes 8-byte pieces of the swizzled A stages of TWO consecutive k-stages.
-//   warps 0-7 dequant    warp 8 B loader    warp 9 MMA issuer    warps 10-13 epilogue
+// 256 TMEM columns).  The quantized rows are read from global memory one super-block column at a
+// time, in 16-byte pieces of the aligned window around each 210-byte block, staged in shared memory
+// and converted by one thread per (row, 16-wide l range); see the helpers below.
+//   warps 0-15 dequant    warp 16 B loader    warp 17 MMA issuer    warps 18-21 epilogue
 constexpr int DN_DQ_WARPS = 16;                       // dequant warps
 constexpr int DN_THREADS = (DN_DQ_WARPS + 6) * 32;    // + B loader, MMA issuer, four epilogue warps
 constexpr int DN_NSA = 3, DN_NSB = 2;
@@ -850,7 +839,7 @@ __device__ __forceinline__ uint4 ldg128_if(const void *p, bool on) {
 //          bytes out of the window - at the byte offset the block has inside it, re-aligned with funnel
 //          shifts - and converts 64 weights with one scale each.
 constexpr int DN_WIN = 224;                         // window bytes per (row, super-block)
-constexpr int DN_RAWP = 228;                        // shared-memory pitch of a staged window
+constexpr int DN_RAWP = DN_WIN + 4;                 // shared-memory pitch of a staged window
 constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP + 64; // + slack: a re-aligning read may touch 16 bytes past a window
 constexpr int DN_LPT = 2 * MM_M / (DN_DQ_WARPS * 2); // window loads per thread (two rows per warp instruction)
 
