@@ -18,6 +18,8 @@
 // rows are the N dimension, so ragged per-expert row counts cost only a
 // rounding to 16.  Every wait is bounded; a wait that runs out records a flag
 // and the kernel drains and exits.
+#include <cuda.h> // CUtensorMap (types only; the encoder is fetched through the runtime)
+
 #include "fused.cuh"
 #include "kquant.cuh"
 
@@ -77,6 +79,13 @@ __device__ __forceinline__ bool mb_wait(uint64_t *b, uint32_t parity, uint32_t *
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)),
                  "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+// 2-D tiled TMA load global -> shared (x = byte offset inside the row, a multiple of 16; y = row).
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     s32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(s32(bar))
+                 : "memory");
 }
 // Ask L2 to fetch a contiguous global range (16-byte aligned, size a multiple of 16).
 __device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
@@ -550,11 +559,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
 // no staging ring for raw blocks.  Epilogue: act = silu(gate) * up, f32, one row per routed row.
 //   warps 0-7   dequant (thread = (projection, weight row))     warp 8   B loader (bulk copy)
 //   warp 9      MMA issuer                                        warps 10-13  epilogue
-constexpr int GU_THREADS = 14 * 32;
+constexpr int GU_THREADS = 15 * 32;
 constexpr int GU_A_STAGE = 2 * A_STAGE_BYTES;
-constexpr int GU_NS = 3;
+constexpr int GU_NS = 2;
+constexpr int GU_RAW_SLOT = MM_M * Q4K_BYTES; // one super-block column of 128 rows of one projection
+constexpr int GU_RAW_SLOTS = 4;               // (column parity, projection)
 
 struct GuParams {
+    // 2-D views of the gate / up stacks as bytes: [n_expert * n_out rows][row_bytes], box = 144 bytes x 128 rows
+    CUtensorMap map_g, map_u;
     const uint8_t *wg, *wu; // gate / up stacks (Q4_K)
     int64_t expert_bytes;
     int n_out, k;
@@ -596,9 +609,11 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *a_st = smem, *b_st = smem + GU_NS * GU_A_STAGE;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(b_st + GU_NS * B_STAGE_BYTES);
-    // full[s]: eight dequant warps + the B loader's expect_tx arrival; empty[s]: one tcgen05.commit
-    uint64_t *full = bars, *empty = bars + 4, *acc_full = bars + 16, *acc_empty = bars + 17;
+    uint8_t *raw = b_st + GU_NS * B_STAGE_BYTES; // quantized super-block columns, TMA-staged
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + GU_RAW_SLOTS * GU_RAW_SLOT);
+    // full[s]: eight dequant warps + the B loader's expect_tx arrival; empty[s]: one tcgen05.commit;
+    // raw_full[i]: the TMA load's bytes; raw_empty[i]: the four dequant warps of the slot's projection
+    uint64_t *full = bars, *empty = bars + 4, *raw_full = bars + 8, *raw_empty = bars + 12, *acc_full = bars + 16, *acc_empty = bars + 17;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -610,6 +625,10 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
         for (int s = 0; s < GU_NS; s++) {
             mb_init(&full[s], 9);
             mb_init(&empty[s], 1);
+        }
+        for (int i = 0; i < GU_RAW_SLOTS; i++) {
+            mb_init(&raw_full[i], 1);
+            mb_init(&raw_empty[i], 4);
         }
         mb_init(acc_full, 1);
         mb_init(acc_empty, 4);
@@ -626,48 +645,60 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 
     if (warp < 8) {
         // ---------------- dequant: thread = (projection, weight row) ----------------
+        // The row's 144-byte super-block sits in the TMA-staged column of its projection (pitch 144 bytes:
+        // eight consecutive rows cover all banks for 16-byte reads).
         const int sub = warp >> 2, r = tid & 127;
-        const uint8_t *wbase = sub ? P.wu : P.wg;
-        uint32_t g = 0;
+        const int n_blk = P.k / QK_K;
+        uint32_t g = 0, col = 0; // k-stage counter, super-block column counter of this projection
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
+            const int m0 = P.tiles[8 * tile + 3];
             const bool rvalid = m0 + r < P.n_out;
-            const uint8_t *row = wbase + (size_t)e * P.expert_bytes + (size_t)(rvalid ? m0 + r : m0) * row_bytes;
-            // a whole super-block (144 B) ahead in registers: while block b is dequantised, block b+1 loads
-            const int n_blk = P.k / QK_K;
-            uint4 ra[9], rb[9];
+            for (int b = 0; b < n_blk && ok; b++, col++) {
+                const int slot = sub + 2 * (col & 1);
+                ok = mb_wait(&raw_full[slot], (col >> 1) & 1, P.flag, 2);
+                const uint4 *blk = reinterpret_cast<const uint4 *>(raw + (size_t)slot * GU_RAW_SLOT + r * Q4K_BYTES);
+                const uint4 hdr = blk[0];
 #pragma unroll
-            for (int i = 0; i < 9; i++) ra[i] = __ldg(reinterpret_cast<const uint4 *>(row) + i);
-            for (int b = 0; b < n_blk && ok; b += 2) {
+                for (int j = 0; j < 4; j++, g++) {
+                    const int s = g % GU_NS;
+                    if (tid == 0) GSTAMP(0, g, 0);
+                    ok = ok && mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
+                    if (tid == 0) GSTAMP(0, g, 1);
+                    uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
+                    if (rvalid) {
+                        dequant_q4k_regs(hdr, blk[1 + 2 * j], blk[2 + 2 * j], j, ast, r);
+                    } else {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    if (b + h >= n_blk) break;
-                    if (b + h + 1 < n_blk) {
-                        const uint4 *nx = reinterpret_cast<const uint4 *>(row + (size_t)(b + h + 1) * Q4K_BYTES);
-                        if (b + h + 2 < n_blk) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 9));
-#pragma unroll
-                        for (int i = 0; i < 9; i++) (h ? ra : rb)[i] = __ldg(nx + i);
+                        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
                     }
+                    if (tid == 0) GSTAMP(0, g, 2);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mb_arrive(&full[s]);
+                    if (tid == 0) GSTAMP(0, g, 3);
+                }
+                // the column is consumed: hand its slot back to the loader
+                __syncwarp();
+                if (lane == 0) mb_arrive(&raw_empty[slot]);
+            }
+        }
+    } else if (warp == 14) {
+        // ---------------- raw loader: one TMA tile load per (super-block column, projection) ----------------
+        if (lane == 0) {
+            const int n_blk = P.k / QK_K;
+            uint32_t col = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
+                const int y = e * P.n_out + m0;
+                for (int b = 0; b < n_blk && ok; b++, col++) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++, g++) {
-                        const int s = g % GU_NS;
-                        if (tid == 0) GSTAMP(0, g, 0);
-                        ok = ok && mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
-                        if (tid == 0) GSTAMP(0, g, 1);
-                        uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
-                        if (rvalid) {
-                            const uint4 *cur = h ? rb : ra;
-                            dequant_q4k_regs(cur[0], cur[1 + 2 * j], cur[2 + 2 * j], j, ast, r);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                        if (tid == 0) GSTAMP(0, g, 2);
-                        fence_async_smem();
-                        __syncwarp();
-                        if (lane == 0) mb_arrive(&full[s]);
-                        if (tid == 0) GSTAMP(0, g, 3);
+                    for (int sub = 0; sub < 2; sub++) {
+                        const int slot = sub + 2 * (col & 1);
+                        ok = ok && mb_wait(&raw_empty[slot], ((col >> 1) & 1) ^ 1, P.flag, 1);
+                        mb_expect_tx(&raw_full[slot], (uint32_t)GU_RAW_SLOT);
+                        tma_load_2d(raw + (size_t)slot * GU_RAW_SLOT, sub ? &P.map_u : &P.map_g, b * Q4K_BYTES, y, &raw_full[slot]);
                     }
                 }
             }
@@ -724,9 +755,9 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                     ok = mb_wait(&full[s], ph, P.flag, 6);
                     tc_fence_after();
                     // slot-indexed descriptors without dynamic register indexing
-                    const uint64_t a0 = s == 0 ? ad0[0] : s == 1 ? ad0[1] : ad0[2];
-                    const uint64_t a1 = s == 0 ? ad1[0] : s == 1 ? ad1[1] : ad1[2];
-                    const uint64_t b0 = s == 0 ? bd[0] : s == 1 ? bd[1] : bd[2];
+                    const uint64_t a0 = s == 0 ? ad0[0] : ad0[GU_NS - 1];
+                    const uint64_t a1 = s == 0 ? ad1[0] : ad1[GU_NS - 1];
+                    const uint64_t b0 = s == 0 ? bd[0] : bd[GU_NS - 1];
 #pragma unroll
                     for (int kk = 0; kk < MM_K / 16; kk++) {
                         tc_mma_f16(tmem_base, a0 + 2 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
@@ -1199,6 +1230,35 @@ cudaError_t launch_gather_tiles(const void *x, int x_f16, int x_per_row, int top
     return cudaGetLastError();
 }
 
+// A 2-D TMA view of an expert stack as bytes: [rows][row_bytes], boxes of box_bytes x box_rows.  The encoder
+// is a driver entry point, fetched through the runtime (no link against the driver library).
+static lmoe_status make_rows_map(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
+                                 uint32_t box_rows) {
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+            q != cudaDriverEntryPointSuccess)
+            return lmoe_fail(LMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = reinterpret_cast<encode_fn>(fn);
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || row_bytes % 16 || box_bytes % 16 || box_bytes > 256 || box_rows > 256)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "expert stack layout does not fit a TMA tile (16-byte alignment of base, row and box)");
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return lmoe_fail(LMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)rc);
+    return LMOE_OK;
+}
+
 // One grouped projection. `xt`: the f16 operand in tile order; `tiles_ws`: mm_tiles_bytes() scratch
 // whose last 256 bytes hold the tile count; `flag`: 4 device words (zero = clean).
 lmoe_status launch_mm_id(const lmoe_expert_stack *st, const void *xt, const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
@@ -1246,10 +1306,14 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)gate->n_expert, (int)gate->n_out, tiles, n_tiles, (int)max_tiles, MM_M);
     LMOE_LAUNCH_CHECK("build_tiles_kernel");
     GuParams P;
+    const uint64_t rb = (uint64_t)(gate->k / QK_K) * Q4K_BYTES, rows_all = (uint64_t)gate->n_expert * gate->n_out;
+    lmoe_status mst = make_rows_map(&P.map_g, gate->blocks(), rb, rows_all, Q4K_BYTES, MM_M);
+    if (mst) return mst;
+    if ((mst = make_rows_map(&P.map_u, up->blocks(), rb, rows_all, Q4K_BYTES, MM_M))) return mst;
     P.wg = gate->blocks(); P.wu = up->blocks(); P.expert_bytes = gate->expert_bytes();
     P.n_out = (int)gate->n_out; P.k = (int)gate->k; P.xt = static_cast<const uint8_t *>(xt);
     P.ids_map = ids_map; P.map_stride = (int)map_stride; P.tiles = tiles; P.n_tiles = n_tiles; P.act = act; P.sorted = sorted; P.flag = flag;
-    const int smem = GU_NS * (GU_A_STAGE + B_STAGE_BYTES) + 256 + 1024;
+    const int smem = GU_NS * (GU_A_STAGE + B_STAGE_BYTES) + GU_RAW_SLOTS * GU_RAW_SLOT + 256 + 1024;
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));
