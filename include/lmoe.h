@@ -260,6 +260,16 @@ lmoe_status lmoe_experts_forward_rows(const lmoe_layer *layer, const float *x, c
 lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *layer, const void *x_f16, const uint32_t *local_ids,
                                           const float *row_weights, int64_t rows, float *out, void *workspace,
                                           size_t workspace_bytes, void *stream);
+/* Token-level form of the same: one half-precision activation row per token and up to top_k local experts
+ * for it.  x_f16 [t, hidden], ids / weights [t, top_k]; a slot whose id is >= the layer's expert count is
+ * empty.  out [t, hidden] f32 = sum over the non-empty slots, in slot order, of weights * FFN_{ids}(x[token]).
+ * A token travels to a rank once, however many of its experts live there, and one summed row comes back.
+ * Needs the fused Q4_K gate/up and Q6_K down kernels (LMOE_ERR_UNSUPPORTED otherwise).
+ * Workspace: lmoe_tokens_workspace_bytes(layer, t, top_k). */
+size_t lmoe_tokens_workspace_bytes(const lmoe_layer *layer, int64_t t, int64_t top_k);
+lmoe_status lmoe_experts_forward_tokens_f16(const lmoe_layer *layer, const void *x_f16, const uint32_t *ids,
+                                            const float *weights, int64_t t, int64_t top_k, float *out,
+                                            void *workspace, size_t workspace_bytes, void *stream);
 /* Token dispatch of the expert-parallel path, packed on the device: rank r owns experts
  * [r * n_expert / world, (r + 1) * n_expert / world).  From x [t, hidden] f32 and the routing decision
  * ids / weights [t, top_k], writes the t * top_k routed rows grouped by destination rank (by expert inside a
@@ -272,7 +282,8 @@ lmoe_status lmoe_ep_pack(const float *x, const uint32_t *ids, const float *weigh
                          float *row_weights, int32_t *row_pos, int64_t *send_counts, void *workspace,
                          size_t workspace_bytes, void *stream);
 /* The return leg: out [t, hidden] = sum over slots, in slot order, of rows[row_pos[token * top_k + slot]]
- * (the weighted expert outputs, back in the order they were sent), then + shared [t, hidden] when non-NULL. */
+ * (the weighted expert outputs, back in the order they were sent), then + shared [t, hidden] when non-NULL.
+ * A negative row_pos entry is skipped (with the token-level dispatch: top_k = ranks, one slot per rank). */
 lmoe_status lmoe_ep_combine(const float *rows, const int32_t *row_pos, const float *shared, int64_t t,
                             int64_t top_k, int64_t hidden, float *out, void *stream);
 /* Bytes of scratch `lmoe_experts_forward_rows` / `lmoe_shared_forward` need for `rows` rows. */

@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restri
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int64_t fid = sfid ? sfid[row] : row;
+    if (fid < 0) return;                                   // no routed row here (masked slots leave a tail unused)
     const float *ar = a + row * ff;
     float ss = 0.f;
     for (int i = lane * 8; i < ff; i += 256) {
@@ -125,7 +126,7 @@ __global__ void sum_slots_kernel(const float *__restrict__ y, const float *__res
 }
 
 // Same sum when the partial rows are unscaled and in expert-sorted order: row spos[flat id] of `y`
-// times scale[that row]; likewise for the shared expert's rows.
+// times scale[that row]; likewise for the shared expert's rows.  A negative position marks an empty slot.
 __global__ void sum_sorted_kernel(const float *__restrict__ y, const float *__restrict__ scale,
                                   const int32_t *__restrict__ spos, const float *__restrict__ shared,
                                   const float *__restrict__ sh_scale, const int32_t *__restrict__ sh_spos, int64_t t,
@@ -136,6 +137,7 @@ __global__ void sum_sorted_kernel(const float *__restrict__ y, const float *__re
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top_k; k++) {
         const int64_t r = spos[tok * top_k + k];
+        if (r < 0) continue;                               // empty slot
         const float sc = scale ? scale[r] : 1.0f;
         const float4 v = reinterpret_cast<const float4 *>(y)[r * n4 + c];
         s.x = __fadd_rn(s.x, __fmul_rn(v.x, sc)); s.y = __fadd_rn(s.y, __fmul_rn(v.y, sc));
@@ -239,12 +241,12 @@ size_t ffn_bytes(int64_t rows, int64_t hidden, int64_t ff, int64_t n_expert) {
 // With `spos` / `scale_out` (both [rows], caller-owned) and the fused kernels available, y instead holds the
 // UNSCALED rows in expert-sorted order: row spos[flat id], to be multiplied by scale_out[that row]; the
 // tensor-core epilogues then store whole tile columns side by side instead of scattering by flat id.
-// *sorted_used tells which form was produced.
+// *sorted_used tells which form was produced.  `masked`: ids >= n_expert were left out of the lists.
 lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const lmoe_expert_stack *down,
                         const void *x, int top_k, int64_t t, const uint32_t *tpe, const int32_t *ids_map,
                         int64_t map_stride, const float *row_w, float *y, uint8_t *ws, uint32_t *flag,
                         cudaStream_t s, int32_t *spos = nullptr, float *scale_out = nullptr, bool *sorted_used = nullptr,
-                        int x_f16 = 0) {
+                        int x_f16 = 0, int masked = 0) {
     const int64_t rows = t * top_k, ff = gate->n_out, hidden = gate->k, ne = gate->n_expert;
     Carver c{ws, 0};
     uint8_t *xt = c.take<uint8_t>(mm_tiled_bytes(rows, ne, hidden));
@@ -259,6 +261,12 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
     const bool fused_dn = down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0;
     const bool sorted = spos && scale_out && fused_gu && fused_dn;
     if (sorted_used) *sorted_used = sorted;
+    if (masked) {
+        // some (token, slot) pairs name no expert: the lists skip them, and the per-row arrays mark them
+        if (!sorted) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "masked slots need the fused Q4_K / Q6_K kernels");
+        LMOE_CUDA(cudaMemsetAsync(spos, 0xFF, (size_t)rows * 4, s));
+        LMOE_CUDA(cudaMemsetAsync(sfid, 0xFF, (size_t)rows * 4, s));
+    }
     LMOE_CUDA(launch_gather_tiles(x, x_f16, 1, top_k, (int)hidden, tpe, ids_map, (int)map_stride, (int)ne, xt, pos,
                                   sorted ? spos : nullptr, sorted ? sfid : nullptr, s));
     if (fused_gu) {
@@ -467,6 +475,53 @@ extern "C" lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *L, const 
                                                      const float *row_weights, int64_t rows, float *out, void *workspace,
                                                      size_t workspace_bytes, void *stream) {
     return experts_rows_run(L, x_f16, 1, local_ids, row_weights, rows, out, workspace, workspace_bytes, stream);
+}
+
+// Token-level form for the expert-parallel exchange: one activation row per token, up to top_k experts each.
+static size_t tokens_ws_bytes(const lmoe_layer *L, int64_t t, int64_t top_k) {
+    const int64_t rows = t * top_k;
+    return 65536 + lmoe_map0_scratch_bytes(L->n_expert, t) + lmoe_align_up((size_t)rows * L->hidden * 4, 256) +
+           2 * lmoe_align_up((size_t)rows * 4, 256) + ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
+}
+
+extern "C" size_t lmoe_tokens_workspace_bytes(const lmoe_layer *L, int64_t t, int64_t top_k) {
+    return L && top_k >= 1 ? tokens_ws_bytes(L, t < 1 ? 1 : t, top_k) : 0;
+}
+
+extern "C" lmoe_status lmoe_experts_forward_tokens_f16(const lmoe_layer *L, const void *x_f16, const uint32_t *ids,
+                                                       const float *weights, int64_t t, int64_t top_k, float *out,
+                                                       void *workspace, size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    if (!L || !x_f16 || !ids || !weights || !out) return lmoe_fail(LMOE_ERR_INVALID, "layer/x/ids/weights/out is NULL");
+    if (top_k < 1 || t < 0 || t * top_k > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "t / top_k out of range");
+    if (t == 0) return LMOE_OK;
+    if ((reinterpret_cast<uintptr_t>(x_f16) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return lmoe_fail(LMOE_ERR_INVALID, "x and out must be 16-byte aligned");
+    if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
+    if (!workspace || workspace_bytes < tokens_ws_bytes(L, t, top_k))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", tokens_ws_bytes(L, t, top_k), workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t rows = t * top_k, H = L->hidden;
+    Carver c{static_cast<uint8_t *>(workspace), 65536};
+    uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
+    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
+    float *y = c.take<float>((size_t)rows * H);
+    int32_t *spos = c.take<int32_t>((size_t)rows);
+    float *rscale = c.take<float>((size_t)rows);
+    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
+    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    // ids >= n_expert match no expert's list: those slots stay empty
+    LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)L->n_expert, tpe, ids_map, s));
+    bool sorted = false;
+    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x_f16, (int)top_k, t, tpe, ids_map, t, weights, y, ffn_ws, flag, s,
+                                 spos, rscale, &sorted, 1, 1);
+    if (st) return st;
+    const int64_t n = t * (H / 4);
+    sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, rscale, spos, nullptr, nullptr, nullptr, t, (int)top_k,
+                                                                  (int)(H / 4), out);
+    LMOE_LAUNCH_CHECK("sum_sorted_kernel");
+    return LMOE_OK;
 }
 
 extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, int64_t t, float *out, void *workspace,

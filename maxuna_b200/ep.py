@@ -18,6 +18,14 @@ exercised on CPU ranks:
   combine_rows_fn(rows_back, row_pos, shared_or_None, t) -> out: the device-side packing of the
   dispatch and the fused return-leg sum (`lmoe_ep_pack` / `lmoe_ep_combine`); optional, the torch
   index arithmetic of `plan` is used otherwise.
+  tokens_fn(x[payload dtype N,H], ids[i32 N,K], w[f32 N,K]) -> y[f32 N,H]: the token-level form.  When it
+  is given, a token travels to a rank ONCE however many of its K experts live there (ids of the other ranks'
+  experts are replaced by the empty-slot id `e_local`), the rank returns one row per token, already summed
+  over its local experts in slot order, and the source adds the ranks' rows in rank order, then the shared
+  expert.  With K = 10 experts over 2 ranks that is 5x fewer rows each way than the row-level exchange; the
+  sum is grouped by rank instead of running in slot order, so it differs from the single-GPU result by f32
+  rounding only.  sum_ranks_fn(rows_back, pos[i32 T,G], shared_or_None, t) -> out is the fused form of the
+  final sum (`lmoe_ep_combine` with one slot per rank); optional.
 On GPUs the shared expert runs on a side stream while the dispatch is in flight.
 """
 from __future__ import annotations
@@ -28,8 +36,10 @@ import torch.distributed as dist
 
 class ExpertParallelMoe:
     def __init__(self, route_fn, rows_fn, shared_fn, n_expert: int, top_k: int, group=None,
-                 payload_dtype=torch.float16, combine_fn=None, pack_fn=None, combine_rows_fn=None):
+                 payload_dtype=torch.float16, combine_fn=None, pack_fn=None, combine_rows_fn=None,
+                 tokens_fn=None, sum_ranks_fn=None):
         self.route_fn, self.rows_fn, self.shared_fn = route_fn, rows_fn, shared_fn
+        self.tokens_fn, self.sum_ranks_fn = tokens_fn, sum_ranks_fn
         self.combine_fn = combine_fn
         self.pack_fn, self.combine_rows_fn = pack_fn, combine_rows_fn
         self._side = None
@@ -52,10 +62,77 @@ class ExpertParallelMoe:
         send_counts = torch.bincount(dest, minlength=self.world)
         return order, send_counts
 
+    def plan_tokens(self, ids: torch.Tensor):
+        """ids [T,K] -> (tok, dst, send_counts): the (token, destination rank) pairs with at least one of the
+        token's experts on that rank, sorted by rank, then token."""
+        dest = ids.to(torch.int64) // self.e_local
+        mask = torch.zeros(ids.shape[0], self.world, dtype=torch.bool, device=ids.device)
+        mask.scatter_(1, dest, True)
+        pairs = mask.t().nonzero()                       # row-major over [G,T]: by rank, then by token
+        return pairs[:, 1], pairs[:, 0], mask.sum(0)
+
+    def _start_shared(self, x):
+        """The shared expert needs nothing from the exchange: on GPUs it runs beside it."""
+        if self.shared_fn is None or not x.is_cuda:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        self._side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(self._side):
+            return self.shared_fn(x)
+
+    def _forward_tokens(self, x, ids, w):
+        t, h = x.shape
+        k, dev = self.top_k, x.device
+        tok, dst, send_counts = self.plan_tokens(ids)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        n_send, n_recv = sum(sc), sum(rc)
+        shared = self._start_shared(x)
+        # payloads: the token's activations once per destination; its K (local id, weight) pairs with the
+        # other ranks' experts blanked
+        xs = x.to(self.payload_dtype).index_select(0, tok)
+        ids_t = ids.to(torch.int64).index_select(0, tok)
+        mine = (ids_t // self.e_local) == dst[:, None]
+        lid = torch.where(mine, ids_t - dst[:, None] * self.e_local, self.e_local).to(torch.int32)
+        wt = torch.where(mine, w.index_select(0, tok), 0.0)
+        meta = torch.stack([lid, wt.contiguous().view(torch.int32)], dim=2).contiguous()     # [N,K,2] words
+        xr = torch.empty(n_recv, h, dtype=xs.dtype, device=dev)
+        dist.all_to_all_single(xr, xs, rc, sc, group=self.group)
+        meta_r = torch.empty(n_recv, k, 2, dtype=torch.int32, device=dev)
+        dist.all_to_all_single(meta_r, meta, rc, sc, group=self.group)
+        ir = meta_r[:, :, 0].contiguous()
+        wr = meta_r[:, :, 1].contiguous().view(torch.float32)
+        yr = self.tokens_fn(xr, ir, wr) if n_recv else torch.empty(0, h, dtype=torch.float32, device=dev)
+        ys = torch.empty(n_send, h, dtype=torch.float32, device=dev)
+        dist.all_to_all_single(ys, yr.contiguous(), sc, rc, group=self.group)
+        if shared is not None:
+            torch.cuda.current_stream(dev).wait_stream(self._side)
+        elif self.shared_fn is not None:
+            shared = self.shared_fn(x)
+        if self.sum_ranks_fn is not None:
+            pos = torch.full((t, self.world), -1, dtype=torch.int32, device=dev)
+            pos[tok, dst] = torch.arange(n_send, dtype=torch.int32, device=dev)
+            out = self.sum_ranks_fn(ys, pos, shared, t)
+        else:
+            out = torch.zeros(t, h, dtype=torch.float32, device=dev)
+            o = 0
+            for g in range(self.world):                  # rank order; a token appears once per rank
+                out.index_add_(0, tok[o:o + sc[g]], ys[o:o + sc[g]])
+                o += sc[g]
+            if shared is not None:
+                out += shared
+        self.last_stats = {"rows_sent": n_send, "rows_received": n_recv,
+                           "remote_rows_sent": n_send - sc[self.rank]}
+        return out
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         t, h = x.shape
         k = self.top_k
         ids, w = self.route_fn(x)                       # [T,K] int32 (u32 bits), [T,K] f32
+        if self.tokens_fn is not None:
+            return self._forward_tokens(x, ids, w)
         dev = x.device
         packed = self.pack_fn is not None and self.combine_rows_fn is not None
         if packed:
@@ -67,14 +144,7 @@ class ExpertParallelMoe:
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
         sc, rc = send_counts.tolist(), recv_counts.tolist()
         n_send, n_recv = sum(sc), sum(rc)
-        # the shared expert needs nothing from the exchange: on GPUs it runs beside it
-        shared = None
-        if self.shared_fn is not None and x.is_cuda:
-            if self._side is None:
-                self._side = torch.cuda.Stream(device=dev)
-            self._side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(self._side):
-                shared = self.shared_fn(x)
+        shared = self._start_shared(x)
         if not packed:
             # dispatch payloads: activations (f16 on the wire: the grouped GEMM consumes f16 operands
             # rounded the same way), local expert id, routing weight
@@ -118,8 +188,11 @@ class ExpertParallelMoe:
         return out
 
 
-def make_gpu_ep_block(full_router, bias, local_block, n_expert, top_k, scale=2.5, norm=True, group=None):
-    """Bind the exchange logic to the CUDA entry points of a local `MoeBlock` shard."""
+def make_gpu_ep_block(full_router, bias, local_block, n_expert, top_k, scale=2.5, norm=True, group=None,
+                      token_level=True):
+    """Bind the exchange logic to the CUDA entry points of a local `MoeBlock` shard.  `token_level` picks
+    the exchange that sends a token once per destination rank (needs Q4_K gate/up and Q6_K down experts);
+    False keeps the row-level exchange, whose sum runs in slot order like the single-GPU path."""
     from . import ops
 
     def route_fn(x):
@@ -158,7 +231,15 @@ def make_gpu_ep_block(full_router, bias, local_block, n_expert, top_k, scale=2.5
                                     t, top_k, ys.shape[1], out.data_ptr(), stream_ptr()))
         return out
 
+    def sum_ranks_fn(ys, pos, shared, t):
+        out = torch.empty(t, ys.shape[1], dtype=torch.float32, device=ys.device)
+        check(lib().lmoe_ep_combine(ys.contiguous().data_ptr(), pos.data_ptr(), shared.data_ptr() if shared is not None else None,
+                                    t, world, ys.shape[1], out.data_ptr(), stream_ptr()))
+        return out
+
     return ExpertParallelMoe(route_fn, local_block.experts_forward_rows,
                              local_block.shared_forward if local_block.shared is not None else None,
                              n_expert, top_k, group, combine_fn=combine_fn, pack_fn=pack_fn,
-                             combine_rows_fn=combine_rows_fn)
+                             combine_rows_fn=combine_rows_fn,
+                             tokens_fn=local_block.experts_forward_tokens if token_level else None,
+                             sum_ranks_fn=sum_ranks_fn if token_level else None)

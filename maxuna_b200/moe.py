@@ -215,11 +215,29 @@ class MoeBlock:
                  out.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
         return out
 
+    def experts_forward_tokens(self, x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """`lmoe_experts_forward_tokens_f16`: x [t, hidden] f16, ids / w [t, k] (id >= local expert count = empty
+        slot) -> [t, hidden] f32, the slot-order sum of the weighted local experts of every token."""
+        x = x.to(torch.float16).contiguous()
+        t, k = ids.shape
+        out = torch.empty(t, self.hidden, dtype=torch.float32, device=x.device)
+        n = lib().lmoe_tokens_workspace_bytes(self._h, t, k)
+        if getattr(self, "_tws", None) is None or self._tws.numel() < n:
+            self._tws = torch.zeros(n, dtype=torch.uint8, device=self.router.device)
+        check(lib().lmoe_experts_forward_tokens_f16(self._h, x.data_ptr(), ids.contiguous().data_ptr(),
+                                                    w.contiguous().data_ptr(), t, k, out.data_ptr(),
+                                                    self._tws.data_ptr(), self._tws.numel(), stream_ptr()))
+        return out
+
     def shared_forward(self, x: torch.Tensor) -> torch.Tensor:
         """`lmoe_shared_forward`: the shared expert alone."""
         x = x.to(torch.float32).contiguous()
         out = torch.empty(x.shape[0], self.hidden, dtype=torch.float32, device=x.device)
-        ws = self._rows_ws(x.shape[0])
+        # a workspace of its own: the shared expert may run on a side stream beside the routed experts
+        n = lib().lmoe_rows_workspace_bytes(self._h, x.shape[0])
+        if getattr(self, "_sws", None) is None or self._sws.numel() < n:
+            self._sws = torch.zeros(n, dtype=torch.uint8, device=self.router.device)
+        ws = self._sws
         check(lib().lmoe_shared_forward(self._h, x.data_ptr(), x.shape[0], out.data_ptr(), ws.data_ptr(), ws.numel(),
                                         stream_ptr()))
         return out

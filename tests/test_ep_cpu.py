@@ -27,7 +27,7 @@ def _layer(orc, seed=3, hidden=256, ff=256, ne=8, top_k=3):
                          sh_gate=q(orc.Q4_K, (ff, hidden)), sh_up=q(orc.Q4_K, (ff, hidden)), sh_down=q(orc.Q6_K, (hidden, ff)))
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, token_level=False):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -65,7 +65,18 @@ def _worker(rank, world, port, q):
                                     orc.mul_id(orc.Q4_K, shared_only.up, 1, L.expert_ff, L.hidden, xn[:, None, :], z)), z)
         return torch.from_numpy(d[:, 0, :])
 
-    ep = ExpertParallelMoe(route_fn, rows_fn, shared_fn, L.n_expert, L.top_k, payload_dtype=torch.float32)
+    def tokens_fn(x, ids, w):
+        # the token-level form out of the row-level one: expand the non-empty slots, sum them back in slot order
+        tok, slot = torch.nonzero(ids < ne_local, as_tuple=True)
+        y = rows_fn(x[tok], ids[tok, slot], w[tok, slot])
+        out = torch.zeros(x.shape[0], L.hidden)
+        for s_ in range(ids.shape[1]):
+            m = slot == s_
+            out.index_add_(0, tok[m], y[m])
+        return out
+
+    ep = ExpertParallelMoe(route_fn, rows_fn, shared_fn, L.n_expert, L.top_k, payload_dtype=torch.float32,
+                           tokens_fn=tokens_fn if token_level else None)
     rng = np.random.default_rng(100 + rank)
     t = 5 + 3 * rank  # ragged token counts per rank
     x = rng.standard_normal((t, L.hidden)).astype(np.float32)
@@ -77,23 +88,29 @@ def _worker(rank, world, port, q):
     order, counts = ep.plan(ids)
     dest = (ids.reshape(-1).to(torch.int64) // ne_local)[order]
     ok_sorted = bool(torch.all(dest[1:] >= dest[:-1])) and int(counts.sum()) == t * L.top_k
-    q.put((rank, err, ok_sorted, ep.last_stats))
+    # token-level plan: one (token, rank) pair per rank that owns at least one of the token's experts
+    tok, dst, tcounts = ep.plan_tokens(ids)
+    want_pairs = sorted({(int(e) // ne_local, i) for i in range(t) for e in ids[i].tolist()})
+    ok_sorted = ok_sorted and list(zip(dst.tolist(), tok.tolist())) == want_pairs
+    ok_sorted = ok_sorted and tcounts.tolist() == [sum(1 for g, _ in want_pairs if g == r) for r in range(world)]
+    q.put((rank, err, ok_sorted, ep.last_stats, len(want_pairs)))
     dist.destroy_process_group()
 
 
-def test_expert_parallel_two_cpu_ranks(orc):
+@pytest.mark.parametrize("token_level", [False, True])
+def test_expert_parallel_two_cpu_ranks(orc, token_level):
     orc.build()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, token_level)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, err, ok_sorted, stats in res:
+    for rank, err, ok_sorted, stats, n_pairs in res:
         assert err < 1e-5, (rank, err)
         assert ok_sorted
-        assert stats["rows_sent"] == (5 + 3 * rank) * 3
+        assert stats["rows_sent"] == (n_pairs if token_level else (5 + 3 * rank) * 3)

@@ -54,6 +54,35 @@ def test_rows_f16_equals_f32_rows(orc):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("t,k", [(1, 1), (130, 3), (700, 4)])
+def test_tokens_entry_matches_rows_entry(t, k):
+    """The token-level entry (empty slots allowed) against the row-level one on the expanded slots."""
+    from maxuna_b200.moe import MoeBlock
+
+    dev = torch.device("cuda:0")
+    ne = 8
+    blk = MoeBlock.random(256, 512, ne, 2, seed=47, device=dev, weight_std=0.25)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9 + t)
+    x16 = torch.randn(t, 256, generator=gen, device=dev).to(torch.float16)
+    # distinct experts per token; about a third of the slots empty (id == ne), slot 0 always used
+    ids = torch.rand(t, ne, generator=gen, device=dev).argsort(dim=1)[:, :k].to(torch.int32)
+    empty = torch.rand(t, k, generator=gen, device=dev) < 0.35
+    empty[:, 0] = False
+    ids = torch.where(empty, torch.full_like(ids, ne), ids)
+    w = torch.rand(t, k, generator=gen, device=dev)
+    got = blk.experts_forward_tokens(x16, ids, w)
+    tok, slot = torch.nonzero(ids < ne, as_tuple=True)
+    y = blk.experts_forward_rows(x16[tok].contiguous(), ids[tok, slot].contiguous(), w[tok, slot].contiguous())
+    want = torch.zeros(t, 256, device=dev)
+    for s_ in range(k):
+        m = slot == s_
+        want.index_add_(0, tok[m], y[m])
+    torch.cuda.synchronize()
+    assert float((got - want).norm() / want.norm()) < 1e-6
+    blk.check_device_flag()
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_ep_pack_and_combine_match_the_index_arithmetic(world):
     """lmoe_ep_pack / lmoe_ep_combine against the torch plan they replace (one device, any world size)."""
@@ -103,7 +132,7 @@ def test_ep_pack_and_combine_match_the_index_arithmetic(world):
     assert torch.equal(out, want)
 
 
-def _ep_worker(rank, world, port, q):
+def _ep_worker(rank, world, port, q, token_level):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -117,7 +146,7 @@ def _ep_worker(rank, world, port, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     full = MoeBlock.random(256, 512, 8, 3, seed=51, device=dev, weight_std=0.25)  # same seed on every rank
-    ep = make_gpu_ep_block(full.router, full.exp_probs_b, full.shard(rank, world), 8, 3)
+    ep = make_gpu_ep_block(full.router, full.exp_probs_b, full.shard(rank, world), 8, 3, token_level=token_level)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7)
     x_all = torch.randn(2 * 96, 256, generator=gen, device=dev)
@@ -126,12 +155,15 @@ def _ep_worker(rank, world, port, q):
     ref = full.forward(x_all)[rank * 96:(rank + 1) * 96]
     torch.cuda.synchronize()
     err = float((out - ref).norm() / ref.norm())
-    q.put((rank, err, ep.last_stats))
+    ids, _ = ep.route_fn(x)
+    pairs = int(torch.zeros(96, world, dtype=torch.bool, device=dev).scatter_(1, ids.to(torch.int64) // (8 // world), True).sum())
+    q.put((rank, err, ep.last_stats, pairs))
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus():
+@pytest.mark.parametrize("token_level", [False, True])
+def test_expert_parallel_two_gpus(token_level):
     import torch.multiprocessing as mp
 
     s = socket.socket()
@@ -140,13 +172,13 @@ def test_expert_parallel_two_gpus():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q, token_level)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, err, stats in res:
-        assert err < 1e-5, (rank, err)  # same f16 operands, same per-element accumulation order
-        assert stats["rows_sent"] == 96 * 3
+    for rank, err, stats, pairs in res:
+        assert err < 1e-5, (rank, err)  # same f16 operands; the token-level sum is grouped by rank (f32 rounding)
+        assert stats["rows_sent"] == (pairs if token_level else 96 * 3)
