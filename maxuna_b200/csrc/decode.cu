@@ -52,7 +52,8 @@ constexpr int NRED = 3;          // K-split partial buffers between the consumer
 constexpr int SYNC_PASS0 = 32;   // layer sync words: [0] grid barrier, [1] exit count, [32 + pass] phase-1 units done
 constexpr int SYNC_WORDS = SYNC_PASS0 + 1024;
 constexpr int NTOK = 2;         // tokens per pass over an expert's weights
-constexpr int NCOL = 2 * NTOK;  // MMA columns in use: (token, hi/lo)
+constexpr int NDIG = 3;         // signed base-128 digits per activation (21 bits under a per-256 scale)
+constexpr int NCOL = NDIG * NTOK; // MMA columns in use: (token, digit)
 constexpr int DEC_MAX_T = 16;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -72,31 +73,32 @@ struct DecodeParams {
     float *logits;    // [t][n_expert]
     uint32_t *ids_ws; // [t][top_k] routing decision, written by the CTA that ranked the token
     float *w_ws;
-    __half *act_hl;   // [t*(top_k+1)][2][ff], k permuted within groups of 8
+    float *act_f;     // [t*(top_k+1)][ff] SwiGLU activations
     float *ypart;     // [t*(top_k+1)][hidden]
 };
 
 // Shared-memory layout (bytes), computed identically on host and device.
 struct DecLayout {
     int stage_bytes, xs, ss;
-    int o_ring, o_xc, o_s, o_red, o_bar, o_ids, o_w, o_cnt, o_off, o_plist, o_act, o_ppre, total;
+    int o_ring, o_xc, o_s, o_sx, o_red, o_bar, o_ids, o_w, o_cnt, o_off, o_plist, o_act, o_ppre, total;
     __host__ __device__ DecLayout(int hidden, int ff, int n_expert, int t, int top_k) {
         const int row4 = hidden / QK_K * Q4K_BYTES, row6 = ff / QK_K * Q6K_BYTES;
         int sb = 16 * row4 > DOWN_ROWS * row6 ? 16 * row4 : DOWN_ROWS * row6;
         stage_bytes = (sb + 127) / 128 * 128;
         const int kmax = hidden > ff ? hidden : ff;
-        xs = kmax + 32; // halfs per column (+64 B so two columns land in different bank halves)
+        xs = kmax + 32; // bytes per column (+32 B: four columns of a half-warp's loads cover all 32 banks)
         int nsb = hidden / 32 > ff / 16 ? hidden / 32 : ff / 16;
         ss = (nsb + 15) / 16 * 16;
         const int tk = t * top_k;
         int o = 0;
         o_ring = o; o += NSTAGE * stage_bytes;
         o_xc = o;
-        int xc_bytes = NCOL * xs * 2;
+        int xc_bytes = NCOL * xs;
         const int sel_bytes = CW * 2 * n_expert * 4; // routing scratch aliases the activation cache
         if (sel_bytes > xc_bytes) xc_bytes = sel_bytes;
         o += (xc_bytes + 15) / 16 * 16;
         o_s = o; o += NCOL * ss * 2;
+        o_sx = o; o += (kmax / QK_K) * 8 * 4; // [256-block][8 columns] digit scales
         // the K-split partial buffers (phases 1-2) share their space with two routing tables that are
         // only alive while the token lists are built: expert counts and the id list
         int red_bytes = NRED * CW * 16 * NCOL * 4;
@@ -163,12 +165,6 @@ __device__ __forceinline__ void bar_sync(int id, int count) {
 __device__ __forceinline__ void bar_arrive(int id, int count) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ uint32_t ld_acquire(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -200,10 +196,6 @@ __device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t *sync, uin
     }
     bar_sync(1, CW * 32);
 }
-
-// Position of element i of an aligned group of 8 activations: [x0 x2 x1 x3 x4 x6 x5 x7]
-// (bits 0 and 1 swapped), which puts each lane's MMA B fragment in consecutive bytes.
-__device__ __forceinline__ int perm8(int i) { return (i & ~3) | ((i & 1) << 1) | ((i >> 1) & 1); }
 
 // One work unit: a row tile of one expert for one pass of <= NTOK tokens.
 struct Unit {
@@ -267,63 +259,64 @@ __device__ __forceinline__ Unit make_pass(const DecodeParams &P, const Tables &T
 }
 
 // ---- activation cache staging --------------------------------------------------
-// Phase 1: x rows (f32, global) -> f16 hi/lo columns, permuted; 32-wide sums S.
-__device__ __forceinline__ void stage_x(const DecodeParams &P, const Unit &U, __half *xc, __half *sh, int xs,
-                                        int ss, int tid) {
-    const int groups = P.hidden / 8;
-    for (int i = tid; i < U.n_tok * groups; i += CW * 32) {
-        const int tk = i / groups, g8 = i - tk * groups;
-        const float *src = P.x + (size_t)U.tok[tk] * P.hidden + g8 * 8;
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(src + 4));
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        __align__(16) __half hi[8], lo[8];
-        float sum = 0.f;
+// Each value of a token's row becomes NDIG signed base-128 digits of X = round(v * (2^19 - 1) / amax), amax
+// taken per 256-wide block: 21 bits under the block's largest value.  Digit d (most significant first) of
+// token tk is int8 column NDIG*tk + d of the cache, in natural k order, and sxs[block][column] is the float
+// that turns the column's integer dot product back into the row's scale.  sh: SUB-wide sums of the quantized
+// values, as f16 hi/lo pairs in columns NDIG*tk and NDIG*tk + 1 (zero in the third), for the Q4_K min term and
+// the Q6_K offset.  One warp per (token, block): a lane owns 8 consecutive values.
+// FROM_X: phase 1, rows of x (global, read-only); else phase 2, SwiGLU activations written by other CTAs.
+template <int SUB, bool FROM_X>
+__device__ __forceinline__ void stage_rows(const DecodeParams &P, const Unit &U, int8_t *xc, __half *sh, float *sxs,
+                                           int xs, int ss, int warp, int lane) {
+    const int k = FROM_X ? P.hidden : P.ff;
+    const int nblk = k / QK_K;
+    for (int it = warp; it < U.n_tok * nblk; it += CW) {
+        const int tk = it / nblk, b = it - tk * nblk;
+        const float *src = (FROM_X ? P.x + (size_t)U.tok[tk] * P.hidden : P.act_f + (size_t)U.pair[tk] * P.ff) +
+                           b * QK_K + lane * 8;
+        float4 a, c;
+        if (FROM_X) {
+            a = __ldg(reinterpret_cast<const float4 *>(src));
+            c = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+        } else {
+            a = __ldcg(reinterpret_cast<const float4 *>(src));
+            c = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+        }
+        const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float inv = amax > 0.f ? 524287.f / amax : 0.f;
+        const float sx = amax * (1.0f / 524287.f);
+        int sum = 0;
+        uint32_t dig[NDIG][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const __half h = __float2half_rn(v[j]);
-            hi[perm8(j)] = h;
-            lo[perm8(j)] = __float2half_rn(v[j] - __half2float(h));
-            sum += v[j];
+            const int X = __float2int_rn(v[j] * inv);
+            sum += X;
+            const int d0 = ((X + 64) & 127) - 64, X1 = (X - d0) >> 7;
+            const int d1 = ((X1 + 64) & 127) - 64, d2 = (X1 - d1) >> 7;
+            dig[0][j >> 2] |= (uint32_t)(d2 & 255) << (8 * (j & 3));
+            dig[1][j >> 2] |= (uint32_t)(d1 & 255) << (8 * (j & 3));
+            dig[2][j >> 2] |= (uint32_t)(d0 & 255) << (8 * (j & 3));
         }
-        *reinterpret_cast<uint4 *>(xc + (2 * tk) * xs + g8 * 8) = *reinterpret_cast<const uint4 *>(hi);
-        *reinterpret_cast<uint4 *>(xc + (2 * tk + 1) * xs + g8 * 8) = *reinterpret_cast<const uint4 *>(lo);
-        // 32-wide sub-block sum = 4 consecutive groups = 4 consecutive lanes (groups % 4 == 0)
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if ((g8 & 3) == 0) {
-            const __half h = __float2half_rn(sum);
-            sh[(2 * tk) * ss + (g8 >> 2)] = h;
-            sh[(2 * tk + 1) * ss + (g8 >> 2)] = __float2half_rn(sum - __half2float(h));
-        }
-    }
-}
-
-// Phase 2: SwiGLU activations (f16 hi/lo, already permuted, global/L2) -> cache; 16-wide sums.
-__device__ __forceinline__ void stage_act(const DecodeParams &P, const Unit &U, __half *xc, __half *sh, int xs,
-                                          int ss, int tid) {
-    const int groups = P.ff / 8;
-    for (int i = tid; i < U.n_tok * groups; i += CW * 32) {
-        const int tk = i / groups, g8 = i - tk * groups;
-        const __half *src = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + g8 * 8;
-        const uint4 hi = __ldcg(reinterpret_cast<const uint4 *>(src));
-        const uint4 lo = __ldcg(reinterpret_cast<const uint4 *>(src + P.ff));
-        *reinterpret_cast<uint4 *>(xc + (2 * tk) * xs + g8 * 8) = hi;
-        *reinterpret_cast<uint4 *>(xc + (2 * tk + 1) * xs + g8 * 8) = lo;
-        const __half2 *h2 = reinterpret_cast<const __half2 *>(&hi);
-        const __half2 *l2 = reinterpret_cast<const __half2 *>(&lo);
-        float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 a = __half22float2(h2[j]), b = __half22float2(l2[j]);
-            sum += (a.x + b.x) + (a.y + b.y);
-        }
+        for (int d = 0; d < NDIG; d++)
+            *reinterpret_cast<uint2 *>(xc + (NDIG * tk + d) * xs + b * QK_K + lane * 8) = make_uint2(dig[d][0], dig[d][1]);
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        if ((g8 & 1) == 0) {
-            const __half h = __float2half_rn(sum);
-            sh[(2 * tk) * ss + (g8 >> 1)] = h;
-            sh[(2 * tk + 1) * ss + (g8 >> 1)] = __float2half_rn(sum - __half2float(h));
+        if (SUB == 32) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((lane & (SUB / 8 - 1)) == 0) {
+            const float sf = sx * (float)sum;
+            const __half h = __float2half_rn(sf);
+            const int idx = b * (QK_K / SUB) + lane / (SUB / 8);
+            sh[(NDIG * tk) * ss + idx] = h;
+            sh[(NDIG * tk + 1) * ss + idx] = __float2half_rn(sf - __half2float(h));
+            sh[(NDIG * tk + 2) * ss + idx] = __float2half_rn(0.f);
         }
+        if (lane < NDIG) sxs[b * 8 + NDIG * tk + lane] = sx * (lane == 0 ? 16384.f : (lane == 1 ? 128.f : 1.f));
     }
 }
 
@@ -335,18 +328,39 @@ __device__ __forceinline__ void mma16816_z(float (&d)[4], uint32_t a0, uint32_t 
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
-// byte i (0..3) of `w` as an exact float: 0x4B0000bb is 2^23 + bb
-template <int I>
-__device__ __forceinline__ float byte_to_float(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + I)) - 8388608.0f;
+// Integer forms: unsigned 8-bit weights (A) times signed 8-bit activation digits (B), exact s32 sums.
+// k = 32: a0/a2 = row g, k slots 4t.. / 16+4t..; a1/a3 = row g+8; b0/b1 = column g, the same k slots.
+__device__ __forceinline__ void imma16832_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// k = 16: a0 = row g, a1 = row g+8, b0 = column g, all k slots 4t..4t+3.
+__device__ __forceinline__ void imma16816_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+// byte i (0..3) of `w`, zero- or sign-extended
+__device__ __forceinline__ int ubyte(uint32_t w, int i) { return (int)__byte_perm(w, 0u, 0x4440u + i); }
+__device__ __forceinline__ int sbyte(uint32_t w, int i) {
+    // selector nibbles i, 8|i, 8|i, 8|i: the byte, then its sign bit replicated (the intrinsic ignores bit 3)
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"((uint32_t)(i | ((8 | i) * 0x1110))));
+    return r;
 }
 
 // 16 Q4_K rows (8 gate + 8 up).  Work item of a warp: a super-block (CW <= 4) or half of one (CW is
 // then even, so a warp always works on the same half).  acc: rows g / g+8, columns 2t, 2t+1.
+// The nibbles of a 32-weight sub-block are the bytes of one k = 32 integer MMA (no unpacking beyond a mask);
+// the six-bit sub-block scales multiply the exact integer sums, and the float factors (d of the row, digit
+// scale of the column) come in once per super-block.
 constexpr int Q4_SPLIT = CW > 4 ? 2 : 1;
 __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
-                                         const __half *xcol, const __half *scol, float (&acc)[4]) {
+                                         const int8_t *xcol, const __half *scol, const float *sxs, float (&acc)[4]) {
     constexpr int HPI = 2 / Q4_SPLIT; // halves per item
+    constexpr uint32_t M4 = 0x0F0F0F0Fu;
     const uint8_t *rg = stage + g * row_bytes;
     const uint8_t *rG = rg + 8 * row_bytes;
     for (int it = warp; it < Q4_SPLIT * nb; it += CW) {
@@ -354,14 +368,14 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
         const uint8_t *bg = rg + b * Q4K_BYTES, *bG = rG + b * Q4K_BYTES;
         const uint4 hg = *reinterpret_cast<const uint4 *>(bg);
         const uint4 hG = *reinterpret_cast<const uint4 *>(bG);
-        const float dg = lmoe_h2f((uint16_t)(hg.x & 0xffff)) * 16777216.f;
+        const float dg = lmoe_h2f((uint16_t)(hg.x & 0xffff));
         const float mg = lmoe_h2f((uint16_t)(hg.x >> 16)) * 16777216.f;
-        const float dG = lmoe_h2f((uint16_t)(hG.x & 0xffff)) * 16777216.f;
+        const float dG = lmoe_h2f((uint16_t)(hG.x & 0xffff));
         const float mG = lmoe_h2f((uint16_t)(hG.x >> 16)) * 16777216.f;
         uint32_t scg[2], mng[2], scG[2], mnG[2]; // (scale, min) pairs, one per byte, per half
         q4k_unpack_scales(hg.y, hg.z, hg.w, scg[0], scg[1], mng[0], mng[1]);
         q4k_unpack_scales(hG.y, hG.z, hG.w, scG[0], scG[1], mnG[0], mnG[1]);
-        // min term: one MMA, A = the six-bit mins of each row (of this item's halves), B = 32-wide activation sums
+        // min term: one f16 MMA, A = the six-bit mins of each row (as f16 subnormals), B = 32-wide activation sums
         float cm[4];
         {
             const bool mine = Q4_SPLIT == 1 || (t >> 1) == h0;
@@ -371,8 +385,7 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
             const uint32_t sb = *reinterpret_cast<const uint32_t *>(scol + 8 * b + 2 * t);
             mma16816_z(cm, ma, mA, 0u, 0u, sb, 0u);
         }
-        // low-nibble and high-nibble sub-blocks accumulate apart (they differ by a factor 16)
-        float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
+        int al[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int hh = 0; hh < HPI; hh++) {
             const int h = h0 + hh;
@@ -380,32 +393,27 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
 #pragma unroll
             for (int jj = 0; jj < 2; jj++) {
                 const int j = 2 * h + jj;
+                // bytes 8t..8t+7 of the 32-byte chunk: low nibbles = sub-block 2j, high nibbles = sub-block 2j+1
                 const uint2 wg = *reinterpret_cast<const uint2 *>(bg + 16 + 32 * j + 8 * t);
                 const uint2 wG = *reinterpret_cast<const uint2 *>(bG + 16 + 32 * j + 8 * t);
-                const uint4 xl = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 8 * t);
-                const uint4 xh = *reinterpret_cast<const uint4 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
-                const uint32_t sg8 = wg.x >> 8, sG8 = wG.x >> 8, tg8 = wg.y >> 8, tG8 = wG.y >> 8;
-                float fl[4], fh[4];
-                mma16816_z(fl, wg.x & 0x000F000Fu, wG.x & 0x000F000Fu, sg8 & 0x000F000Fu, sG8 & 0x000F000Fu, xl.x, xl.y);
-                mma16816(fl, wg.y & 0x000F000Fu, wG.y & 0x000F000Fu, tg8 & 0x000F000Fu, tG8 & 0x000F000Fu, xl.z, xl.w);
-                mma16816_z(fh, wg.x & 0x00F000F0u, wG.x & 0x00F000F0u, sg8 & 0x00F000F0u, sG8 & 0x00F000F0u, xh.x, xh.y);
-                mma16816(fh, wg.y & 0x00F000F0u, wG.y & 0x00F000F0u, tg8 & 0x00F000F0u, tG8 & 0x00F000F0u, xh.z, xh.w);
-                float s0g, s1g, s0G, s1G;
-                if (jj) {
-                    s0g = byte_to_float<2>(sg); s1g = byte_to_float<3>(sg);
-                    s0G = byte_to_float<2>(sG); s1G = byte_to_float<3>(sG);
-                } else {
-                    s0g = byte_to_float<0>(sg); s1g = byte_to_float<1>(sg);
-                    s0G = byte_to_float<0>(sG); s1G = byte_to_float<1>(sG);
-                }
-                al[0] += s0g * fl[0]; al[1] += s0g * fl[1]; al[2] += s0G * fl[2]; al[3] += s0G * fl[3];
-                ah[0] += s1g * fh[0]; ah[1] += s1g * fh[1]; ah[2] += s1G * fh[2]; ah[3] += s1G * fh[3];
+                const uint2 xl = *reinterpret_cast<const uint2 *>(xcol + 256 * b + 64 * j + 8 * t);
+                const uint2 xh = *reinterpret_cast<const uint2 *>(xcol + 256 * b + 64 * j + 32 + 8 * t);
+                int fl[4], fh[4];
+                imma16832_z(fl, wg.x & M4, wG.x & M4, wg.y & M4, wG.y & M4, xl.x, xl.y);
+                imma16832_z(fh, (wg.x >> 4) & M4, (wG.x >> 4) & M4, (wg.y >> 4) & M4, (wG.y >> 4) & M4, xh.x, xh.y);
+                const int s0g = ubyte(sg, 2 * jj), s1g = ubyte(sg, 2 * jj + 1);
+                const int s0G = ubyte(sG, 2 * jj), s1G = ubyte(sG, 2 * jj + 1);
+                al[0] += s0g * fl[0] + s1g * fh[0];
+                al[1] += s0g * fl[1] + s1g * fh[1];
+                al[2] += s0G * fl[2] + s1G * fh[2];
+                al[3] += s0G * fl[3] + s1G * fh[3];
             }
         }
-        acc[0] += dg * (al[0] + 0.0625f * ah[0]) - mg * cm[0];
-        acc[1] += dg * (al[1] + 0.0625f * ah[1]) - mg * cm[1];
-        acc[2] += dG * (al[2] + 0.0625f * ah[2]) - mG * cm[2];
-        acc[3] += dG * (al[3] + 0.0625f * ah[3]) - mG * cm[3];
+        const float2 cs = *reinterpret_cast<const float2 *>(sxs + 8 * b + 2 * t);
+        acc[0] += dg * (cs.x * (float)al[0]) - mg * cm[0];
+        acc[1] += dg * (cs.y * (float)al[1]) - mg * cm[1];
+        acc[2] += dG * (cs.x * (float)al[2]) - mG * cm[2];
+        acc[3] += dG * (cs.y * (float)al[3]) - mG * cm[3];
     }
 }
 
@@ -429,20 +437,18 @@ __device__ __forceinline__ uint32_t sc_pair_half2(const int8_t *p) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// byte I (0..3) of `w`, which holds int8 + 128, as an exact float
-__device__ __forceinline__ float biased_byte_to_float(uint32_t w, int i) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + i)) - 8388736.0f; // 2^23 + 128
-}
-
-// One Q6_K super-block of rows g (bg) and g+8 (bG), which have the same alignment.
+// One Q6_K super-block of rows g (bg) and g+8 (bG), which have the same alignment.  The six-bit value of a
+// weight (low nibble | two high bits << 4, 0..63) is one byte of a k = 16 integer MMA: one MMA per 16-wide
+// sub-block, whose signed scale multiplies the exact integer sum.
 template <int MIS>
-__device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, int b, int t, const __half *xcol,
-                                          const __half *scol, float (&acc)[4]) {
+__device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, int b, int t, const int8_t *xcol,
+                                          const __half *scol, const float *sxs, float (&acc)[4]) {
+    constexpr uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
     const int8_t *scg = reinterpret_cast<const int8_t *>(bg + 192);
     const int8_t *scG = reinterpret_cast<const int8_t *>(bG + 192);
     const float dg = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bg + 208));
     const float dG = lmoe_h2f(*reinterpret_cast<const uint16_t *>(bG + 208));
-    // "-32" offset: one MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
+    // "-32" offset: one f16 MMA, A = the 16 sub-block scales of each row, B = 16-wide activation sums
     float co[4];
     {
         const uint32_t s0 = *reinterpret_cast<const uint32_t *>(scol + 16 * b + 2 * t);
@@ -450,12 +456,11 @@ __device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, 
         mma16816_z(co, sc_pair_half2(scg + 2 * t), sc_pair_half2(scG + 2 * t), sc_pair_half2(scg + 2 * t + 8),
                    sc_pair_half2(scG + 2 * t + 8), s0, s1);
     }
-    float al[4] = {0.f, 0.f, 0.f, 0.f}, ah[4] = {0.f, 0.f, 0.f, 0.f};
+    int al[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int n = 0; n < 2; n++) {
-        // the eight scales of this half, biased to unsigned so a byte permute turns them into floats
-        const uint32_t swg0 = lds32<MIS>(bg, 192 + 8 * n) ^ 0x80808080u, swg1 = lds32<MIS>(bg, 196 + 8 * n) ^ 0x80808080u;
-        const uint32_t swG0 = lds32<MIS>(bG, 192 + 8 * n) ^ 0x80808080u, swG1 = lds32<MIS>(bG, 196 + 8 * n) ^ 0x80808080u;
+        const uint32_t swg0 = lds32<MIS>(bg, 192 + 8 * n), swg1 = lds32<MIS>(bg, 196 + 8 * n);
+        const uint32_t swG0 = lds32<MIS>(bG, 192 + 8 * n), swG1 = lds32<MIS>(bG, 196 + 8 * n);
 #pragma unroll
         for (int c = 0; c < 2; c++) {
             const int l0 = 16 * c + 4 * t;
@@ -463,47 +468,43 @@ __device__ __forceinline__ void q6k_block(const uint8_t *bg, const uint8_t *bG, 
             const uint32_t qh_g = lds32<MIS>(bg, 128 + 32 * n + l0);
             const uint32_t qa_G = lds32<MIS>(bG, 64 * n + l0), qb_G = lds32<MIS>(bG, 64 * n + 32 + l0);
             const uint32_t qh_G = lds32<MIS>(bG, 128 + 32 * n + l0);
-            const __half *xp = xcol + 256 * b + 128 * n + 16 * c + 4 * t;
+            const int8_t *xp = xcol + 256 * b + 128 * n + l0;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 // group i: q1 (ql lo | qh 0-1), q2 (ql+32 lo | qh 2-3), q3 (ql hi | qh 4-5), q4 (ql+32 hi | qh 6-7)
                 const uint32_t qg = (i & 1) ? qb_g : qa_g, qG = (i & 1) ? qb_G : qa_G;
-                const uint32_t hg = (i & 1) ? (qh_g << 2) : (qh_g << 4), hG = (i & 1) ? (qh_G << 2) : (qh_G << 4);
-                const uint32_t hg8 = (i & 1) ? (qh_g >> 6) : (qh_g >> 4), hG8 = (i & 1) ? (qh_G >> 6) : (qh_G >> 4);
-                const uint32_t ml = (i & 2) ? 0x00F000F0u : 0x000F000Fu, mh = (i & 2) ? 0x03000300u : 0x00300030u;
-                const uint32_t a0 = (qg & ml) | (hg & mh), a1 = (qG & ml) | (hG & mh);
-                const uint32_t a2 = ((qg >> 8) & ml) | (hg8 & mh), a3 = ((qG >> 8) & ml) | (hG8 & mh);
-                const uint2 xv = *reinterpret_cast<const uint2 *>(xp + 32 * i);
-                float f[4];
-                mma16816_z(f, a0, a1, a2, a3, xv.x, xv.y);
+                const uint32_t lg = (i & 2) ? (qg >> 4) : qg, lG = (i & 2) ? (qG >> 4) : qG;
+                const uint32_t hg = i == 0 ? (qh_g << 4) : (i == 1 ? (qh_g << 2) : (i == 2 ? qh_g : (qh_g >> 2)));
+                const uint32_t hG = i == 0 ? (qh_G << 4) : (i == 1 ? (qh_G << 2) : (i == 2 ? qh_G : (qh_G >> 2)));
+                const uint32_t a0 = (lg & M4) | (hg & M2), a1 = (lG & M4) | (hG & M2);
+                const uint32_t xv = *reinterpret_cast<const uint32_t *>(xp + 32 * i);
+                int f[4];
+                imma16816_z(f, a0, a1, xv);
                 // scale index within the half: 2*i + c -> byte 2*(i & 1) + c of word i >> 1
-                const float sg = biased_byte_to_float(i < 2 ? swg0 : swg1, 2 * (i & 1) + c);
-                const float sG = biased_byte_to_float(i < 2 ? swG0 : swG1, 2 * (i & 1) + c);
-                if (i < 2) {
-                    al[0] += sg * f[0]; al[1] += sg * f[1]; al[2] += sG * f[2]; al[3] += sG * f[3];
-                } else {
-                    ah[0] += sg * f[0]; ah[1] += sg * f[1]; ah[2] += sG * f[2]; ah[3] += sG * f[3];
-                }
+                const int sg = sbyte(i < 2 ? swg0 : swg1, 2 * (i & 1) + c);
+                const int sG = sbyte(i < 2 ? swG0 : swG1, 2 * (i & 1) + c);
+                al[0] += sg * f[0]; al[1] += sg * f[1]; al[2] += sG * f[2]; al[3] += sG * f[3];
             }
         }
     }
-    acc[0] += dg * ((al[0] + 0.0625f * ah[0]) * 16777216.f - 32.f * co[0]);
-    acc[1] += dg * ((al[1] + 0.0625f * ah[1]) * 16777216.f - 32.f * co[1]);
-    acc[2] += dG * ((al[2] + 0.0625f * ah[2]) * 16777216.f - 32.f * co[2]);
-    acc[3] += dG * ((al[3] + 0.0625f * ah[3]) * 16777216.f - 32.f * co[3]);
+    const float2 cs = *reinterpret_cast<const float2 *>(sxs + 8 * b + 2 * t);
+    acc[0] += dg * (cs.x * (float)al[0] - 32.f * co[0]);
+    acc[1] += dg * (cs.y * (float)al[1] - 32.f * co[1]);
+    acc[2] += dG * (cs.x * (float)al[2] - 32.f * co[2]);
+    acc[3] += dG * (cs.y * (float)al[3] - 32.f * co[3]);
 }
 
 // 32 Q6_K rows: warp w takes row tile w & 1 (16 rows) and every (CW/2)-th super-block of it.
 // Super-blocks are 210 bytes long, so every other one starts 2 bytes off a word boundary.
 __device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, int nb, int warp, int g, int t,
-                                         const __half *xcol, const __half *scol, float (&acc)[4]) {
+                                         const int8_t *xcol, const __half *scol, const float *sxs, float (&acc)[4]) {
     const uint8_t *rg = stage + ((warp & 1) * 16 + g) * row_bytes;
     const uint8_t *rG = rg + 8 * row_bytes;
     for (int b = warp >> 1; b < nb; b += CW / 2) {
         const uint8_t *bg = rg + b * Q6K_BYTES, *bG = rG + b * Q6K_BYTES;
-        if (row_bytes & 2) q6k_block<2>(bg, bG, b, t, xcol, scol, acc); // odd block count: rows alternate too
-        else if (b & 1) q6k_block<1>(bg, bG, b, t, xcol, scol, acc);
-        else q6k_block<0>(bg, bG, b, t, xcol, scol, acc);
+        if (row_bytes & 2) q6k_block<2>(bg, bG, b, t, xcol, scol, sxs, acc); // odd block count: rows alternate too
+        else if (b & 1) q6k_block<1>(bg, bG, b, t, xcol, scol, sxs, acc);
+        else q6k_block<0>(bg, bG, b, t, xcol, scol, sxs, acc);
     }
 }
 
@@ -542,8 +543,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     extern __shared__ __align__(128) uint8_t smem[];
     const DecLayout L(P.hidden, P.ff, P.n_expert, P.t, P.top_k);
     uint8_t *ring = smem + L.o_ring;
-    __half *xc = reinterpret_cast<__half *>(smem + L.o_xc);
+    int8_t *xc = reinterpret_cast<int8_t *>(smem + L.o_xc);
     __half *sh = reinterpret_cast<__half *>(smem + L.o_s);
+    float *sxs = reinterpret_cast<float *>(smem + L.o_sx);
     float *red = reinterpret_cast<float *>(smem + L.o_red);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.o_bar);
     uint64_t *empty = full + NSTAGE;
@@ -684,17 +686,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                             float gv = 0.f, uv = 0.f;
 #pragma unroll
                             for (int w = 0; w < CW; w++) {
-                                gv += rb[(w * 16 + r) * NCOL + 2 * tk];
-                                gv += rb[(w * 16 + r) * NCOL + 2 * tk + 1];
-                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk];
-                                uv += rb[(w * 16 + 8 + r) * NCOL + 2 * tk + 1];
+#pragma unroll
+                                for (int d = 0; d < NDIG; d++) {
+                                    gv += rb[(w * 16 + r) * NCOL + NDIG * tk + d];
+                                    uv += rb[(w * 16 + 8 + r) * NCOL + NDIG * tk + d];
+                                }
                             }
                             const float sv = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
                             const float av = __fmul_rn(sv, uv);
-                            const __half h = __float2half_rn(av);
-                            __half *dst = P.act_hl + (size_t)U.pair[tk] * 2 * P.ff + tile * 8 + perm8(r);
-                            dst[0] = h;
-                            dst[P.ff] = __float2half_rn(av - __half2float(h));
+                            __stcg(P.act_f + (size_t)U.pair[tk] * P.ff + tile * 8 + r, av);
                         }
                     } else {
                         // weighted partial rows of this (pair, tile); summed over slots in phase 3.
@@ -704,8 +704,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                             float yv = 0.f;
 #pragma unroll
                             for (int w = 0; w < CW / 2; w++) {
-                                yv += rb[((2 * w + rt) * 16 + r) * NCOL + 2 * tk];
-                                yv += rb[((2 * w + rt) * 16 + r) * NCOL + 2 * tk + 1];
+#pragma unroll
+                                for (int d = 0; d < NDIG; d++) yv += rb[((2 * w + rt) * 16 + r) * NCOL + NDIG * tk + d];
                             }
                             const int slot = U.pair[tk] - U.tok[tk] * (K + 1);
                             if (slot < K) yv = __fmul_rn(yv, w_s[U.tok[tk] * K + slot]);
@@ -1014,6 +1014,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     // ---- phases 1 and 2 ----
     for (int phase = 1; phase <= 2; phase++) {
         const int tiles = phase == 1 ? tiles1 : tiles2;
+        // column pitch of the activation cache: 32 (mod 128) bytes for the 8-byte loads of phase 1, 16 for the
+        // 4-byte loads of phase 2, so that the columns of one load instruction cover distinct banks
+        const int xs_ph = phase == 1 ? L.xs : L.xs - 16;
         for (int kind = 0; kind < 2; kind++) { // shared units first, then routed
             const int shared = kind == 0;
             int u0, u1;
@@ -1036,8 +1039,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                                            : ((2 << 30) | (U.n_tok << 24) | (U.pair[0] << 12) | U.pair[1]);
                 if (key != xkey) {
                     bar_sync(1, CW * 32); // everyone is done with the previous contents
-                    if (phase == 1) stage_x(P, U, xc, sh, L.xs, L.ss, tid);
-                    else stage_act(P, U, xc, sh, L.xs, L.ss, tid);
+                    if (phase == 1) stage_rows<32, true>(P, U, xc, sh, sxs, xs_ph, L.ss, warp, lane);
+                    else stage_rows<16, false>(P, U, xc, sh, sxs, xs_ph, L.ss, warp, lane);
                     xkey = key;
                     bar_sync(1, CW * 32);
                 }
@@ -1046,16 +1049,16 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 const uint8_t *stage = ring + (size_t)s * L.stage_bytes;
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 // MMA columns beyond the staged ones alias them: their results are never read
-                const int col = g & (NCOL - 1);
-                if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
-                else unit_q6k(stage, row6, nb6, warp, g, t4, xc + col * L.xs, sh + col * L.ss, acc);
+                const int col = g < NCOL ? g : g - 2;
+                if (phase == 1) unit_q4k(stage, row4, nb4, warp, g, t4, xc + col * xs_ph, sh + col * L.ss, sxs, acc);
+                else unit_q6k(stage, row6, nb6, warp, g, t4, xc + col * xs_ph, sh + col * L.ss, sxs, acc);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 // K-split partials -> shared memory, handed to the epilogue warp (two buffers in flight)
                 const int buf = n % NRED;
                 mbar_wait(&red_free[buf], ((n / NRED) & 1) ^ 1, P.ctrl, 0x28 + phase);
                 float *rb = red + buf * (CW * 16 * NCOL);
-                if (t4 < NTOK) {
+                if (2 * t4 < NCOL) {
                     float *r0 = rb + (warp * 16 + g) * NCOL + 2 * t4;
                     r0[0] = acc[0]; r0[1] = acc[1];
                     r0[8 * NCOL] = acc[2]; r0[8 * NCOL + 1] = acc[3];
@@ -1181,7 +1184,7 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
     P.logits = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * E * 4, 256);
     P.ids_ws = reinterpret_cast<uint32_t *>(ws + o); o += lmoe_align_up((size_t)t * K * 4, 256);
     P.w_ws = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * K * 4, 256);
-    P.act_hl = reinterpret_cast<__half *>(ws + o); o += lmoe_align_up((size_t)t * (K + 1) * 2 * F * 2, 256);
+    P.act_f = reinterpret_cast<float *>(ws + o); o += lmoe_align_up((size_t)t * (K + 1) * F * 4, 256);
     P.ypart = reinterpret_cast<float *>(ws + o);
     void *args[] = {&P};
     LMOE_CUDA(cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(occ * sms), dim3(DEC_THREADS), args,
