@@ -414,7 +414,7 @@ def main():
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K x f16(hi+lo) -> f32",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K x s8 digits (3 per activation, 21 bits) -> s32 -> f32",
             "data": "synthetic",
             "config": {"workload": "config2: single MoE layer decode sweep B=1/2/4/8/16 (31 tokens per step)",
                        "hidden": H, "expert_ff": F, "n_expert": E, "top_k": K, "shared_expert": True,

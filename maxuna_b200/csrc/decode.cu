@@ -15,14 +15,14 @@
 //     copies (cp.async.bulk + mbarrier) through a 3-stage ring: each DISTINCT
 //     selected expert (and the shared expert) is read from HBM exactly once per
 //     call, however many tokens selected it.
-//   * Consumers decode 4/6-bit fields into f16 bit patterns in registers
-//     (the integers are placed in the f16 subnormal range, which is exact) and
-//     use mma.sync m16n8k16 with the weights as the A operand (16 rows) and the
-//     activations as B: each activation is carried as an f16 hi/lo pair in two
-//     MMA columns, so products are exact and accumulation is f32.  Sub-block
-//     scales are applied to the f32 accumulator fragments; the Q4_K "min" term
-//     and the Q6_K "-32" offset are one extra MMA per super-block against
-//     per-sub-block activation sums.
+//   * Consumers feed the 4/6-bit fields to the integer tensor-core path: a Q4_K nibble (after one mask)
+//     or a Q6_K value (low nibble | two high bits) is one unsigned byte of the A operand of mma.sync
+//     u8 x s8 -> s32 (m16n8k32 per 32-wide Q4_K sub-block, m16n8k16 per 16-wide Q6_K sub-block; 16 weight
+//     rows per MMA).  The activations are B: each value is quantized under the largest magnitude of its
+//     256-wide block to 21 bits and carried as three signed base-128 digits in three MMA columns, so the
+//     integer sums are exact; the integer sub-block scales multiply them (IMAD), and the float factors
+//     (d of the row, digit scale of the column) come in once per super-block.  The Q4_K "min" term and the
+//     Q6_K "-32" offset are one f16 MMA per super-block against per-sub-block activation sums.
 //   * Work units (8 gate+8 up rows, or 32 down rows, of one expert) are split
 //     contiguously over CTAs; the K dimension of a unit is split over the four
 //     consumer warps, whose partial sums go through mbarrier-guarded shared-memory
