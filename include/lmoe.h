@@ -245,6 +245,20 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
                                   uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                   size_t workspace_bytes, void *stream);
 
+/* The FFN half of a transformer layer around the block, src/model.rs:340-350:
+ *   ffn_normed = rms_norm(ffn_inp) * norm_weight;  out = ffn_inp + MoeBlock::forward(ffn_normed).
+ * rms_norm is candle's `RmsNorm` (x * 1/sqrt(mean(x^2) + eps) * weight, f32); its sum of squares runs in
+ * the same fixed order as the router logits (128 fmaf chains, lane fold, warp butterfly), so the expert
+ * selection downstream is reproducible.  ffn_inp / out [t, hidden] f32 (out must not alias ffn_inp),
+ * norm_weight [hidden] f32; ids_out / weights_out as in lmoe_moe_forward_*; t < LMOE_MM_ID_MIN_SEQ runs the
+ * decode kernel, larger t the grouped-GEMM path.  Workspace: lmoe_moe_layer_workspace_bytes(layer, t). */
+lmoe_status lmoe_rms_norm(const float *x, const float *weight, float eps, int64_t t, int64_t hidden,
+                          float *out, void *stream);
+size_t lmoe_moe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens);
+lmoe_status lmoe_moe_layer_forward(const lmoe_layer *layer, const float *ffn_inp, const float *norm_weight,
+                                   float eps, int64_t t, float *out, uint32_t *ids_out, float *weights_out,
+                                   void *workspace, size_t workspace_bytes, void *stream);
+
 /* Expert-parallel pieces (experts [first, first + n_local) of the layer are
  * resident on this GPU; the reference has no multi-GPU path, this is new):
  * run the routed experts of pre-routed, pre-dispatched rows.

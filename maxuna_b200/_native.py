@@ -54,6 +54,9 @@ PROTOTYPES = {
     "lmoe_ep_combine": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "lmoe_experts_forward_rows_f16": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_rows_workspace_bytes": (c_sz, [c_vp, c_i64]),
+    "lmoe_rms_norm": (c_i32, [c_vp, c_vp, C.c_float, c_i64, c_i64, c_vp, c_vp]),
+    "lmoe_moe_layer_workspace_bytes": (c_sz, [c_vp, c_i64]),
+    "lmoe_moe_layer_forward": (c_i32, [c_vp, c_vp, c_vp, C.c_float, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_tokens_workspace_bytes": (c_sz, [c_vp, c_i64, c_i64]),
     "lmoe_experts_forward_tokens_f16": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_shared_forward": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),

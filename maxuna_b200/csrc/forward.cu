@@ -100,3 +100,49 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     LMOE_CUDA(cudaStreamSynchronize(s));
     return LMOE_OK;
 }
+
+// ---- the transformer layer's FFN half around the block (src/model.rs:340-350) -------------
+extern "C" lmoe_status lmoe_rms_norm(const float *x, const float *weight, float eps, int64_t t, int64_t hidden,
+                                     float *out, void *stream) {
+    lmoe_clear_error();
+    if (!x || !weight || !out) return lmoe_fail(LMOE_ERR_INVALID, "x/weight/out is NULL");
+    if (t < 0 || t > (1 << 22) || hidden < 4 || hidden % 4 || hidden > (1 << 20))
+        return lmoe_fail(LMOE_ERR_INVALID, "rms_norm: t >= 0 and hidden a multiple of 4 required (t=%lld, hidden=%lld)",
+                         (long long)t, (long long)hidden);
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return lmoe_fail(LMOE_ERR_INVALID, "rms_norm: x, weight and out must be 16-byte aligned");
+    LMOE_CUDA(launch_rms_norm(x, weight, eps, t, (int)hidden, out, (cudaStream_t)stream));
+    return LMOE_OK;
+}
+
+extern "C" size_t lmoe_moe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens) {
+    if (!layer || max_tokens < 0) return 0;
+    return lmoe_layer_workspace_bytes(layer, max_tokens) + lmoe_align_up((size_t)(max_tokens < 1 ? 1 : max_tokens) * layer->hidden * 4, 256);
+}
+
+extern "C" lmoe_status lmoe_moe_layer_forward(const lmoe_layer *layer, const float *ffn_inp, const float *norm_weight,
+                                              float eps, int64_t t, float *out, uint32_t *ids_out, float *weights_out,
+                                              void *workspace, size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, ffn_inp, t, out);
+    if (st) return st;
+    if (!norm_weight) return lmoe_fail(LMOE_ERR_INVALID, "norm_weight is NULL");
+    if (ffn_inp == out) return lmoe_fail(LMOE_ERR_INVALID, "out must not alias ffn_inp (the residual is read after the block)");
+    if (t == 0) return LMOE_OK;
+    const size_t need = lmoe_moe_layer_workspace_bytes(layer, t);
+    if (!workspace || workspace_bytes < need)
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes for %lld tokens, got %zu", need, (long long)t,
+                         workspace_bytes);
+    const size_t block_ws = lmoe_layer_workspace_bytes(layer, t);
+    float *normed = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + block_ws);
+    if ((st = lmoe_rms_norm(ffn_inp, norm_weight, eps, t, layer->hidden, normed, stream))) return st;
+    // `use_mm`, src/moe.rs:236-240
+    if (t >= LMOE_MM_ID_MIN_SEQ)
+        st = lmoe_moe_forward_prefill(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);
+    else
+        st = lmoe_moe_forward_decode(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);
+    if (st) return st;
+    // x = ffn_inp + ffn_out
+    LMOE_CUDA(launch_add_inplace(out, ffn_inp, t * layer->hidden, (cudaStream_t)stream));
+    return LMOE_OK;
+}

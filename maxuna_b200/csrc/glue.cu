@@ -3,6 +3,7 @@
 // Reference: src/ops/silu_mul.metal:57-72, src/ops/combine.metal:70-133,
 // src/ops/mm_id.metal:207-269.
 #include "common.cuh"
+#include "route_math.cuh"
 
 namespace {
 
@@ -86,7 +87,46 @@ map0_kernel(const uint32_t *__restrict__ ids, int t, int top_k, int n_expert, ui
     if (threadIdx.x == 0) tpe[e] = (uint32_t)base;
 }
 
+// RMS norm of one row per warp (`ffn_norm`, src/model.rs:340): out = (x * inv) * weight with
+// inv = 1 / sqrt(sum(x^2) / hidden + eps).  The sum of squares runs in the router's reduction order
+// (128 fmaf chains over elements c, c + 128, ..., folded per lane and by the warp butterfly), so the
+// router input - and with it the expert selection - does not depend on the launch geometry.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps,
+                                                       int t, int hidden, float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= t) return;
+    const float *xr = x + (size_t)row * hidden;
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+    for (int i = lane * 4; i < hidden; i += 128) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        p0 = __fmaf_rn(v.x, v.x, p0);
+        p1 = __fmaf_rn(v.y, v.y, p1);
+        p2 = __fmaf_rn(v.z, v.z, p2);
+        p3 = __fmaf_rn(v.w, v.w, p3);
+    }
+    const float ss = lmoe_router_fold(p0, p1, p2, p3);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
+    float *orow = out + (size_t)row * hidden;
+    for (int i = lane * 4; i < hidden; i += 128) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        const float4 g = __ldg(reinterpret_cast<const float4 *>(w + i));
+        float4 o;
+        o.x = __fmul_rn(__fmul_rn(v.x, inv), g.x);
+        o.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
+        o.z = __fmul_rn(__fmul_rn(v.z, inv), g.z);
+        o.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
+        *reinterpret_cast<float4 *>(orow + i) = o;
+    }
+}
+
 } // namespace
+
+cudaError_t launch_rms_norm(const float *x, const float *w, float eps, int64_t t, int hidden, float *out, cudaStream_t s) {
+    if (t == 0) return cudaSuccess;
+    rms_norm_kernel<<<(unsigned)((t + 7) / 8), 256, 0, s>>>(x, w, eps, (int)t, hidden, out);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_silu_mul(const float *g, const float *u, int64_t n, float *out, cudaStream_t s) {
     if (n == 0) return cudaSuccess;

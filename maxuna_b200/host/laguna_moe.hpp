@@ -165,6 +165,14 @@ public:
         return Result::from(lmoe_moe_forward_decode(h_, x_normed, seq, out, ids_out, weights_out, workspace, workspace_bytes,
                                                     stream));
     }
+    // The FFN half of a layer (src/model.rs:340-350): out = ffn_inp + forward(ffn_norm(ffn_inp)).
+    size_t layer_workspace_bytes(int64_t max_tokens) const { return lmoe_moe_layer_workspace_bytes(h_, max_tokens); }
+    Result layer_forward(const float *ffn_inp, const float *ffn_norm_weight, float rms_eps, int64_t seq, float *out,
+                         void *workspace, size_t workspace_bytes, void *stream, uint32_t *ids_out = nullptr,
+                         float *weights_out = nullptr) const {
+        return Result::from(lmoe_moe_layer_forward(h_, ffn_inp, ffn_norm_weight, rms_eps, seq, out, ids_out, weights_out,
+                                                   workspace, workspace_bytes, stream));
+    }
     const lmoe_layer *handle() const { return h_; }
 
 private:

@@ -185,6 +185,27 @@ class MoeBlock:
                  None if w is None else w.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
         return (out, ids, w) if return_routing else out
 
+    def layer_forward(self, ffn_inp: torch.Tensor, norm_weight: torch.Tensor, eps: float = 1e-6,
+                      return_routing: bool = False):
+        """`lmoe_moe_layer_forward`: ``ffn_inp + MoeBlock::forward(ffn_norm(ffn_inp))``, src/model.rs:340-350."""
+        x = ffn_inp.to(torch.float32).contiguous()
+        seq = x.shape[0]
+        if x.dim() != 2 or x.shape[1] != self.hidden:
+            raise LmoeError(-1, f"ffn_inp must be [seq, {self.hidden}], got {tuple(x.shape)}")
+        g = norm_weight.to(torch.float32).contiguous()
+        out = torch.empty(seq, self.hidden, dtype=torch.float32, device=x.device)
+        ids = w = None
+        if return_routing:
+            ids = torch.empty(seq, self.n_expert_used, dtype=torch.int32, device=x.device)
+            w = torch.empty(seq, self.n_expert_used, dtype=torch.float32, device=x.device)
+        n = lib().lmoe_moe_layer_workspace_bytes(self._h, seq)
+        if getattr(self, "_lws", None) is None or self._lws.numel() < n:
+            self._lws = torch.zeros(n, dtype=torch.uint8, device=x.device)
+        check(lib().lmoe_moe_layer_forward(self._h, x.data_ptr(), g.data_ptr(), eps, seq, out.data_ptr(),
+                                           None if ids is None else ids.data_ptr(), None if w is None else w.data_ptr(),
+                                           self._lws.data_ptr(), self._lws.numel(), stream_ptr()))
+        return (out, ids, w) if return_routing else out
+
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor = None):
         """Host-buffer call (x and result in pinned host memory), `lmoe_moe_forward_host`."""
         assert not x_host.is_cuda and x_host.dtype == torch.float32 and x_host.is_contiguous()

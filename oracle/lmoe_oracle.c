@@ -354,6 +354,22 @@ void lmo_route_logits(const float *router, const float *x, int t, int hidden, in
             logits[(int64_t)i * n_expert + e] = router_dot(x + (int64_t)i * hidden, router + (int64_t)e * hidden, hidden);
 }
 
+/* `ffn_norm`, src/model.rs:340 (candle RmsNorm: x * 1/sqrt(mean(x^2) + eps) * weight, f32).  The sum of
+ * squares uses the router's reduction order (this build's definition, shared with the GPU). */
+void lmo_rms_norm(const float *x, const float *w, float eps, int t, int hidden, float *out) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < t; i++) {
+        const float *xr = x + (int64_t)i * hidden;
+        const float ss = router_dot(xr, xr, hidden);
+        const float mean = ss / (float)hidden;
+        const float inv = 1.0f / sqrtf(mean + eps);
+        for (int c = 0; c < hidden; c++) {
+            const float v = xr[c] * inv;
+            out[(int64_t)i * hidden + c] = v * w[c];
+        }
+    }
+}
+
 /* src/moe.rs:94-119.  ids ordered by descending selection score, ties to the
  * lower expert index (stable sort, src/moe.rs:104-105); weights gathered from
  * the UNBIASED probabilities, divided by max(sum, 2^-14) when `norm`, then

@@ -107,6 +107,15 @@ def route_logits(router: np.ndarray, x: np.ndarray) -> np.ndarray:
     return out
 
 
+def rms_norm(x, weight, eps=1e-6) -> np.ndarray:
+    """``lmo_rms_norm``: the reference's ``ffn_norm`` (src/model.rs:340), x ``[T,H]``, weight ``[H]``."""
+    x, weight = _f32(x), _f32(weight)
+    t, h = x.shape
+    out = np.empty((t, h), np.float32)
+    lib().lmo_rms_norm(_p(x), _p(weight), C.c_float(eps), C.c_int(t), C.c_int(h), _p(out))
+    return out
+
+
 def route_from_logits(logits, bias, top_k, scale=2.5, norm=True):
     """``lmo_route_from_logits`` -> (ids ``[T,K]`` u32, weights ``[T,K]`` f32)."""
     logits = _f32(logits)
