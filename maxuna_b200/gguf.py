@@ -9,6 +9,7 @@ GGUF tensor.
 from __future__ import annotations
 
 import ctypes as C
+import warnings
 
 import numpy as np
 import torch
@@ -73,7 +74,10 @@ class ExpertStack:
         """One upload of raw GGUF super-blocks (``expert_stack_classic``, src/gguf.rs:567-607)."""
         raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
         buf = torch.zeros(base_off + raw.size + 128, dtype=torch.uint8, device=device)
-        buf[base_off:base_off + raw.size] = torch.from_numpy(raw).to(device)
+        with warnings.catch_warnings():
+            # a read-only view of a mapped file is only read here: one host-to-device copy
+            warnings.simplefilter("ignore", UserWarning)
+            buf[base_off:base_off + raw.size] = torch.from_numpy(raw).to(device)
         return cls(buf, dtype, n_expert, n_out, k, base_off)
 
     @classmethod
