@@ -228,6 +228,63 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None):
     return res
 
 
+def measure_stack(dev, n_layers, steps=3, warmup=3):
+    """The expert portion of a Laguna-shaped model on ONE GPU (config 5 is quoted on 8 GPUs; 48 layers are
+    75.5 GB and fit one B200): a residual stack of `n_layers` MoE layers, x <- x + block_l(rms_norm_l(x)),
+    through `lmoe_moe_layer_forward`.  Batched decode of 64 sequences (one token each) and a 2048-token
+    prefill; for the 64-token step the mat-vec kernel (4 launches of 16 tokens per layer) is timed beside the
+    grouped-GEMM path the reference's `seq >= 32` rule picks."""
+    import torch
+
+    from maxuna_b200 import _native
+    from maxuna_b200.moe import MoeBlock
+
+    lib = _native.lib()
+    layers = [MoeBlock.random(H, F, E, K, seed=7000 + i, device=dev) for i in range(n_layers)]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    norms = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in layers]
+    need = max(lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 2048), lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 64))
+    ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    res = {"layers": n_layers, "weights_gb": n_layers * ((E + 1) * EXPERT_BYTES + ROUTER_BYTES) / 1e9}
+
+    def layer_path(x, bufs):
+        for i, ly in enumerate(layers):
+            a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
+            src = x if i == 0 else a
+            _native.check(lib.lmoe_moe_layer_forward(ly.handle, src.data_ptr(), norms[i].data_ptr(), 1e-6, x.shape[0],
+                                                     b.data_ptr(), None, None, ws.data_ptr(), ws.numel(), stream))
+
+    def matvec_path(x, bufs, normed):
+        t = x.shape[0]
+        for i, ly in enumerate(layers):
+            a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
+            src = x if i == 0 else a
+            _native.check(lib.lmoe_rms_norm(src.data_ptr(), norms[i].data_ptr(), 1e-6, t, H, normed.data_ptr(), stream))
+            _native.check(lib.lmoe_moe_forward_decode(ly.handle, normed.data_ptr(), t, b.data_ptr(), None, None,
+                                                      ws.data_ptr(), ws.numel(), stream))
+            b.add_(src)
+
+    for name, t, fn in (("decode64_grouped_gemm", 64, layer_path), ("decode64_matvec", 64, matvec_path),
+                        ("prefill2048", 2048, layer_path)):
+        x = torch.randn(t, H, generator=gen, device=dev)
+        bufs = [torch.empty(t, H, device=dev), torch.empty(t, H, device=dev)]
+        extra = (torch.empty(t, H, device=dev),) if fn is matvec_path else ()
+        for _ in range(warmup):
+            fn(x, bufs, *extra)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn(x, bufs, *extra)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        res[name] = {"tokens": t, "ms_per_pass": ms, "tok_per_s": t / ms * 1e3, "us_per_layer": ms * 1e3 / n_layers}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -239,6 +296,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (grouped GEMM) measurement")
     ap.add_argument("--prefill-only", action="store_true", help="profiling aid: run only the prefill measurement and print it")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="profiling aid: token count of the prefill measurement")
+    ap.add_argument("--stack-layers", type=int, default=0,
+                    help="run only the residual stack of this many MoE layers on one GPU (48 = the model's expert portion) and print it")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -265,6 +324,12 @@ def main():
     from maxuna_b200.moe import MoeBlock
 
     _native.lib()
+    if args.stack_layers > 0:
+        if rank == 0:
+            print(json.dumps({"stack": measure_stack(dev, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=args.warmup)}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.prefill_only:
         res = measure_prefill(dev, rank, world, steps=max(1, min(args.steps, 8)), warmup=args.warmup,
                               tokens=args.prefill_tokens or None)

@@ -57,6 +57,10 @@ enum {
 /* Token count from which the block switches from the indexed mat-vec to the
  * grouped GEMM: `MM_ID_MIN_SEQ`, src/ops/mod.rs:31. */
 #define LMOE_MM_ID_MIN_SEQ 32
+/* Largest token count of the fused mat-vec (decode) entry.  The entries that pick a path themselves
+ * (lmoe_moe_forward_host, lmoe_moe_layer_forward) use the mat-vec kernel up to here and the grouped GEMM
+ * beyond: on B200 the mat-vec kernel is ahead at 64 tokens (772 against 901 us per layer). */
+#define LMOE_DECODE_MAX_SEQ 64
 
 const char *lmoe_version(void);
 /* Message of the last failing call made by this thread ("" if none). */
@@ -238,7 +242,7 @@ lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, in
                                      size_t workspace_bytes, void *stream);
 
 /* `MoeBlock::forward` with HOST buffers: copies x to the device, runs the decode
- * or prefill path (t >= LMOE_MM_ID_MIN_SEQ -> prefill, src/moe.rs:236-240),
+ * or prefill path (t > LMOE_DECODE_MAX_SEQ -> prefill; the reference's own switch, src/moe.rs:236-240, is at 32),
  * copies the result back and synchronises the stream. `x_host` / `out_host`
  * should be pinned for full copy bandwidth. */
 lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
@@ -250,7 +254,7 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
  * rms_norm is candle's `RmsNorm` (x * 1/sqrt(mean(x^2) + eps) * weight, f32); its sum of squares runs in
  * the same fixed order as the router logits (128 fmaf chains, lane fold, warp butterfly), so the expert
  * selection downstream is reproducible.  ffn_inp / out [t, hidden] f32 (out must not alias ffn_inp),
- * norm_weight [hidden] f32; ids_out / weights_out as in lmoe_moe_forward_*; t < LMOE_MM_ID_MIN_SEQ runs the
+ * norm_weight [hidden] f32; ids_out / weights_out as in lmoe_moe_forward_*; t <= LMOE_DECODE_MAX_SEQ runs the
  * decode kernel, larger t the grouped-GEMM path.  Workspace: lmoe_moe_layer_workspace_bytes(layer, t). */
 lmoe_status lmoe_rms_norm(const float *x, const float *weight, float eps, int64_t t, int64_t hidden,
                           float *out, void *stream);

@@ -39,7 +39,7 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
     lmoe_clear_error();
     lmoe_status st = forward_check(layer, x, t, out);
     if (st) return st;
-    if (t > 64) return lmoe_fail(LMOE_ERR_INVALID, "the decode path takes at most 64 tokens, got %lld", (long long)t);
+    if (t > LMOE_DECODE_MAX_SEQ) return lmoe_fail(LMOE_ERR_INVALID, "the decode path takes at most %d tokens, got %lld", LMOE_DECODE_MAX_SEQ, (long long)t);
     const int step = decode_max_tokens();
     for (int64_t t0 = 0; t0 < t; t0 += step) {
         const int n = (int)(t - t0 < step ? t - t0 : step);
@@ -85,8 +85,9 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     float *wd = reinterpret_cast<float *>(ws + kernel_ws + 2 * xb + ib);
     LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
     lmoe_status st;
-    // `use_mm`, src/moe.rs:236-240
-    if (t >= LMOE_MM_ID_MIN_SEQ)
+    // the reference switches to its grouped GEMM at 32 tokens (`use_mm`, src/moe.rs:236-240); here the mat-vec
+    // kernel, which streams each distinct expert once per 16 tokens, stays ahead up to its limit of 64
+    if (t > LMOE_DECODE_MAX_SEQ)
         st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
                                       workspace, kernel_ws, stream);
     else
@@ -136,8 +137,8 @@ extern "C" lmoe_status lmoe_moe_layer_forward(const lmoe_layer *layer, const flo
     const size_t block_ws = lmoe_layer_workspace_bytes(layer, t);
     float *normed = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + block_ws);
     if ((st = lmoe_rms_norm(ffn_inp, norm_weight, eps, t, layer->hidden, normed, stream))) return st;
-    // `use_mm`, src/moe.rs:236-240
-    if (t >= LMOE_MM_ID_MIN_SEQ)
+    // mat-vec kernel up to 64 tokens, grouped GEMM beyond (measured crossover; the reference's own is 32)
+    if (t > LMOE_DECODE_MAX_SEQ)
         st = lmoe_moe_forward_prefill(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);
     else
         st = lmoe_moe_forward_decode(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);

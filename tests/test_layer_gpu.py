@@ -65,3 +65,28 @@ def test_layer_forward_argument_errors():
     blk = MoeBlock.random(256, 256, 8, 3, seed=63, device=dev)
     with pytest.raises(LmoeError):
         blk.layer_forward(torch.zeros(2, 128, device=dev), torch.ones(128, device=dev))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t", [4, 40])
+def test_stack_of_layers_matches_oracle(orc, t):
+    """A short residual stack (the shape of BASELINE config 5 at toy size): x <- x + block_l(norm_l(x))."""
+    from maxuna_b200.moe import MoeBlock
+
+    orc.build()
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(70 + t)
+    layers = [MoeBlock.random(256, 256, 8, 3, seed=80 + i, device=dev, weight_std=0.25) for i in range(3)]
+    norms = [rng.uniform(0.5, 1.5, 256).astype(np.float32) for _ in layers]
+    x0 = rng.standard_normal((t, 256)).astype(np.float32)
+    x = torch.from_numpy(x0).to(dev)
+    want = x0.copy()
+    for i, (blk, g) in enumerate(zip(layers, norms)):
+        x, ids, _ = blk.layer_forward(x, torch.from_numpy(g).to(dev), 1e-6, return_routing=True)
+        host = blk.host_layer(orc)
+        ffn_out, ids_o, _ = host.forward(orc.rms_norm(want, g, 1e-6))
+        if i == 0:      # later layers see inputs that differ in the last bits, so only the values are compared
+            assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+        want = want + ffn_out
+    torch.cuda.synchronize()
+    assert orc.rel_l2(x.cpu().numpy(), want) < 2e-3
