@@ -46,6 +46,8 @@ H, F, E, K = 3072, 1024, 256, 10
 SWEEP = (1, 2, 4, 8, 16)
 EXPERT_BYTES = 2 * F * (H // 256) * 144 + H * (F // 256) * 210  # 6 119 424
 ROUTER_BYTES = E * H * 4
+# DRAM traffic of one decode sweep (B = 1, 2, 4, 8, 16) measured once under ncu: 72.1 + 135.8 + 224.3 + 415.1 + 737.2 MB
+NCU_TRAFFIC_PER_SWEEP = 1.5845e9
 NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
            "clocks_event_reasons.sw_power_cap")
@@ -492,7 +494,10 @@ def main():
                     "h2d_bytes_per_step": tokens_per_step * H * 4, "d2h_bytes_per_step": tokens_per_step * H * 4,
                     "steps": e2e_steps},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                         "frac": achieved / peak_gbs, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak_gbs, "traffic": NCU_TRAFFIC_PER_SWEEP, "peak_source": peak_src,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the five launches of one "
+                                           "sweep in an ncu --set full capture (profiles/moe_decode_kernel_sweep.md; "
+                                           "algorithmic bytes of that sweep: 1.457e9)",
                          "kernel": "moe_decode_kernel", "algorithmic_bytes_per_sweep": bytes_sweep},
             "sweep": sweep_tab,
             "clocks": clocks,
