@@ -281,16 +281,19 @@ __global__ void __launch_bounds__(256) gather_tiles_kernel(const void *__restric
     }
     __syncthreads();
     const int slot0 = slot0_s, srow0 = row0_s, rows = (int)tpe[e], k_stages = k / MM_K, chunks = k / 8;
-    for (int i = blockIdx.y; i < rows; i += gridDim.y) {
+    // one warp per routed row, eight rows of the expert in flight per block
+    const int lane = threadIdx.x & 31;
+    for (int i = blockIdx.y * 8 + (threadIdx.x >> 5); i < rows; i += gridDim.y * 8) {
         const int fid = ids_map[(size_t)e * map_stride + i];
         const size_t srow = (size_t)(x_per_row == 1 ? fid / top_k : fid) * k;
         const int slot = slot0 + i / MM_N, rr = i % MM_N;
-        if (threadIdx.x == 0) {
+        if (lane == 0) {
             if (pos) pos[fid] = slot * MM_N + rr;
             if (spos) spos[fid] = srow0 + i;
             if (sfid) sfid[srow0 + i] = fid;
         }
-        for (int ci = threadIdx.x; ci < chunks; ci += 256) {
+#pragma unroll 4
+        for (int ci = lane; ci < chunks; ci += 32) {
             uint4 o;
             if (XF16) {
                 // rows already in f16 (the expert-parallel wire format): only the order inside the chunk changes
