@@ -151,7 +151,7 @@ def test_routing_known_answers(orc, dev):
     assert torch.equal(ids, ids2) and torch.equal(w, w2)
 
 
-@pytest.mark.parametrize("t", [1, 2, 3, 16, 33, 257])
+@pytest.mark.parametrize("t", [1, 2, 3, 16, 33, 257, 2100, 2400])   # the last two: tokens per block sized to whole waves
 def test_routing_bit_exact_vs_oracle(orc, dev, t):
     from maxuna_b200 import ops
 
