@@ -20,6 +20,11 @@ int main() {
     r = ops::combine((const float *)4096, nullptr, (const float *)4096, 1, 200, 8, (float *)4096, nullptr);
     if (r.ok()) return 1;
     if (!ops::supported(GgmlDType::Q6K, 10)) return 1;
+    // the layer entry without a layer handle: an Err
+    MoeBlock blk;
+    r = blk.layer_forward((const float *)4096, (const float *)4096, 1e-6f, 1, (float *)8192, nullptr, 0, nullptr);
+    if (r.ok() || r.message.find("layer is NULL") == std::string::npos) { std::printf("bad: %s\n", r.message.c_str()); return 1; }
+    if (blk.layer_workspace_bytes(16) != 0) return 1;
     std::printf("ok\n");
     return 0;
 }
