@@ -234,8 +234,8 @@ def measure_stack(dev, n_layers, steps=3, warmup=3):
     """The expert portion of a Laguna-shaped model on ONE GPU (config 5 is quoted on 8 GPUs; 48 layers are
     75.5 GB and fit one B200): a residual stack of `n_layers` MoE layers, x <- x + block_l(rms_norm_l(x)),
     through `lmoe_moe_layer_forward`.  Batched decode of 64 sequences (one token each) and a 2048-token
-    prefill; for the 64-token step the mat-vec kernel (4 launches of 16 tokens per layer) is timed beside the
-    grouped-GEMM path the reference's `seq >= 32` rule picks."""
+    prefill; for the 64-token step the grouped-GEMM path (what the reference's `seq >= 32` rule would pick) is
+    timed beside the mat-vec kernel that the layer entry uses up to 64 tokens."""
     import torch
 
     from maxuna_b200 import _native
@@ -258,21 +258,21 @@ def measure_stack(dev, n_layers, steps=3, warmup=3):
             _native.check(lib.lmoe_moe_layer_forward(ly.handle, src.data_ptr(), norms[i].data_ptr(), 1e-6, x.shape[0],
                                                      b.data_ptr(), None, None, ws.data_ptr(), ws.numel(), stream))
 
-    def matvec_path(x, bufs, normed):
+    def gemm_path(x, bufs, normed):
         t = x.shape[0]
         for i, ly in enumerate(layers):
             a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
             src = x if i == 0 else a
             _native.check(lib.lmoe_rms_norm(src.data_ptr(), norms[i].data_ptr(), 1e-6, t, H, normed.data_ptr(), stream))
-            _native.check(lib.lmoe_moe_forward_decode(ly.handle, normed.data_ptr(), t, b.data_ptr(), None, None,
+            _native.check(lib.lmoe_moe_forward_prefill(ly.handle, normed.data_ptr(), t, b.data_ptr(), None, None,
                                                       ws.data_ptr(), ws.numel(), stream))
             b.add_(src)
 
-    for name, t, fn in (("decode64_grouped_gemm", 64, layer_path), ("decode64_matvec", 64, matvec_path),
+    for name, t, fn in (("decode64", 64, layer_path), ("decode64_grouped_gemm", 64, gemm_path),
                         ("prefill2048", 2048, layer_path)):
         x = torch.randn(t, H, generator=gen, device=dev)
         bufs = [torch.empty(t, H, device=dev), torch.empty(t, H, device=dev)]
-        extra = (torch.empty(t, H, device=dev),) if fn is matvec_path else ()
+        extra = (torch.empty(t, H, device=dev),) if fn is gemm_path else ()
         for _ in range(warmup):
             fn(x, bufs, *extra)
         torch.cuda.synchronize()

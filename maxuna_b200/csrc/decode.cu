@@ -1,4 +1,4 @@
-// Fused MoE block for decode batches (t <= 16 tokens per launch): routing, the
+// Fused MoE block for decode batches (t <= 64 tokens per launch): routing, the
 // gate/up mat-vecs with SwiGLU, the down mat-vec, the weighted combine and the
 // shared expert in ONE persistent kernel.
 //
@@ -54,7 +54,7 @@ constexpr int SYNC_WORDS = SYNC_PASS0 + 1024;
 constexpr int NTOK = 2;         // tokens per pass over an expert's weights
 constexpr int NDIG = 3;         // signed base-128 digits per activation (21 bits under a per-256 scale)
 constexpr int NCOL = NDIG * NTOK; // MMA columns in use: (token, digit)
-constexpr int DEC_MAX_T = 16;
+constexpr int DEC_MAX_T = 64;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 struct DecodeParams {

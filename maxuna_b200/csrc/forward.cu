@@ -86,7 +86,7 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
     lmoe_status st;
     // the reference switches to its grouped GEMM at 32 tokens (`use_mm`, src/moe.rs:236-240); here the mat-vec
-    // kernel, which streams each distinct expert once per 16 tokens, stays ahead up to its limit of 64
+    // kernel, which streams each distinct expert once per launch, stays ahead up to its limit of 64 tokens
     if (t > LMOE_DECODE_MAX_SEQ)
         st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
                                       workspace, kernel_ws, stream);

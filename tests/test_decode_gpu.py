@@ -62,12 +62,31 @@ def full_host(orc, full_block):
     return full_block.host_layer(orc)
 
 
-@pytest.mark.parametrize("t", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("t", [1, 2, 4, 8, 16, 31])
 def test_decode_production_shape(orc, full_block, full_host, t):
     # BASELINE configs 1 and 2: hidden 3072, 256 experts + shared, top-10, N(0,1) inputs
     x = np.random.default_rng(1000 + t).standard_normal((t, 3072)).astype(np.float32)
     _, err = _check(orc, full_block, full_host, x)
-    assert err < 1e-4  # f16 hi/lo operands keep the kernel at f32-level accuracy
+    assert err < 1e-4  # 21-bit activations and exact integer products keep the kernel at f32-level accuracy
+
+
+def test_decode_64_tokens_in_one_launch(orc, full_block, full_host, dev):
+    """The mat-vec entry at its limit: 64 tokens share one pass over the distinct experts."""
+    from maxuna_b200._native import check, lib
+    from maxuna_b200.gguf import stream_ptr
+
+    x = np.random.default_rng(64).standard_normal((64, 3072)).astype(np.float32)
+    xd = torch.from_numpy(x).to(dev)
+    out = torch.empty_like(xd)
+    ids = torch.empty(64, 10, dtype=torch.int32, device=dev)
+    ws = full_block.workspace(64)
+    check(lib().lmoe_moe_forward_decode(full_block.handle, xd.data_ptr(), 64, out.data_ptr(), ids.data_ptr(), None,
+                                        ws.data_ptr(), ws.numel(), stream_ptr()))
+    torch.cuda.synchronize()
+    full_block.check_device_flag()
+    want, ids_o, _ = full_host.forward(x)
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+    assert orc.rel_l2(out.cpu().numpy(), want) < 1e-4
 
 
 def test_decode_host_buffers(orc, full_block, full_host):
