@@ -97,13 +97,13 @@ def _worker(rank, world, port, q, token_level=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("token_level", [False, True])
-def test_expert_parallel_two_cpu_ranks(orc, token_level):
+@pytest.mark.parametrize("token_level,world", [(False, 2), (True, 2), (True, 4)])
+def test_expert_parallel_cpu_ranks(orc, token_level, world):
     orc.build()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, token_level)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, token_level)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in procs]
