@@ -496,7 +496,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                          "frac": achieved / peak_gbs, "traffic": NCU_TRAFFIC_PER_SWEEP, "peak_source": peak_src,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the five launches of one "
-                                           "sweep in an ncu --set full capture (profiles/moe_decode_kernel_sweep.md; "
+                                           "sweep in an ncu --set full capture (summary kept with the committed profiles; "
                                            "algorithmic bytes of that sweep: 1.457e9)",
                          "kernel": "moe_decode_kernel", "algorithmic_bytes_per_sweep": bytes_sweep},
             "sweep": sweep_tab,
