@@ -54,16 +54,21 @@ enum {
     LMOE_Q6_K = 14  /* 210-byte super-block, 256 weights (src/ops/mv.metal:70-75) */
 };
 
-/* Token count from which the block switches from the indexed mat-vec to the
- * grouped GEMM: `MM_ID_MIN_SEQ`, src/ops/mod.rs:31. */
+/* The reference's own switch from the indexed mat-vec to the grouped GEMM:
+ * `MM_ID_MIN_SEQ`, src/ops/mod.rs:31 (kept for documentation; see lmoe_mm_id_min_seq). */
 #define LMOE_MM_ID_MIN_SEQ 32
-/* Largest token count of the fused mat-vec (decode) entry.  The entries that pick a path themselves
- * (lmoe_moe_forward_host, lmoe_moe_layer_forward) use the mat-vec kernel up to here and the grouped GEMM
- * beyond: on B200 the mat-vec kernel, which takes all 64 tokens in one launch, is ahead there (535 against
- * 901 us per layer). */
+/* Tokens one launch of the fused mat-vec (decode) kernel serves.  On B200 that kernel, which takes all 64
+ * tokens in one launch and streams each of their distinct experts once, is ahead of the grouped GEMM up to
+ * here (535 against 901 us per layer at 64 tokens). */
 #define LMOE_DECODE_MAX_SEQ 64
 
 const char *lmoe_version(void);
+/* Token count from which every entry that picks a path itself (lmoe_moe_forward_host,
+ * lmoe_moe_layer_forward, lmoe_experts_forward, and the host mirrors above this ABI) uses the grouped
+ * GEMM; below it the mat-vec kernel.  LMOE_DECODE_MAX_SEQ + 1 unless the reference's process-wide switches
+ * are set (src/ops/mod.rs:24-60): LAGUNA_MM_ID_MIN_SEQ=<n> moves it, LAGUNA_NO_MM_ID (presence) forces the
+ * mat-vec path everywhere.  Read once per process. */
+int64_t lmoe_mm_id_min_seq(void);
 /* Message of the last failing call made by this thread ("" if none). */
 const char *lmoe_last_error(void);
 
@@ -122,8 +127,9 @@ lmoe_status lmoe_route(const float *router, const float *bias, const float *x, i
  * library instead of a workspace.  It has no counterpart in the reference.
  *   - limit: t * n_expert <= 32768 (128 KB of scratch held by every GPU that loads the
  *     library, until exit); larger requests are rejected with LMOE_ERR_INVALID;
- *   - the first call on each device looks up the array's device address: make that call once
- *     before starting any stream capture;
+ *   - the first call on each device looks up the array's device address, and the first call with
+ *     more than 64 tokens and hidden = 3072 also sets a kernel attribute (cudaFuncSetAttribute):
+ *     make one call of each kind you will use before starting any stream capture;
  *   - all calls share the one array (it keeps the previous call's logits; nothing needs
  *     clearing because each call overwrites what it reads): calls that overlap on the GPU,
  *     e.g. on two streams, race.
@@ -143,8 +149,8 @@ lmoe_status lmoe_route_from_logits(const float *logits, const float *bias, int64
  *   out[t, s, :] = W[ids[t, s]] . x[t, (x_per_row == 1 ? 0 : s), :]
  *   x [t, x_per_row, k] f32, ids [t_ids, top_k] u32, out [t, top_k, n_out] f32.
  * Errors (not faults): k != stack k, t_ids != t, x_per_row not in {1, top_k},
- * k % 256 != 0. An id >= n_expert yields a zero row and sets the device flag
- * of `lmoe_check_device_flag`. */
+ * k % 256 != 0, top_k > 65535. An id >= n_expert yields a zero row (this op has no
+ * workspace and therefore no device flag; the whole-block entries record one). */
 lmoe_status lmoe_mul_mv_id(const lmoe_expert_stack *stack, const float *x, int64_t t, int64_t x_per_row,
                            int64_t k, const uint32_t *ids, int64_t t_ids, int64_t top_k, float *out,
                            void *stream);
@@ -221,14 +227,15 @@ void lmoe_layer_destroy(lmoe_layer *layer);
 size_t lmoe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens);
 
 /* `MoeBlock::forward` on the decode path (t < LMOE_MM_ID_MIN_SEQ in the
- * reference; any t <= 64 here), src/moe.rs:73-78 with the mv_id branch of
+ * reference; any t here: LMOE_DECODE_MAX_SEQ tokens per launch), src/moe.rs:73-78 with the mv_id branch of
  * src/moe.rs:221-323 fused: route, stream each DISTINCT selected expert and the
  * shared expert once, SwiGLU and the weighted combine in the same kernels.
  *   x [t, hidden] f32 -> out [t, hidden] f32; ids_out [t, top_k] / weights_out
  * [t, top_k] receive the routing decision when non-NULL.
  * The workspace needs no initialisation.  The kernel's CTAs synchronise through
  * device words owned by `layer`: at most one decode call in flight per layer
- * handle (create a second handle over the same stacks for a second stream). */
+ * handle (create a second handle over the same stacks for a second stream).  A call
+ * on another stream while the previous one is still running fails with LMOE_ERR_INVALID. */
 lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
                                     uint32_t *ids_out, float *weights_out, void *workspace,
                                     size_t workspace_bytes, void *stream);
@@ -243,7 +250,7 @@ lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, in
                                      size_t workspace_bytes, void *stream);
 
 /* `MoeBlock::forward` with HOST buffers: copies x to the device, runs the decode
- * or prefill path (t > LMOE_DECODE_MAX_SEQ -> prefill; the reference's own switch, src/moe.rs:236-240, is at 32),
+ * or prefill path (t >= lmoe_mm_id_min_seq() -> prefill; the reference's own switch, src/moe.rs:236-240, is at 32),
  * copies the result back and synchronises the stream. `x_host` / `out_host`
  * should be pinned for full copy bandwidth. */
 lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
@@ -255,7 +262,7 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
  * rms_norm is candle's `RmsNorm` (x * 1/sqrt(mean(x^2) + eps) * weight, f32); its sum of squares runs in
  * the same fixed order as the router logits (128 fmaf chains, lane fold, warp butterfly), so the expert
  * selection downstream is reproducible.  ffn_inp / out [t, hidden] f32 (out must not alias ffn_inp),
- * norm_weight [hidden] f32; ids_out / weights_out as in lmoe_moe_forward_*; t <= LMOE_DECODE_MAX_SEQ runs the
+ * norm_weight [hidden] f32; ids_out / weights_out as in lmoe_moe_forward_*; t < lmoe_mm_id_min_seq() runs the
  * decode kernel, larger t the grouped-GEMM path.  Workspace: lmoe_moe_layer_workspace_bytes(layer, t). */
 lmoe_status lmoe_rms_norm(const float *x, const float *weight, float eps, int64_t t, int64_t hidden,
                           float *out, void *stream);

@@ -18,6 +18,7 @@ c_i32, c_i64, c_f32, c_sz, c_vp = C.c_int32, C.c_int64, C.c_float, C.c_size_t, C
 PROTOTYPES = {
     "lmoe_version": (C.c_char_p, []),
     "lmoe_last_error": (C.c_char_p, []),
+    "lmoe_mm_id_min_seq": (c_i64, []),
     "lmoe_expert_stack_create": (c_i32, [c_i32, c_i64, c_i64, c_i64, c_vp, c_sz, c_sz, C.POINTER(c_vp)]),
     "lmoe_expert_stack_wrap": (c_i32, [c_i32, c_i64, c_i64, c_i64, c_vp, c_sz, c_sz, C.POINTER(c_vp)]),
     "lmoe_expert_stack_destroy": (None, [c_vp]),

@@ -192,7 +192,7 @@ lmoe_status lmoe_id_shape_check(const lmoe_expert_stack *stack, const void *x, i
                                 int64_t k, const void *ids, int64_t t_ids, int64_t top_k, const void *out) {
     REQUIRE(stack != nullptr, "expert stack is NULL");
     REQUIRE(x && ids && out, "x/ids/out is NULL");
-    REQUIRE(t >= 0 && top_k >= 1, "t must be >= 0 and top_k >= 1");
+    REQUIRE(t >= 0 && top_k >= 1 && top_k <= 65535, "t must be >= 0 and top_k in [1, 65535]");
     REQUIRE(k == stack->k, "x k (%lld) does not match expert stack k (%lld)", (long long)k, (long long)stack->k);
     REQUIRE(t_ids == t, "ids t (%lld) does not match x t (%lld)", (long long)t_ids, (long long)t);
     REQUIRE(x_per_row == 1 || x_per_row == top_k,
@@ -319,16 +319,31 @@ extern "C" lmoe_status lmoe_layer_create(int64_t hidden, int64_t expert_ff, int6
         cudaFree(sync);
         return lmoe_fail(LMOE_ERR_CUDA, "could not clear the layer's synchronisation words");
     }
-    *out = new (std::nothrow) lmoe_layer{hidden, expert_ff, n_expert, top_k, scale, norm, router, bias, gate, up, down,
-                                         shared_gate, shared_up, shared_down, sync};
-    if (*out == nullptr) cudaFree(sync);
-    REQUIRE(*out != nullptr, "out of host memory");
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaFree(sync);
+        return lmoe_fail(LMOE_ERR_CUDA, "could not create the layer's completion event");
+    }
+    lmoe_layer *ly = new (std::nothrow) lmoe_layer;
+    if (ly == nullptr) {
+        cudaFree(sync);
+        cudaEventDestroy(ev);
+    }
+    REQUIRE(ly != nullptr, "out of host memory");
+    ly->hidden = hidden; ly->expert_ff = expert_ff; ly->n_expert = n_expert; ly->top_k = top_k;
+    ly->scale = scale; ly->norm = norm; ly->router = router; ly->bias = bias;
+    ly->gate = gate; ly->up = up; ly->down = down;
+    ly->sh_gate = shared_gate; ly->sh_up = shared_up; ly->sh_down = shared_down;
+    ly->sync = sync;
+    ly->dec_event = ev;
+    *out = ly;
     return LMOE_OK;
 }
 
 extern "C" void lmoe_layer_destroy(lmoe_layer *layer) {
     if (!layer) return;
     cudaFree(layer->sync);
+    if (layer->dec_event) cudaEventDestroy(layer->dec_event);
     delete layer;
 }
 

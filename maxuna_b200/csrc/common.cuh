@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/lmoe.h"
 
 #define QK_K 256
@@ -54,6 +56,12 @@ struct lmoe_layer {
     // device words the fused decode kernel synchronises its CTAs through; zero between launches,
     // so one decode call at a time per layer
     uint32_t *sync;
+    // guard of that rule: the stream and completion event of the latest decode call.  A call on a
+    // different stream while the event is still pending is refused instead of corrupting `sync`.
+    mutable std::mutex dec_mutex;
+    mutable cudaEvent_t dec_event = nullptr;
+    mutable cudaStream_t dec_stream = nullptr;
+    mutable bool dec_pending = false;
 };
 
 static inline int lmoe_type_size(int32_t dtype) {

@@ -67,7 +67,7 @@ struct DecodeParams {
     int t, hidden, ff, n_expert, top_k;
     float scale;
     int norm, has_shared;
-    uint32_t *ctrl;   // workspace: [0..3] device flag (zeroed by the launch with first_launch set), [8192..] optional timing stamps
+    uint32_t *ctrl;   // workspace: [0..3] device flag (zeroed by the launch with first_launch set)
     uint32_t *sync;   // owned by the layer, zero between launches: [0] grid barrier, [1] exit count, [32..] per-pass counts
     int first_launch;
     float *logits;    // [t][n_expert]
@@ -508,16 +508,6 @@ __device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, in
     }
 }
 
-#ifdef LMOE_DECODE_TIMING
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long v;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
-    return v;
-}
-#define STAMP(i) do { if (tid == 0) reinterpret_cast<unsigned long long *>(P.ctrl + 8192)[blockIdx.x * 16 + (i)] = gtime(); } while (0)
-#else
-#define STAMP(i) do { } while (0)
-#endif
 
 // Per-pass hand-over between phases 1 and 2 (small batches).  Out of line on purpose: they run once per
 // pass and must not disturb the register allocation of the unit loops.
@@ -736,7 +726,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     // ========================= consumer warps =========================
     const int g = lane >> 2, t4 = lane & 3;
 
-    STAMP(0);
     if (P.first_launch && blockIdx.x == 0 && tid < 4) P.ctrl[tid] = 0u; // a fresh device flag for this call
     // ---- phase 0a: router logits (bit-specified reduction, see route_math.cuh) ----
     if (P.hidden == 128 * 24) {
@@ -834,9 +823,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
     float *bias_s = reinterpret_cast<float *>(cnt_s);
     for (int e = tid; e < E; e += CW * 32) bias_s[e] = P.bias ? __ldg(P.bias + e) : 0.0f;
     bar_sync(3, RING_THREADS); // the weight ring is free from here on: the producer may start
-    STAMP(1);
     grid_barrier(P.ctrl, P.sync, (uint32_t)G, tid);
-    STAMP(2);
 
     // ---- phase 0b: selection.  Token i is handled by CTA i: each of the four warps ranks a quarter of
     //      the experts (register-light, rolled loops: this code runs once), warp 0 merges the 4*K
@@ -926,7 +913,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
             if (lane < K) P.w_ws[tok * K + lane] = my_w;
         }
     }
-    STAMP(8);
     grid_barrier(P.ctrl, P.sync, (uint32_t)(2 * G), tid);
     for (int i = tid; i < P.t * K; i += CW * 32) {
         const uint32_t id = __ldcg(P.ids_ws + i);
@@ -1002,10 +988,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
         }
     }
     bar_sync(1, CW * 32);
-    STAMP(9);
     bar_sync(2, DEC_THREADS); // release the producer: the routing tables are complete
 
-    STAMP(3);
     Tables T{ids_s, w_s, off_s, plist_s, act_s, ppre_s, s_n_active, s_routed_passes, shared_passes};
 
     uint32_t n = 0; // ring fill counter, same sequence as the producer's
@@ -1073,10 +1057,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) moe_decode_kernel(const __grid
                 }
             }
         }
-        STAMP(phase == 1 ? 4 : 6);
         if (phase == 2 || !pass_flags) {
             grid_barrier(P.ctrl, P.sync, (uint32_t)((pass_flags ? 3 : phase + 2) * G), tid, 4, EPI_THREADS);
-            STAMP(phase == 1 ? 5 : 7);
         }
     }
 

@@ -1,4 +1,6 @@
 // Whole-block entry points (`MoeBlock::forward`, src/moe.rs:73-78).
+#include <stdlib.h>
+
 #include "fused.cuh"
 
 // decode.cu
@@ -12,6 +14,22 @@ lmoe_status launch_moe_prefill(const lmoe_layer *Ly, const float *x, int64_t t, 
                                float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The one place that decides mat-vec or grouped GEMM for the entries that pick a path themselves.
+// Process-wide and read once, like the reference's `OnceLock` switches (src/ops/mod.rs:24-60).
+extern "C" int64_t lmoe_mm_id_min_seq(void) {
+    static const int64_t v = [] {
+        if (getenv("LAGUNA_NO_MM_ID")) return (int64_t)INT64_MAX; // presence-based: mat-vec everywhere
+        const char *e = getenv("LAGUNA_MM_ID_MIN_SEQ");
+        if (e && *e) {
+            char *end = nullptr;
+            const long long n = strtoll(e, &end, 10);
+            if (end != e && n >= 1) return (int64_t)n;
+        }
+        return (int64_t)LMOE_DECODE_MAX_SEQ + 1;
+    }();
+    return v;
+}
 
 extern "C" size_t lmoe_layer_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens) {
     if (!layer || max_tokens < 0) return 0;
@@ -39,15 +57,35 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
     lmoe_clear_error();
     lmoe_status st = forward_check(layer, x, t, out);
     if (st) return st;
-    if (t > LMOE_DECODE_MAX_SEQ) return lmoe_fail(LMOE_ERR_INVALID, "the decode path takes at most %d tokens, got %lld", LMOE_DECODE_MAX_SEQ, (long long)t);
+    if (t == 0) return LMOE_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    // The kernel's CTAs meet through words owned by the layer: a second call may only start once the
+    // previous one has finished.  Calls on one stream are ordered; a call on another stream is refused
+    // while the previous call's completion event is still pending.
+    std::lock_guard<std::mutex> lock(layer->dec_mutex);
+    if (layer->dec_pending && layer->dec_stream != s) {
+        const cudaError_t q = cudaEventQuery(layer->dec_event);
+        if (q == cudaErrorNotReady)
+            return lmoe_fail(LMOE_ERR_INVALID,
+                             "a decode call on this layer handle is still in flight on another stream; one call at a "
+                             "time per handle (create a second handle over the same stacks for a second stream)");
+        if (q != cudaSuccess) (void)cudaGetLastError(); // e.g. an event recorded inside a capture: not decidable here
+    }
+    // more than 64 tokens: several launches, 64 tokens each, through the same workspace
     const int step = decode_max_tokens();
     for (int64_t t0 = 0; t0 < t; t0 += step) {
         const int n = (int)(t - t0 < step ? t - t0 : step);
         st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
                                ids_out ? ids_out + t0 * layer->top_k : nullptr,
                                weights_out ? weights_out + t0 * layer->top_k : nullptr, workspace, workspace_bytes,
-                               t0 == 0, (cudaStream_t)stream);
+                               t0 == 0, s);
         if (st) return st;
+    }
+    if (cudaEventRecord(layer->dec_event, s) == cudaSuccess) {
+        layer->dec_stream = s;
+        layer->dec_pending = true;
+    } else {
+        (void)cudaGetLastError();
     }
     return LMOE_OK;
 }
@@ -86,8 +124,8 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
     lmoe_status st;
     // the reference switches to its grouped GEMM at 32 tokens (`use_mm`, src/moe.rs:236-240); here the mat-vec
-    // kernel, which streams each distinct expert once per launch, stays ahead up to its limit of 64 tokens
-    if (t > LMOE_DECODE_MAX_SEQ)
+    // kernel, which streams each distinct expert once per launch, stays ahead up to 64 tokens
+    if (t >= lmoe_mm_id_min_seq())
         st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
                                       workspace, kernel_ws, stream);
     else
@@ -138,7 +176,7 @@ extern "C" lmoe_status lmoe_moe_layer_forward(const lmoe_layer *layer, const flo
     float *normed = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + block_ws);
     if ((st = lmoe_rms_norm(ffn_inp, norm_weight, eps, t, layer->hidden, normed, stream))) return st;
     // mat-vec kernel up to 64 tokens, grouped GEMM beyond (measured crossover; the reference's own is 32)
-    if (t > LMOE_DECODE_MAX_SEQ)
+    if (t >= lmoe_mm_id_min_seq())
         st = lmoe_moe_forward_prefill(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);
     else
         st = lmoe_moe_forward_decode(layer, normed, t, out, ids_out, weights_out, workspace, block_ws, stream);

@@ -326,11 +326,6 @@ struct MmSmem {
     }
 };
 
-#ifdef MM_DBG_STAMP
-#define MSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && DT == LMOE_Q4_K && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
-#else
-#define MSTAMP(role, g, i) do { } while (0)
-#endif
 
 // ---- the grouped GEMM kernel -------------------------------------------------------------
 template <int DT>
@@ -424,11 +419,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 const int slot = rg % P.raw_slots;
                 const bool first = DT == LMOE_Q4_K ? (ks & 3) == 0 : ks == 0;
                 const bool last = DT == LMOE_Q4_K ? (ks & 3) == 3 : ks == k_stages - 1;
-                if (tid == 32) MSTAMP(0, g, 0);
                 if (first) ok = mb_wait(&raw_full[slot], (rg / P.raw_slots) & 1, P.flag, 2);
-                if (tid == 32) MSTAMP(0, g, 1);
                 ok = ok && mb_wait(&ab_empty[s], ((g / NS) & 1) ^ 1, P.flag, 3);
-                if (tid == 32) MSTAMP(0, g, 2);
                 uint8_t *ast = a_st + (size_t)s * A_STAGE_BYTES;
                 const uint8_t *rs = raw + (size_t)slot * raw_slot_stride;
                 if (rvalid) {
@@ -441,7 +433,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (tid == 32) MSTAMP(0, g, 3);
                 if (lane == 0) {
                     mb_arrive(&a_full[s]);
                     if (last) mb_arrive(&raw_empty[slot]);
@@ -480,11 +471,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % NS, sb = g % NSB;
-                    MSTAMP(1, g, 0);
                     ok = mb_wait(&a_full[s], (g / NS) & 1, P.flag, 6);
-                    MSTAMP(1, g, 1);
                     ok = ok && mb_wait(&b_full[sb], (g / NSB) & 1, P.flag, 7);
-                    MSTAMP(1, g, 2);
                     tc_fence_after();
                     const uint64_t ad = umma_desc(s32(a_st + (size_t)s * A_STAGE_BYTES));
                     const uint64_t bd = umma_desc(s32(b_st + (size_t)sb * B_STAGE_BYTES));
@@ -493,7 +481,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
                         tc_mma_f16(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     tc_commit(&ab_empty[s]); // frees both stages when these MMAs have read them
                     tc_commit(&b_empty[sb]);
-                    MSTAMP(1, g, 3);
                 }
                 tc_commit(&acc_full[buf]);
             }
@@ -548,11 +535,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
 }
 
 
-#ifdef MM_DBG_STAMP
-#define GSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
-#else
-#define GSTAMP(role, g, i) do { } while (0)
-#endif
 
 // ================= gate + up in one pass, SwiGLU in the epilogue =========================
 // Same tile list as above, but a CTA multiplies one block of routed rows by 128 gate rows AND the
@@ -665,9 +647,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < 4; j++, g++) {
                     const int s = g % GU_NS;
-                    if (tid == 0) GSTAMP(0, g, 0);
                     ok = ok && mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
-                    if (tid == 0) GSTAMP(0, g, 1);
                     uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
                     if (rvalid) {
                         dequant_q4k_regs(hdr, blk[1 + 2 * j], blk[2 + 2 * j], j, ast, r);
@@ -675,11 +655,9 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 #pragma unroll
                         for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
                     }
-                    if (tid == 0) GSTAMP(0, g, 2);
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) mb_arrive(&full[s]);
-                    if (tid == 0) GSTAMP(0, g, 3);
                 }
                 // the column is consumed: hand its slot back to the loader
                 __syncwarp();
@@ -973,11 +951,6 @@ __device__ __forceinline__ void dn_dequant_stage(const DnFields &F, int hn, uint
     }
 }
 
-#ifdef MM_DBG_STAMP_DN
-#define DSTAMP(role, g, i) do { if (blockIdx.x == 0 && (g) < 200 && n_tiles > 1000) reinterpret_cast<long long *>(P.flag + 1024)[((role) * 200 + (g)) * 4 + (i)] = clock64(); } while (0)
-#else
-#define DSTAMP(role, g, i) do { } while (0)
-#endif
 __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_constant__ DnParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1030,14 +1003,12 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             dn_load<0>(R, tw, row_bytes, rows_valid, 0, warp, lane);
             dn_load<1>(R, tw, row_bytes, rows_valid, 0, warp, lane);
             for (int b = 0; b < n_blk; b++) {
-                if (tid == 0) DSTAMP(0, g >> 1, 0);
                 asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the previous column's windows are consumed
                 dn_stage(R, raw, warp, lane);
                 // the next column is requested now (first half) and between the two conversions (second half),
                 // and only touched after this one is converted
                 if (b + 1 < n_blk) dn_load<0>(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
                 asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory");
-                if (tid == 0) DSTAMP(0, g >> 1, 1);
                 // byte offset of this row's block inside its window
                 const int sh = (int)((reinterpret_cast<uintptr_t>(tw) + (size_t)drow * row_bytes + (size_t)b * Q6K_BYTES) & 15u);
 #pragma unroll 1
@@ -1046,11 +1017,9 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                     dn_fields(rowp, sh, n, dlh, F);
                     const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
                     ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3);
-                    if (tid == 0) DSTAMP(0, g >> 1, 2);
                     dn_dequant_stage(F, 0, a_st + (size_t)s0 * GU_A_STAGE, drow, dlh);
                     ok = ok && mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
                     dn_dequant_stage(F, 1, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
-                    if (tid == 0) DSTAMP(0, g >> 1, 3);
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
@@ -1100,11 +1069,8 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % DN_NSA, sb = g % DN_NSB;
-                    DSTAMP(1, g, 0);
                     ok = mb_wait(&a_full[s], (g / DN_NSA) & 1, P.flag, 6);
-                    DSTAMP(1, g, 1);
                     ok = ok && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
-                    DSTAMP(1, g, 2);
                     tc_fence_after();
                     const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
                     const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
@@ -1116,7 +1082,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                     }
                     tc_commit(&a_empty[s]);
                     tc_commit(&b_empty[sb]);
-                    DSTAMP(1, g, 3);
                 }
                 tc_commit(acc_full);
             }
@@ -1141,10 +1106,8 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             }
 #pragma unroll
             for (int c = 0; c < MM_N / 32; c++) scs[c] = (P.row_scale && 32 * c + lane < nv) ? P.row_scale[fids[c]] : 1.0f;
-            if (q == 0 && lane == 0) DSTAMP(2, it, 0);
             ok = mb_wait(acc_full, it & 1, P.flag, 8);
             tc_fence_after();
-            if (q == 0 && lane == 0) DSTAMP(2, it, 1);
             for (int sub = 0; sub < 2; sub++) {
                 const int mrow = m0 + sub * MM_M + m;
                 const bool mvalid = mrow < P.n_out;
@@ -1174,7 +1137,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             }
             tc_fence_before();
             __syncwarp();
-            if (q == 0 && lane == 0) DSTAMP(2, it, 2);
             if (lane == 0) mb_arrive(acc_empty);
         }
     }

@@ -335,6 +335,7 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     float *sh_scale = c.take<float>((size_t)t);
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
 
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s)); // a fresh device flag: the workspace needs no initialisation
     LMOE_CUDA(launch_route_logits(L->router, x, (int)t, (int)H, (int)L->n_expert, logits, s));
     LMOE_CUDA(launch_route_select(logits, L->bias, (int)t, (int)L->n_expert, (int)L->top_k, L->scale, L->norm, ids, w, s));
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
@@ -460,6 +461,7 @@ static lmoe_status experts_rows_run(const lmoe_layer *L, const void *x, int x_f1
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
     LMOE_CUDA(launch_map0(local_ids, (int)rows, 1, (int)L->n_expert, tpe, ids_map, s));
     return ffn_grouped(L->gate, L->up, L->down, x, 1, rows, tpe, ids_map, rows, row_weights, out, ffn_ws, flag, s, nullptr,
                        nullptr, nullptr, x_f16);
@@ -511,6 +513,7 @@ extern "C" lmoe_status lmoe_experts_forward_tokens_f16(const lmoe_layer *L, cons
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
     uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
     int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
     // ids >= n_expert match no expert's list: those slots stay empty
     LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)L->n_expert, tpe, ids_map, s));
     bool sorted = false;
@@ -539,6 +542,7 @@ extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, 
     uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
     uint32_t *list = c.take<uint32_t>((size_t)t + 64);
     uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
     iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, list, reinterpret_cast<int32_t *>(list + 64));
     LMOE_LAUNCH_CHECK("iota_list_kernel");
     return ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, list, reinterpret_cast<int32_t *>(list + 64), t, nullptr,

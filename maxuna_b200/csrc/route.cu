@@ -211,10 +211,11 @@ extern "C" lmoe_status lmoe_route_noalloc(const float *router, const float *bias
     if (t < 0 || n_expert < 1 || n_expert > 512 || top_k < 1 || top_k > 32 || top_k > n_expert)
         return lmoe_fail(LMOE_ERR_INVALID, "route_noalloc: t >= 0, n_expert in [1, 512], top_k in [1, min(32, n_expert)] required");
     if (hidden < 1 || hidden > (1 << 20)) return lmoe_fail(LMOE_ERR_INVALID, "hidden (%lld) out of range", (long long)hidden);
-    if (t * n_expert > LMOE_ROUTE_NOALLOC_MAX_LOGITS)
+    // t is bounded before the product is formed, so the comparison below cannot wrap around
+    if (t > LMOE_ROUTE_NOALLOC_MAX_LOGITS || t * n_expert > LMOE_ROUTE_NOALLOC_MAX_LOGITS)
         return lmoe_fail(LMOE_ERR_INVALID,
                          "route_noalloc: t * n_expert = %lld exceeds the built-in scratch of %d logits; use lmoe_route with a workspace",
-                         (long long)(t * n_expert), LMOE_ROUTE_NOALLOC_MAX_LOGITS);
+                         t > LMOE_ROUTE_NOALLOC_MAX_LOGITS ? (long long)t : (long long)(t * n_expert), LMOE_ROUTE_NOALLOC_MAX_LOGITS);
     if (!router || !x || !ids_out || !weights_out) return lmoe_fail(LMOE_ERR_INVALID, "router/x/ids_out/weights_out is NULL");
     if (hidden % 4 == 0 && (((uintptr_t)router | (uintptr_t)x) & 15u))
         return lmoe_fail(LMOE_ERR_INVALID, "router and x must be 16-byte aligned");

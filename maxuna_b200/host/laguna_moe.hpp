@@ -156,10 +156,11 @@ public:
         return Result::from(lmoe_route(router_, bias_, x_normed, seq, hidden_, n_expert_, top_k_, scale_, norm_ ? 1 : 0, ids,
                                        weights, workspace, workspace_bytes, stream));
     }
-    // `MoeBlock::forward`: the mat-vec path below LMOE_MM_ID_MIN_SEQ tokens, the grouped GEMM from there on.
+    // `MoeBlock::forward`: the mat-vec path below lmoe_mm_id_min_seq() tokens, the grouped GEMM from there on
+    // (the same rule as lmoe_moe_forward_host and lmoe_moe_layer_forward).
     Result forward(const float *x_normed, int64_t seq, float *out, void *workspace, size_t workspace_bytes, void *stream,
                    uint32_t *ids_out = nullptr, float *weights_out = nullptr) const {
-        if (seq >= LMOE_MM_ID_MIN_SEQ)
+        if (seq >= lmoe_mm_id_min_seq())
             return Result::from(lmoe_moe_forward_prefill(h_, x_normed, seq, out, ids_out, weights_out, workspace,
                                                          workspace_bytes, stream));
         return Result::from(lmoe_moe_forward_decode(h_, x_normed, seq, out, ids_out, weights_out, workspace, workspace_bytes,

@@ -37,12 +37,14 @@ class FusedExperts(ExpertFfn):
                                 f"up={up.n_expert}, down={down.n_expert}")
         self.gate, self.up, self.down = gate, up, down
 
-    def forward(self, x, ids, weights):
+    def forward(self, x, ids, weights, use_mm=None):
+        """`use_mm`: None applies the `seq >= mm_id_min_seq()` rule of src/moe.rs:236-240; True / False force
+        the grouped-GEMM or the mat-vec op chain."""
         seq, hidden = x.shape
         top_k = ids.shape[1]
         x = x.to(torch.float32)
         mm_supported = all(ops.supported(s.dtype, top_k) for s in (self.gate, self.up, self.down))
-        use_mm = seq >= ops.mm_id_min_seq() and not ops.no_mm_id() and mm_supported
+        use_mm = (seq >= ops.mm_id_min_seq() if use_mm is None else bool(use_mm)) and mm_supported
         map0 = ops.prepare_map0(self.gate.n_expert, ids) if use_mm else None
 
         def matmul(stack, xin):
@@ -150,11 +152,11 @@ class MoeBlock:
         return ops.route(self.router, self.exp_probs_b, x_normed.to(torch.float32).contiguous(),
                          self.n_expert_used, self.weights_scale, self.weights_norm)
 
-    def forward_unfused(self, x_normed: torch.Tensor) -> torch.Tensor:
+    def forward_unfused(self, x_normed: torch.Tensor, use_mm=None) -> torch.Tensor:
         """The reference's op-by-op sequence, src/moe.rs:73-78."""
         x = x_normed.to(torch.float32).contiguous()
         ids, weights = self.route(x)
-        routed = self.experts.forward(x, ids, weights)
+        routed = self.experts.forward(x, ids, weights, use_mm)
         if self.shared is None:
             return routed
         return routed + self.shared.forward(x)
@@ -166,8 +168,11 @@ class MoeBlock:
             self._ws_tokens = tokens
         return self._ws
 
-    def forward(self, x_normed: torch.Tensor, return_routing: bool = False, out: torch.Tensor = None):
-        """`MoeBlock::forward`, src/moe.rs:73-78, through the fused CUDA entry points."""
+    def forward(self, x_normed: torch.Tensor, return_routing: bool = False, out: torch.Tensor = None,
+                path: str = None):
+        """`MoeBlock::forward`, src/moe.rs:73-78, through the fused CUDA entry points.  `path`: None picks
+        the mat-vec kernel below `ops.mm_id_min_seq()` tokens and the grouped GEMM from there on (the same
+        rule as `lmoe_moe_forward_host` / `lmoe_moe_layer_forward`); "decode" / "prefill" force one."""
         x = x_normed.to(torch.float32).contiguous()
         seq = x.shape[0]
         if x.dim() != 2 or x.shape[1] != self.hidden:
@@ -179,7 +184,9 @@ class MoeBlock:
             ids = torch.empty(seq, self.n_expert_used, dtype=torch.int32, device=x.device)
             w = torch.empty(seq, self.n_expert_used, dtype=torch.float32, device=x.device)
         ws = self.workspace(seq)
-        prefill = seq >= ops.mm_id_min_seq() and not ops.no_mm_id()
+        if path not in (None, "decode", "prefill"):
+            raise LmoeError(-1, f"path must be None, 'decode' or 'prefill', got {path!r}")
+        prefill = path == "prefill" or (path is None and seq >= ops.mm_id_min_seq())
         fn = lib().lmoe_moe_forward_prefill if prefill else lib().lmoe_moe_forward_decode
         check(fn(self._h, x.data_ptr(), seq, out.data_ptr(), None if ids is None else ids.data_ptr(),
                  None if w is None else w.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
@@ -275,7 +282,12 @@ class MoeBlock:
                         self.weights_norm)
 
     def check_device_flag(self):
-        check(lib().lmoe_check_device_flag(self.workspace(1).data_ptr(), stream_ptr()))
+        """Raise if any call on this block recorded a device flag: every workspace the block has used
+        (block, layer, row-level, token-level and shared-expert entries) is inspected."""
+        for name in ("_ws", "_lws", "_rws", "_tws", "_sws", "_ews"):
+            ws = getattr(self, name, None)
+            if ws is not None:
+                check(lib().lmoe_check_device_flag(ws.data_ptr(), stream_ptr()))
 
     # ---- checker support ------------------------------------------------------
     def host_layer(self, orc):

@@ -18,7 +18,6 @@ mismatches raise :class:`LmoeError` before anything is launched.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 
 import torch
@@ -27,18 +26,19 @@ from . import _native
 from ._native import LmoeError, check, lib
 from .gguf import ExpertStack, stream_ptr
 
-MM_ID_MIN_SEQ_DEFAULT = 32  # src/ops/mod.rs:31
+MM_ID_MIN_SEQ_REFERENCE = 32  # src/ops/mod.rs:31: the reference's own crossover, for documentation
 
 
 def mm_id_min_seq() -> int:
-    """`LAGUNA_MM_ID_MIN_SEQ`, src/ops/mod.rs (value-carrying override)."""
-    v = os.environ.get("LAGUNA_MM_ID_MIN_SEQ")
-    return int(v) if v else MM_ID_MIN_SEQ_DEFAULT
+    """Token count from which the grouped GEMM is used (`lmoe_mm_id_min_seq`): 65 on B200 unless
+    `LAGUNA_MM_ID_MIN_SEQ` / `LAGUNA_NO_MM_ID` (src/ops/mod.rs:24-60) say otherwise.  One value for the C
+    entries that pick a path themselves and for the host mirrors, read once per process by the library."""
+    return int(lib().lmoe_mm_id_min_seq())
 
 
 def no_mm_id() -> bool:
     """`LAGUNA_NO_MM_ID`: presence-based, forces the mat-vec path everywhere."""
-    return "LAGUNA_NO_MM_ID" in os.environ
+    return mm_id_min_seq() >= (1 << 62)
 
 
 def _require(cond, msg):

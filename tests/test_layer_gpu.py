@@ -34,7 +34,7 @@ def test_rms_norm_bit_exact(orc, t, hidden):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [1, 3, 17, 40])
+@pytest.mark.parametrize("t", [1, 3, 17, 40, 64, 65, 200])   # 65 and 200 take the grouped-GEMM branch
 def test_layer_forward_matches_oracle(orc, t):
     from maxuna_b200.moe import MoeBlock
 
@@ -48,6 +48,7 @@ def test_layer_forward_matches_oracle(orc, t):
     out, ids, w = blk.layer_forward(torch.from_numpy(ffn_inp).to(dev), torch.from_numpy(g).to(dev), 1e-6,
                                     return_routing=True)
     torch.cuda.synchronize()
+    blk.check_device_flag()
     normed = orc.rms_norm(ffn_inp, g, 1e-6)
     ffn_out, ids_o, w_o = host.forward(normed)
     assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
@@ -68,7 +69,7 @@ def test_layer_forward_argument_errors():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [4, 40])
+@pytest.mark.parametrize("t", [4, 40, 130])
 def test_stack_of_layers_matches_oracle(orc, t):
     """A short residual stack (the shape of BASELINE config 5 at toy size): x <- x + block_l(norm_l(x))."""
     from maxuna_b200.moe import MoeBlock

@@ -84,7 +84,7 @@ def test_mm_errors_not_faults(orc, dev):
 
 def _check_block(orc, blk, host, x, tol):
     xd = torch.from_numpy(x).to(blk.router.device)
-    out, ids, w = blk.forward(xd, return_routing=True)
+    out, ids, w = blk.forward(xd, return_routing=True, path="prefill")
     torch.cuda.synchronize()
     blk.check_device_flag()
     want, ids_o, w_o = host.forward(x)
@@ -106,7 +106,7 @@ def test_prefill_block_tiny(orc, dev):
     # the op-by-op sequence of the reference (mm_id + rescale + combine) agrees too
     x = rng.standard_normal((64, 256)).astype(np.float32)
     want, _, _ = host.forward(x)
-    got = blk.forward_unfused(torch.from_numpy(x).to(dev)).cpu().numpy()
+    got = blk.forward_unfused(torch.from_numpy(x).to(dev), use_mm=True).cpu().numpy()
     assert orc.rel_l2(got, want) < 2e-3
 
 

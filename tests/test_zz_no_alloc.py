@@ -22,7 +22,7 @@ def test_route_noalloc_matches_route_twice():
     n_expert, hidden, top_k = 256, 3072, 10
     router = torch.randn(n_expert, hidden, generator=gen, device=dev) * 0.02
     bias = torch.rand(n_expert, generator=gen, device=dev) * 0.2 - 0.1
-    for call, t in enumerate((16, 5)):  # the second call reuses the array the first one left dirty
+    for call, t in enumerate((16, 5, 100)):  # later calls reuse the array the earlier ones left dirty; 100 tokens take the tiled logits kernel
         x = torch.randn(t, hidden, generator=gen, device=dev)
         ids_a = torch.empty(t, top_k, dtype=torch.int32, device=dev)
         w_a = torch.empty(t, top_k, dtype=torch.float32, device=dev)
@@ -40,5 +40,9 @@ def test_route_noalloc_matches_route_twice():
     t_big = 32768 // n_expert + 1
     rc = lib.lmoe_route_noalloc(router.data_ptr(), bias.data_ptr(), router.data_ptr(), t_big, hidden, n_expert, top_k, 2.5, 1,
                                 ids_a.data_ptr(), w_a.data_ptr(), stream_ptr())
+    assert rc == -1 and b"exceeds the built-in scratch" in lib.lmoe_last_error()
+    # a token count whose product with n_expert wraps around 64 bits is refused as well
+    rc = lib.lmoe_route_noalloc(router.data_ptr(), bias.data_ptr(), router.data_ptr(), (1 << 54) + (1 << 31) - 1, hidden, 512, top_k,
+                                2.5, 1, ids_a.data_ptr(), w_a.data_ptr(), stream_ptr())
     assert rc == -1 and b"exceeds the built-in scratch" in lib.lmoe_last_error()
     torch.cuda.synchronize()
