@@ -25,6 +25,7 @@ at batch <= 16 does not shard; weak scaling).
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -46,8 +47,12 @@ H, F, E, K = 3072, 1024, 256, 10
 SWEEP = (1, 2, 4, 8, 16)
 EXPERT_BYTES = 2 * F * (H // 256) * 144 + H * (F // 256) * 210  # 6 119 424
 ROUTER_BYTES = E * H * 4
-# DRAM traffic of one decode sweep (B = 1, 2, 4, 8, 16) measured once under ncu: 72.1 + 135.8 + 224.3 + 415.1 + 737.2 MB
-NCU_TRAFFIC_PER_SWEEP = 1.5845e9
+WORKLOAD = "config2: single MoE layer decode sweep B=1/2/4/8/16 (31 tokens per step)"
+# DRAM traffic of one decode sweep (B = 1, 2, 4, 8, 16) from an ncu capture of the five launches
+# (dram__bytes_read.sum + dram__bytes_write.sum: 72.1 + 135.8 + 224.3 + 415.1 + 737.2 MB).  The figure belongs to
+# the kernel source it was captured on: when csrc/decode.cu has changed since, the line reports null.
+NCU_TRAFFIC = {"bytes_per_sweep": 1.5845e9, "algorithmic_bytes_of_that_sweep": 1.457e9,
+               "decode_cu_sha256_16": "0000000000000000"}
 NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
            "clocks_event_reasons.sw_power_cap")
@@ -60,7 +65,9 @@ def algorithmic_bytes(n_distinct: int, batch: int) -> int:
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 10 ms; every row carries the host time at which it
+    was read, so the rows that fall inside the timed region can be told from those of the loaded windows
+    around it (warm-up before, per-batch timing loops after)."""
 
     def __init__(self, gpu_index: int):
         self.rows = []
@@ -70,30 +77,36 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={NVSMI_Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "10", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary over the rows read in [t0, t1] (the timed region); when the region was too short to
+        hold a sample, over every row read while the GPU was under load, and `window` says so."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.06)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.03)
         self.proc.terminate()
-        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        rows = [r for r in self.rows if len(r[1]) >= 9 and r[1][1].replace(".", "").isdigit()]
+        inside = [r for r in rows if t0 is not None and t0 <= r[0] <= t1 + 0.02]
+        window = "timed region"
+        if not inside:
+            inside, window = rows, "warm-up, timed region and per-batch loops (the timed region is shorter than one sample period)"
+        sm = [float(r[1][1]) for r in inside]
+        mx = [float(r[1][2]) for r in inside if r[1][2].replace(".", "").isdigit()]
         reasons = set()
-        for r in self.rows:
-            if len(r) >= 9:
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
+        for _, r in inside:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window, "period_ms": 10}
 
 
 def build_host_layer(orc, seed=0):
@@ -163,9 +176,10 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "moe_layer_decode_tok_per_s", "value": val, "unit": "tok/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8xq4/q6 -> f32", "data": "synthetic",
-        "config": {"workload": "config2: single MoE layer decode sweep B=1/2/4/8/16", "hidden": H, "expert_ff": F,
-                   "n_expert": E, "top_k": K, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD, "hidden": H, "expert_ff": F,
+                   "n_expert": E, "top_k": K, "shared_expert": True, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample,
+                         "build": "int8-activation k-quant dots, -O3 -march=native, 256-bit integer SIMD where the host has it, OpenMP"},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference's CPU k-quant path (the reference itself is Rust + Metal: not buildable here)",
     }))
@@ -183,49 +197,156 @@ def zipf_bias(n_expert, seed, device):
     return b.to(device)
 
 
-def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None):
-    """Prefill of one MoE layer: N=1 -> config 3 (4096 tokens, Zipf-skewed routing, one GPU);
-    N>1 -> config 4 (16384 tokens split over the ranks, experts sharded 256/N per GPU,
-    NCCL all-to-all dispatch / combine), uniform and Zipf.  Returns TFLOP/s figures."""
+def _time_gpu(run, steps, warmup, world, dev):
+    """Mean milliseconds of `run()` over `steps` calls after `warmup`: CUDA events on the current stream,
+    barrier + synchronize on both sides, max over ranks."""
     import torch
     import torch.distributed as dist
 
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt[0])
+    return ms
+
+
+def prefill_parity(blk, x, out, ids, n_sample, seed):
+    """Outside every timed region: a token sample of a prefill result against the CPU oracle (routing
+    decision bit for bit, block output in relative L2), plus the count of tokens whose 10th and 11th
+    selection scores lie within 1e-6 of each other in float64 (the ones f32 noise could re-rank)."""
+    import torch
+
+    from oracle import oracle as orc
+
+    orc.build()
+    host = blk.host_layer(orc)
+    t = x.shape[0]
+    rng = np.random.default_rng(seed)
+    sample = np.sort(rng.choice(t, min(n_sample, t), replace=False))
+    xs = x[torch.from_numpy(sample).to(x.device)].cpu().numpy()
+    want, ids_o, _ = host.forward(xs)
+    got = out[torch.from_numpy(sample).to(out.device)].cpu().numpy()
+    ids_g = ids[torch.from_numpy(sample).to(ids.device)].cpu().numpy().astype(np.uint32)
+    logits = orc.route_logits(host.router, x.cpu().numpy()).astype(np.float64)
+    sel = 1.0 / (1.0 + np.exp(-logits)) + (0.0 if host.bias is None else host.bias.astype(np.float64))
+    part = -np.sort(-sel, axis=1)
+    return {"tokens": int(len(sample)), "ids_exact": bool(np.array_equal(ids_g, ids_o)),
+            "rel_l2": orc.rel_l2(got, want), "against": "CPU oracle (dequantize -> f32 dot)",
+            "near_ties_lt_1e-6": int(np.count_nonzero(part[:, K - 1] - part[:, K] < 1e-6)), "of_tokens": int(t)}
+
+
+def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=True):
+    """Prefill of one MoE layer: N=1 -> config 3 (4096 tokens, Zipf-skewed routing, one GPU), plus the
+    16384-token single-GPU run that anchors the expert-parallel scaling curve; N>1 -> config 4 (16384 tokens
+    split over the ranks, experts sharded 256/N per GPU, all-to-all dispatch / combine), uniform and Zipf.
+    Each result carries a parity check of a token sample made outside the timed region."""
+    import torch
+    import torch.distributed as dist
+
+    from maxuna_b200 import _native
     from maxuna_b200.ep import make_gpu_ep_block
     from maxuna_b200.moe import MoeBlock
 
+    lib = _native.lib()
     res = {}
     t_total = tokens if tokens else (4096 if world == 1 else 16384)
-    for name in (("zipf",) if world == 1 else ("uniform", "zipf")):
-        bias = zipf_bias(E, 3, dev) if name == "zipf" else None
+    cases = [("zipf", t_total)] if world == 1 else [("uniform", t_total), ("zipf", t_total)]
+    if world == 1 and not tokens:
+        cases.append(("zipf_t16384", 16384))
+    for name, t_case in cases:
+        zipf = name.startswith("zipf")
+        bias = zipf_bias(E, 3, dev) if zipf else None
         blk = MoeBlock.random(H, F, E, K, seed=4242, device=dev, bias=bias)
         gen = torch.Generator(device=dev)
         gen.manual_seed(99 + rank)
-        t_loc = t_total // world
+        t_loc = t_case // world
         x = torch.randn(t_loc, H, generator=gen, device=dev)
+        out = torch.empty(t_loc, H, device=dev)
+        entry = {"tokens": t_case, "seed_layer": 4242, "seed_tokens": 99, "bias": "zipf(1.1), seed 3" if zipf else "U(-0.1, 0.1)"}
         if world == 1:
-            run = lambda: blk.forward(x)
+            ids = torch.empty(t_loc, K, dtype=torch.int32, device=dev)
+            ws = blk.workspace(t_loc)
+            stream = torch.cuda.current_stream().cuda_stream
+
+            def run():
+                _native.check(lib.lmoe_moe_forward_prefill(blk.handle, x.data_ptr(), t_loc, out.data_ptr(), ids.data_ptr(), None,
+                                                           ws.data_ptr(), ws.numel(), stream))
+            ep = None
+            entry["path"] = "lmoe_moe_forward_prefill: router, expert-sorted gather, tcgen05 grouped GEMMs, slot-order sum"
         else:
             ep = make_gpu_ep_block(blk.router, blk.exp_probs_b, blk.shard(rank, world), E, K)
-            run = lambda: ep.forward(x)
-        for _ in range(warmup):
-            run()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            run()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        if world > 1:
-            tt = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms = float(tt[0])
-        flops = t_total * (K + 1) * 18874368
-        res[name] = {"tokens": t_total, "ms": ms, "tflops": flops / ms / 1e9, "tok_per_s": t_total / ms * 1e3}
-        del blk
+
+            def run():
+                out.copy_(ep.forward(x))
+            entry["path"] = "expert parallel, token-level exchange (maxuna_b200/ep.py)"
+        ms = _time_gpu(run, steps, warmup, world, dev)
+        flops = t_case * (K + 1) * 18874368
+        entry.update({"ms": ms, "tflops": flops / ms / 1e9, "tok_per_s": t_case / ms * 1e3})
+        if checks:
+            if world == 1:
+                if rank == 0:
+                    entry["parity"] = prefill_parity(blk, x, out, ids, 32, 7)
+            else:
+                # the same tokens through the single-GPU block on this rank (it holds the full layer): a sample
+                # of the expert-parallel result must agree to f32 rounding (the sums are grouped by rank)
+                n_s = min(256, t_loc)
+                ref, ids_ref, _ = blk.forward(x[:n_s], return_routing=True, path="prefill")
+                got = ep.forward(x)[:n_s]
+                torch.cuda.synchronize()
+                d = (got.double() - ref.double()).pow(2).sum().sqrt() / ref.double().pow(2).sum().sqrt()
+                tt = torch.tensor([float(d)], device=dev, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                entry["parity"] = {"tokens": n_s * world, "rel_l2": float(tt[0]),
+                                   "against": "the single-GPU grouped-GEMM block on the same tokens, max over ranks",
+                                   "ids_exact": True, "ids_note": "every rank routes its own tokens with the replicated router"}
+                if getattr(ep, "last_phases", None):
+                    entry["phases_ms"] = ep.last_phases
+                entry["rows"] = dict(ep.last_stats)
+        if checks and world == 1 and rank == 0 and t_case == t_total:
+            # end to end through the host-buffer entry (pinned x in, result out, copies inside the timed region)
+            xh = x.cpu().pin_memory()
+            oh = torch.empty(t_loc, H).pin_memory()
+            n_ws = lib.lmoe_layer_workspace_bytes(blk.handle, t_loc)
+            wsh = torch.empty(n_ws, dtype=torch.uint8, device=dev)
+            stream = torch.cuda.current_stream().cuda_stream
+
+            def host_call():
+                _native.check(lib.lmoe_moe_forward_host(blk.handle, xh.data_ptr(), t_loc, oh.data_ptr(), None, None, wsh.data_ptr(),
+                                                        n_ws, stream))
+            for _ in range(2):
+                host_call()
+            t0 = time.perf_counter()
+            for _ in range(4):
+                host_call()
+            e2e_ms = (time.perf_counter() - t0) / 4 * 1e3
+            entry["e2e"] = {"ms": e2e_ms, "tflops": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": t_loc * H * 4,
+                            "d2h_bytes_per_step": t_loc * H * 4}
+            # bounded CPU leg: the int8-activation port on 16 of these tokens
+            from oracle import oracle as orc
+
+            host = blk.host_layer(orc)
+            xs_cpu = x[:16].cpu().numpy()
+            host.forward_q8(xs_cpu[:1])
+            t0 = time.perf_counter()
+            host.forward_q8(xs_cpu)
+            sec = time.perf_counter() - t0
+            entry["cpu_baseline"] = {"value": 16 * (K + 1) * 18874368 / sec / 1e12, "unit": "TFLOP/s", "cores": orc.num_threads(),
+                                     "kind": "port", "sample": "16 tokens of this prefill through the int8-activation CPU path"}
+        res[name] = entry
+        del blk, ep
         torch.cuda.empty_cache()
     return res
 
@@ -365,7 +486,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up ----
+    # ---- warm-up (the clock sampler starts first: nvidia-smi needs a moment before its first row) ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     i = 0
     for _ in range(args.warmup):
         for b in SWEEP:
@@ -374,10 +497,9 @@ def main():
     barrier()
 
     # ---- timed region: K sweeps, device-resident inputs ----
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_region0 = time.perf_counter()
     e0.record()
     row = 0
     for _ in range(args.steps):
@@ -387,13 +509,13 @@ def main():
             row += 1
     e1.record()
     barrier()
+    t_region1 = time.perf_counter()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
 
-    # ---- per-batch timing (same rotation), for the sweep table and the roofline ----
+    # ---- per-batch timing (same rotation), for the sweep table and the roofline: at least 0.2 s per size ----
     per_b = {}
     for b in SWEEP:
-        n = max(50, args.steps // 2)
+        n = max(50, args.steps // 2, int(0.2 / (ms * 1e-3 / args.steps / len(SWEEP))))
         barrier()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a0.record()
@@ -403,6 +525,7 @@ def main():
         a1.record()
         torch.cuda.synchronize()
         per_b[b] = a0.elapsed_time(a1) / n * 1e-3  # seconds per launch
+    clocks = sampler.stop(t_region0, t_region1)
 
     # distinct experts per launch from the logged routing decisions
     ids_host = ids_log.cpu().numpy()
@@ -419,6 +542,15 @@ def main():
     else:
         peak_gbs, peak_src = 6650.0, "fallback"
     achieved = bytes_sweep / launch_s / 1e9
+    decode_hash = hashlib.sha256(open(os.path.join(ROOT, "maxuna_b200", "csrc", "decode.cu"), "rb").read()).hexdigest()[:16]
+    if decode_hash == NCU_TRAFFIC["decode_cu_sha256_16"]:
+        traffic = NCU_TRAFFIC["bytes_per_sweep"]
+        traffic_src = ("constant: dram__bytes_read.sum + dram__bytes_write.sum of the five launches of one sweep in an ncu "
+                       f"capture of this kernel source (decode.cu sha256 {decode_hash}); algorithmic bytes of that sweep: "
+                       f"{NCU_TRAFFIC['algorithmic_bytes_of_that_sweep']:.4g}")
+    else:
+        traffic = None
+        traffic_src = "no ncu capture of this kernel source yet (decode.cu changed since the last one)"
     sweep_tab = []
     for b in SWEEP:
         by = algorithmic_bytes(1, b) - EXPERT_BYTES + mean_u[b] * EXPERT_BYTES
@@ -469,7 +601,8 @@ def main():
         cpu_time_sweep(host, xs_cpu, (1,), 1e9)
         tok, sec = cpu_time_sweep(host, xs_cpu, SWEEP + SWEEP + SWEEP, 20.0)
         cpu = {"value": tok / sec, "unit": "tok/s", "cores": orc.num_threads(), "kind": "port",
-               "sample": f"{tok} tokens of the decode sweep on layer 0 (int8-activation k-quant dots, OpenMP)"}
+               "sample": f"{tok} tokens of the decode sweep on layer 0 (int8-activation k-quant dots, OpenMP)",
+               "build": "-O3 -march=native, 256-bit integer SIMD where the host has it"}
 
     prefill = None
     if not args.no_prefill:
@@ -483,7 +616,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K x s8 digits (3 per activation, 21 bits) -> s32 -> f32",
             "data": "synthetic",
-            "config": {"workload": "config2: single MoE layer decode sweep B=1/2/4/8/16 (31 tokens per step)",
+            "config": {"workload": WORKLOAD,
                        "hidden": H, "expert_ff": F, "n_expert": E, "top_k": K, "shared_expert": True,
                        "layers_rotated": args.layers,
                        "l2": f"inputs larger than L2: {args.layers} layer copies ({args.layers * 1.573:.1f} GB), "
@@ -494,11 +627,14 @@ def main():
                     "h2d_bytes_per_step": tokens_per_step * H * 4, "d2h_bytes_per_step": tokens_per_step * H * 4,
                     "steps": e2e_steps},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                         "frac": achieved / peak_gbs, "traffic": NCU_TRAFFIC_PER_SWEEP, "peak_source": peak_src,
-                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the five launches of one "
-                                           "sweep in an ncu --set full capture (summary kept with the committed profiles; "
-                                           "algorithmic bytes of that sweep: 1.457e9)",
+                         "frac": achieved / peak_gbs, "traffic": traffic, "peak_source": peak_src,
+                         "traffic_source": traffic_src,
                          "kernel": "moe_decode_kernel", "algorithmic_bytes_per_sweep": bytes_sweep},
+            "provenance": {"library": lib.lmoe_version().decode(), "decode_path": "moe_decode_kernel: fused routing + indexed "
+                           "mat-vecs + SwiGLU + combine + shared expert, one cooperative launch per batch",
+                           "mm_id_min_seq": int(lib.lmoe_mm_id_min_seq()),
+                           "seeds": {"layers": [100 * rank + i for i in range(args.layers)], "hidden_states": 1234 + rank},
+                           "decode_cu_sha256_16": decode_hash},
             "sweep": sweep_tab,
             "clocks": clocks,
         }
@@ -507,9 +643,10 @@ def main():
         if prefill is not None:
             peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"bf16_tflops": 1590.0}
             line["prefill"] = {
-                "workload": ("config3: 4096-token prefill of one layer, Zipf-skewed routing, 1 GPU" if world == 1 else
+                "workload": ("config3: 4096-token prefill of one layer, Zipf-skewed routing, 1 GPU (zipf_t16384: the "
+                             "16384 tokens of config4 on one GPU, the anchor of the expert-parallel curve)" if world == 1 else
                              f"config4: 16384-token expert-parallel prefill over {world} GPUs (256/{world} experts per GPU, "
-                             "NCCL all-to-all dispatch and combine)"),
+                             "all-to-all dispatch and combine)"),
                 "unit": "TFLOP/s", "flops_per_token": (K + 1) * 18874368,
                 "peak_tflops": peaks.get("bf16_tflops"), "results": prefill,
                 "frac_of_peak": {k: v["tflops"] / (peaks.get("bf16_tflops") * world) for k, v in prefill.items()},

@@ -26,7 +26,8 @@
  * encoder that emits valid super-blocks; parity is defined on identical bytes
  * fed to both sides, so byte-identity with a candle run is "parity unpinned".
  *
- * Build:  make -C oracle      (gcc -O2 -ffp-contract=off -fopenmp -shared)
+ * Build:  make -C oracle      (gcc -O2 -ffp-contract=off -fopenmp -shared; the timed CPU
+ *         baseline is a separate unit, lmoe_cpu_baseline.c, with its own flags)
  * -ffp-contract=off matters: the router reduction below is specified to the
  * bit and must not be re-associated or fused by the compiler.
  */
@@ -38,11 +39,7 @@
 #include <omp.h>
 #endif
 
-#define QK_K 256
-#define Q4K_BYTES 144
-#define Q6K_BYTES 210
-
-enum { LMO_Q4_K = 12, LMO_Q6_K = 14 }; /* ggml type ids */
+#include "lmoe_oracle.h"
 
 /* ---------------------------------------------------------------- f16 ---- */
 
@@ -99,18 +96,6 @@ uint16_t lmo_f2h(float f) { return f2h(f); }
 
 int lmo_type_size(int dtype) {
     return dtype == LMO_Q4_K ? Q4K_BYTES : dtype == LMO_Q6_K ? Q6K_BYTES : 0;
-}
-
-/* 6-bit (scale, min) pair j of a Q4_K super-block; src/ops/mm_id.metal:89-92
- * decodes the same packing two at a time. */
-static void q4k_scale_min(const uint8_t *s, int j, int *sc, int *mn) {
-    if (j < 4) {
-        *sc = s[j] & 63;
-        *mn = s[j + 4] & 63;
-    } else {
-        *sc = (s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4);
-        *mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
-    }
 }
 
 /* One Q4_K super-block -> 256 floats: w = (d*sc_j)*q - (dmin*m_j). */
@@ -542,20 +527,6 @@ int lmo_map0(const uint32_t *ids, int t, int top_k, int n_expert, uint32_t *tpe,
 
 /* --------------------------------------------------------- whole block ---- */
 
-typedef struct {
-    int hidden, expert_ff, n_expert, top_k;
-    float scale;
-    int norm;
-    const float *router;   /* [n_expert, hidden] */
-    const float *bias;     /* [n_expert] */
-    const uint8_t *gate;   /* Q4_K [n_expert, expert_ff, hidden] */
-    const uint8_t *up;     /* Q4_K [n_expert, expert_ff, hidden] */
-    const uint8_t *down;   /* Q6_K [n_expert, hidden, expert_ff] */
-    const uint8_t *sh_gate; /* Q4_K [expert_ff, hidden] or NULL */
-    const uint8_t *sh_up;
-    const uint8_t *sh_down; /* Q6_K [hidden, expert_ff] */
-    int gate_dtype, down_dtype;
-} lmo_layer;
 
 /* One SwiGLU expert on one token: out += wgt * down(silu(gate x) * up x).
  * f32 dequantize-then-dot, src/moe.rs:173-183; `accum64` as above. */
@@ -620,145 +591,34 @@ int lmo_moe_forward(const lmo_layer *L, const float *x, int t, float *out, uint3
     return 0;
 }
 
-/* ------------------------------------------------ timed CPU baseline ----- */
-/* A restatement of the ggml/candle CPU convention for k-quant matmuls:
- * activations are quantized to 8-bit blocks of 256 (one f32 scale per block,
- * plus per-16 sums), and every super-block contributes an integer dot product.
- * candle's source is not available here, so this is "restated, unverified
- * against candle"; it is the TIMED baseline only, never the parity oracle
- * (int8 activations alone move a product by ~7e-3 relative L2). */
-
-typedef struct {
-    float d;
-    int8_t qs[QK_K];
-    int16_t bsums[16];
-} q8k_block;
-
-static void quantize_q8k(const float *x, int k, q8k_block *y) {
-    for (int b = 0; b < k / QK_K; b++) {
-        float amax = 0.f, vmax = 0.f;
-        for (int i = 0; i < QK_K; i++) {
-            const float a = fabsf(x[b * QK_K + i]);
-            if (a > amax) { amax = a; vmax = x[b * QK_K + i]; }
-        }
-        if (amax == 0.f) { memset(&y[b], 0, sizeof y[b]); continue; }
-        const float iscale = -127.f / vmax;
-        for (int i = 0; i < QK_K; i++) {
-            int v = nearest_int(iscale * x[b * QK_K + i]);
-            y[b].qs[i] = (int8_t)(v > 127 ? 127 : v < -128 ? -128 : v);
-        }
-        for (int j = 0; j < 16; j++) {
-            int s = 0;
-            for (int i = 0; i < 16; i++) s += y[b].qs[16 * j + i];
-            y[b].bsums[j] = (int16_t)s;
-        }
-        y[b].d = 1.f / iscale;
-    }
-}
-
-static float dot_q4k_q8k(const uint8_t *row, const q8k_block *y, int nb) {
-    float sum = 0.f;
-    for (int b = 0; b < nb; b++) {
-        const uint8_t *blk = row + b * Q4K_BYTES;
-        uint16_t dh, mh;
-        memcpy(&dh, blk, 2);
-        memcpy(&mh, blk + 2, 2);
-        const float d = h2f(dh) * y[b].d, dmin = h2f(mh) * y[b].d;
-        const uint8_t *qs = blk + 16;
-        int32_t isum = 0, msum = 0;
-        for (int j = 0; j < 4; j++) {
-            int s1, m1, s2, m2;
-            q4k_scale_min(blk + 4, 2 * j, &s1, &m1);
-            q4k_scale_min(blk + 4, 2 * j + 1, &s2, &m2);
-            int32_t a = 0, c = 0;
-            for (int l = 0; l < 32; l++) {
-                a += (qs[32 * j + l] & 0x0f) * y[b].qs[64 * j + l];
-                c += (qs[32 * j + l] >> 4) * y[b].qs[64 * j + 32 + l];
-            }
-            isum += a * s1 + c * s2;
-            msum += m1 * (y[b].bsums[4 * j] + y[b].bsums[4 * j + 1]) +
-                    m2 * (y[b].bsums[4 * j + 2] + y[b].bsums[4 * j + 3]);
-        }
-        sum += d * (float)isum - dmin * (float)msum;
-    }
-    return sum;
-}
-
-static float dot_q6k_q8k(const uint8_t *row, const q8k_block *y, int nb) {
-    float sum = 0.f;
-    for (int b = 0; b < nb; b++) {
-        const uint8_t *blk = row + b * Q6K_BYTES;
-        const uint8_t *ql = blk, *qh = blk + 128;
-        const int8_t *sc = (const int8_t *)(blk + 192);
-        uint16_t dh;
-        memcpy(&dh, blk + 208, 2);
-        const float d = h2f(dh) * y[b].d;
-        int32_t isum = 0;
-        for (int n = 0; n < 2; n++) {
-            int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int l = 0; l < 32; l++) {
-                const int is = l / 16;
-                const int q1 = (int)((ql[64 * n + l] & 0x0f) | (((qh[32 * n + l] >> 0) & 3) << 4)) - 32;
-                const int q2 = (int)((ql[64 * n + 32 + l] & 0x0f) | (((qh[32 * n + l] >> 2) & 3) << 4)) - 32;
-                const int q3 = (int)((ql[64 * n + l] >> 4) | (((qh[32 * n + l] >> 4) & 3) << 4)) - 32;
-                const int q4 = (int)((ql[64 * n + 32 + l] >> 4) | (((qh[32 * n + l] >> 6) & 3) << 4)) - 32;
-                acc[is] += q1 * y[b].qs[128 * n + l];
-                acc[is + 2] += q2 * y[b].qs[128 * n + 32 + l];
-                acc[is + 4] += q3 * y[b].qs[128 * n + 64 + l];
-                acc[is + 6] += q4 * y[b].qs[128 * n + 96 + l];
-            }
-            for (int j = 0; j < 8; j++) isum += acc[j] * sc[8 * n + j];
-        }
-        sum += d * (float)isum;
-    }
-    return sum;
-}
-
-static float dot_q8k(int dtype, const uint8_t *row, const q8k_block *y, int nb) {
-    return dtype == LMO_Q4_K ? dot_q4k_q8k(row, y, nb) : dot_q6k_q8k(row, y, nb);
-}
-
-/* One SwiGLU expert for one token, rows spread over the OpenMP team. */
-static void expert_ffn_q8(const lmo_layer *L, const uint8_t *g, const uint8_t *u, const uint8_t *d,
-                          const q8k_block *xq, float wgt, float *out, float *act, q8k_block *aq) {
+/* `ExpertFfn::forward`, src/moe.rs:19-21, as `ReferenceExperts` implements it (src/moe.rs:142-187):
+ * the routing decision comes from the caller.  out[t] = sum over slots, in slot order, of
+ * weights[t,k] * FFN_{ids[t,k]}(x[t]); an id >= n_expert is an empty slot; the same expert may
+ * appear more than once in a row (each slot is evaluated on its own).  No shared expert. */
+int lmo_experts_forward(const lmo_layer *L, const float *x, const uint32_t *ids, const float *w, int t, int top_k,
+                        float *out, int accum64) {
     const int H = L->hidden, F = L->expert_ff;
-    const int64_t grow = (int64_t)(H / QK_K) * lmo_type_size(L->gate_dtype);
-    const int64_t drow = (int64_t)(F / QK_K) * lmo_type_size(L->down_dtype);
-#pragma omp parallel for schedule(static)
-    for (int f = 0; f < F; f++) {
-        const float gv = dot_q8k(L->gate_dtype, g + f * grow, xq, H / QK_K);
-        const float uv = dot_q8k(L->gate_dtype, u + f * grow, xq, H / QK_K);
-        act[f] = (gv / (1.0f + expf(-gv))) * uv;
-    }
-    quantize_q8k(act, F, aq);
-#pragma omp parallel for schedule(static)
-    for (int h = 0; h < H; h++) out[h] += wgt * dot_q8k(L->down_dtype, d + h * drow, aq, F / QK_K);
-}
-
-/* Whole block through the int8-activation convention (timed baseline). */
-int lmo_moe_forward_q8(const lmo_layer *L, const float *x, int t, float *out) {
-    const int H = L->hidden, F = L->expert_ff, K = L->top_k;
     if (H % QK_K || F % QK_K) return -1;
-    uint32_t *ids = (uint32_t *)malloc(sizeof(uint32_t) * (size_t)t * K);
-    float *w = (float *)malloc(sizeof(float) * (size_t)t * K);
-    lmo_route(L->router, L->bias, x, t, H, L->n_expert, K, L->scale, L->norm, ids, w);
     const int64_t gexp = (int64_t)F * (H / QK_K) * lmo_type_size(L->gate_dtype);
     const int64_t dexp = (int64_t)H * (F / QK_K) * lmo_type_size(L->down_dtype);
-    q8k_block *xq = (q8k_block *)malloc(sizeof(q8k_block) * (size_t)(H / QK_K));
-    q8k_block *aq = (q8k_block *)malloc(sizeof(q8k_block) * (size_t)(F / QK_K));
-    float *act = (float *)malloc(sizeof(float) * (size_t)F);
-    for (int i = 0; i < t; i++) {
-        float *o = out + (int64_t)i * H;
-        for (int h = 0; h < H; h++) o[h] = 0.0f;
-        quantize_q8k(x + (int64_t)i * H, H, xq);
-        for (int k = 0; k < K; k++) {
-            const uint32_t e = ids[(int64_t)i * K + k];
-            expert_ffn_q8(L, L->gate + e * gexp, L->up + e * gexp, L->down + e * dexp, xq,
-                          w[(int64_t)i * K + k], o, act, aq);
+#pragma omp parallel
+    {
+        float *act = (float *)malloc(sizeof(float) * (size_t)F);
+        float *wrow = (float *)malloc(sizeof(float) * (size_t)(H > F ? H : F));
+#pragma omp for schedule(dynamic, 1)
+        for (int i = 0; i < t; i++) {
+            float *o = out + (int64_t)i * H;
+            for (int h = 0; h < H; h++) o[h] = 0.0f;
+            for (int k = 0; k < top_k; k++) {
+                const uint32_t e = ids[(int64_t)i * top_k + k];
+                if (e >= (uint32_t)L->n_expert) continue;
+                expert_ffn(L, L->gate + e * gexp, L->up + e * gexp, L->down + e * dexp, x + (int64_t)i * H,
+                           w[(int64_t)i * top_k + k], o, act, wrow, accum64);
+            }
         }
-        if (L->sh_gate) expert_ffn_q8(L, L->sh_gate, L->sh_up, L->sh_down, xq, 1.0f, o, act, aq);
+        free(act);
+        free(wrow);
     }
-    free(ids); free(w); free(xq); free(aq); free(act);
     return 0;
 }
 

@@ -8,6 +8,7 @@ file:line it restates.
 from __future__ import annotations
 
 import ctypes as C
+import hashlib
 import os
 import subprocess
 
@@ -23,11 +24,31 @@ _SO = os.path.join(_HERE, "_build", "liblmoe_oracle.so")
 _lib = None
 
 
+def _cpu_tag() -> str:
+    """Identifies the host CPU's instruction set: the baseline unit is compiled with -march=native, so a
+    library built on another machine must not be loaded here."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return hashlib.sha256(line.encode()).hexdigest()[:16]
+    except OSError:
+        pass
+    return "unknown"
+
+
 def build(force: bool = False) -> str:
-    """Compile the oracle with gcc (``make -C oracle``)."""
-    src = os.path.join(_HERE, "lmoe_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
-        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    """Compile the oracle with gcc (``make -C oracle``); rebuilt when a source is newer or when the
+    existing library was built for a different CPU."""
+    srcs = [os.path.join(_HERE, n) for n in ("lmoe_oracle.c", "lmoe_cpu_baseline.c", "lmoe_oracle.h", "Makefile")]
+    tag_file = os.path.join(_HERE, "_build", "cpu_tag.txt")
+    tag = _cpu_tag()
+    stale = (not os.path.exists(_SO) or any(os.path.getmtime(_SO) < os.path.getmtime(p) for p in srcs)
+             or not os.path.exists(tag_file) or open(tag_file).read().strip() != tag)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+        with open(tag_file, "w") as f:
+            f.write(tag)
     return _SO
 
 
@@ -217,6 +238,18 @@ class HostLayer:
         rc = lib().lmo_moe_forward(C.byref(s), _p(x), C.c_int(t), _p(out), _p(ids), _p(w), C.c_int(int(accum64)))
         assert rc == 0
         return out, ids, w
+
+    def experts_forward(self, x, ids, weights, accum64=False):
+        """``lmo_experts_forward``: the `ExpertFfn` seam (src/moe.rs:19-21) -- caller-supplied routing,
+        routed experts only; ids >= n_expert are empty slots."""
+        x, ids, weights = _f32(x), _u32(ids), _f32(weights)
+        t, k = ids.shape
+        out = np.empty((t, self.hidden), np.float32)
+        s = self._struct()
+        rc = lib().lmo_experts_forward(C.byref(s), _p(x), _p(ids), _p(weights), C.c_int(t), C.c_int(k), _p(out),
+                                       C.c_int(int(accum64)))
+        assert rc == 0
+        return out
 
     def forward_q8(self, x):
         """``lmo_moe_forward_q8``: the int8-activation CPU convention (timed baseline)."""
