@@ -240,6 +240,23 @@ lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int
                                     uint32_t *ids_out, float *weights_out, void *workspace,
                                     size_t workspace_bytes, void *stream);
 
+/* `ExpertFfn::forward`, src/moe.rs:19-21 (the seam `FusedExperts`, src/moe.rs:194-324, implements and
+ * `MoeBlock::forward` calls after routing, src/moe.rs:73-78): the routed experts on a routing decision the
+ * CALLER made.
+ *   x [t, hidden] f32, ids [t, top_k] u32, weights [t, top_k] f32 (top_k = the layer's), all on the device
+ *   -> out [t, hidden] f32 = sum over slots, in slot order, of weights[t,k] * FFN_{ids[t,k]}(x[t]);
+ *   add_shared != 0 adds the layer's shared expert (src/moe.rs:76-77), 0 is the bare trait.
+ * An id >= the layer's expert count is an empty slot (contributes nothing).  Below lmoe_mm_id_min_seq()
+ * tokens the fused mat-vec kernel runs with its routing phase skipped and accepts the same expert more
+ * than once in a row (src/ops/mv_id.rs:100-203); from there on the grouped GEMM runs, which, like the
+ * reference's (src/ops/dispatch.rs:2341-2346), needs the experts of a token to be distinct.
+ * The one-call-in-flight rule of lmoe_moe_forward_decode applies on the mat-vec path.
+ * Workspace: lmoe_experts_workspace_bytes(layer, t); needs no initialisation. */
+size_t lmoe_experts_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens);
+lmoe_status lmoe_experts_forward(const lmoe_layer *layer, const float *x, const uint32_t *ids, const float *weights,
+                                 int64_t t, int32_t add_shared, float *out, void *workspace, size_t workspace_bytes,
+                                 void *stream);
+
 /* `MoeBlock::forward` on the prefill path (the mm_id branch of src/moe.rs:236-323):
  * route, sort token-slots by expert, grouped GEMM on tensor cores with f16
  * operand tiles dequantized in shared memory and f32 accumulation, SwiGLU in

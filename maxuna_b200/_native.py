@@ -47,6 +47,8 @@ PROTOTYPES = {
     "lmoe_layer_destroy": (None, [c_vp]),
     "lmoe_layer_workspace_bytes": (c_sz, [c_vp, c_i64]),
     "lmoe_moe_forward_decode": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_experts_workspace_bytes": (c_sz, [c_vp, c_i64]),
+    "lmoe_experts_forward": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_prefill": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_host": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_forward_rows": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),

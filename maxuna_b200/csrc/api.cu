@@ -359,5 +359,6 @@ extern "C" lmoe_status lmoe_check_device_flag(void *workspace, void *stream) {
                      flag[3],
                      flag[0] == LMOE_FLAG_BAD_EXPERT_ID ? "expert id out of range"
                      : flag[0] == LMOE_FLAG_WAIT_TIMEOUT ? "bounded wait ran out"
+                     : flag[0] == LMOE_FLAG_BAD_INDEX    ? "index guard tripped"
                                                          : "unknown");
 }

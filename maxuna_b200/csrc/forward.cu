@@ -7,11 +7,16 @@
 size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k);
 int decode_max_tokens();
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
-                              float *w_out, void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream);
+                              float *w_out, const uint32_t *ext_ids, const float *ext_w, int with_shared, void *workspace,
+                              size_t workspace_bytes, int first_launch, cudaStream_t stream);
 // prefill.cu
 size_t prefill_workspace_bytes(const lmoe_layer *Ly, int64_t t);
 lmoe_status launch_moe_prefill(const lmoe_layer *Ly, const float *x, int64_t t, float *out, uint32_t *ids_out,
                                float *w_out, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
+size_t experts_prefill_workspace_bytes(const lmoe_layer *L, int64_t t);
+lmoe_status launch_experts_prefill(const lmoe_layer *L, const float *x, const uint32_t *ids, const float *w, int64_t t,
+                                   int add_shared, float *out, void *workspace, size_t workspace_bytes, cudaStream_t s);
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -51,14 +56,11 @@ static lmoe_status forward_check(const lmoe_layer *layer, const float *x, int64_
     return LMOE_OK;
 }
 
-extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
-                                               uint32_t *ids_out, float *weights_out, void *workspace,
-                                               size_t workspace_bytes, void *stream) {
-    lmoe_clear_error();
-    lmoe_status st = forward_check(layer, x, t, out);
-    if (st) return st;
-    if (t == 0) return LMOE_OK;
-    cudaStream_t s = (cudaStream_t)stream;
+// The mat-vec kernel over any token count, 64 tokens per launch, with the one-call-per-handle guard.
+// ext_ids / ext_w: NULL = route inside the kernel, else the caller's decision [t, top_k].
+static lmoe_status decode_run(const lmoe_layer *layer, const float *x, int64_t t, float *out, uint32_t *ids_out,
+                              float *weights_out, const uint32_t *ext_ids, const float *ext_w, int with_shared,
+                              void *workspace, size_t workspace_bytes, cudaStream_t s) {
     // The kernel's CTAs meet through words owned by the layer: a second call may only start once the
     // previous one has finished.  Calls on one stream are ordered; a call on another stream is refused
     // while the previous call's completion event is still pending.
@@ -73,12 +75,13 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
     }
     // more than 64 tokens: several launches, 64 tokens each, through the same workspace
     const int step = decode_max_tokens();
+    const int64_t K = layer->top_k;
     for (int64_t t0 = 0; t0 < t; t0 += step) {
         const int n = (int)(t - t0 < step ? t - t0 : step);
-        st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
-                               ids_out ? ids_out + t0 * layer->top_k : nullptr,
-                               weights_out ? weights_out + t0 * layer->top_k : nullptr, workspace, workspace_bytes,
-                               t0 == 0, s);
+        lmoe_status st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
+                                           ids_out ? ids_out + t0 * K : nullptr, weights_out ? weights_out + t0 * K : nullptr,
+                                           ext_ids ? ext_ids + t0 * K : nullptr, ext_w ? ext_w + t0 * K : nullptr, with_shared,
+                                           workspace, workspace_bytes, t0 == 0, s);
         if (st) return st;
     }
     if (cudaEventRecord(layer->dec_event, s) == cudaSuccess) {
@@ -88,6 +91,44 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
         (void)cudaGetLastError();
     }
     return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const float *x, int64_t t, float *out,
+                                               uint32_t *ids_out, float *weights_out, void *workspace,
+                                               size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, x, t, out);
+    if (st) return st;
+    if (t == 0) return LMOE_OK;
+    return decode_run(layer, x, t, out, ids_out, weights_out, nullptr, nullptr, 1, workspace, workspace_bytes,
+                      (cudaStream_t)stream);
+}
+
+// `ExpertFfn::forward`, src/moe.rs:19-21: the caller routed (ids / weights on the device).
+extern "C" size_t lmoe_experts_workspace_bytes(const lmoe_layer *layer, int64_t max_tokens) {
+    if (!layer || max_tokens < 0) return 0;
+    const int tdec = (int)(max_tokens < decode_max_tokens() ? (max_tokens < 1 ? 1 : max_tokens) : decode_max_tokens());
+    const size_t dec = decode_workspace_bytes(tdec, (int)layer->hidden, (int)layer->expert_ff, (int)layer->n_expert,
+                                              (int)layer->top_k);
+    const size_t pre = experts_prefill_workspace_bytes(layer, max_tokens);
+    return lmoe_align_up(dec > pre ? dec : pre, 256);
+}
+
+extern "C" lmoe_status lmoe_experts_forward(const lmoe_layer *layer, const float *x, const uint32_t *ids,
+                                            const float *weights, int64_t t, int32_t add_shared, float *out,
+                                            void *workspace, size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, x, t, out);
+    if (st) return st;
+    if (!ids || !weights) return lmoe_fail(LMOE_ERR_INVALID, "ids/weights is NULL");
+    if (t == 0) return LMOE_OK;
+    if (!workspace || workspace_bytes < lmoe_experts_workspace_bytes(layer, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes for %lld tokens, got %zu",
+                         lmoe_experts_workspace_bytes(layer, t), (long long)t, workspace_bytes);
+    if (t >= lmoe_mm_id_min_seq())
+        return launch_experts_prefill(layer, x, ids, weights, t, add_shared, out, workspace, workspace_bytes, (cudaStream_t)stream);
+    return decode_run(layer, x, t, out, nullptr, nullptr, ids, weights, add_shared, workspace, workspace_bytes,
+                      (cudaStream_t)stream);
 }
 
 extern "C" lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, int64_t t, float *out,

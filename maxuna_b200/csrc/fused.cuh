@@ -7,6 +7,7 @@
 enum {
     LMOE_FLAG_BAD_EXPERT_ID = 0x1,
     LMOE_FLAG_WAIT_TIMEOUT = 0x2,
+    LMOE_FLAG_BAD_INDEX = 0x4,
 };
 
 // seam checks shared by the mat-vec and grouped-GEMM entry points (api.cu)

@@ -296,12 +296,10 @@ bool layer_mm_ok(const lmoe_layer *L) {
 
 } // namespace
 
-size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
-    if (t < 1) t = 1;
-    const int64_t rows = t * L->top_k;
-    size_t o = 65536;
-    o += lmoe_align_up((size_t)t * L->n_expert * 4, 256);            // logits
-    o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // ids, weights
+// Scratch of the routed (+ shared) experts of `t` tokens with `top_k` slots each, after the routing decision.
+static size_t experts_ws_bytes(const lmoe_layer *L, int64_t t, int64_t top_k) {
+    const int64_t rows = t * top_k;
+    size_t o = 0;
     o += lmoe_map0_scratch_bytes(L->n_expert, t);
     o += lmoe_align_up((size_t)rows * L->hidden * 4, 256);           // routed partial rows
     o += lmoe_align_up((size_t)t * L->hidden * 4, 256);              // shared expert rows
@@ -309,6 +307,62 @@ size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
     o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // sorted position and scale of every routed row
     o += 2 * lmoe_align_up((size_t)t * 4, 256);                      // the same for the shared expert's rows
     o += ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
+    return o;
+}
+
+// The experts of a block on a routing decision that is already on the device: per-expert row lists, grouped
+// GEMMs, slot-order sum, optionally the shared expert.  x: [t, hidden] f32 or f16; ids / w: [t, top_k]
+// (`masked`: ids >= n_expert are empty slots).  `ws` holds experts_ws_bytes(); `flag` is the device flag.
+static lmoe_status experts_prefill(const lmoe_layer *L, const void *x, int x_f16, const uint32_t *ids, const float *w,
+                                   int64_t t, int64_t top_k, int masked, int add_shared, float *out, uint8_t *ws,
+                                   uint32_t *flag, cudaStream_t s) {
+    const int64_t rows = t * top_k, H = L->hidden;
+    Carver c{ws, 0};
+    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
+    float *y = c.take<float>((size_t)rows * H);
+    float *ysh = c.take<float>((size_t)t * H);
+    uint32_t *sh_list = c.take<uint32_t>((size_t)t + 64);
+    int32_t *spos = c.take<int32_t>((size_t)rows);
+    float *rscale = c.take<float>((size_t)rows);
+    int32_t *sh_spos = c.take<int32_t>((size_t)t);
+    float *sh_scale = c.take<float>((size_t)t);
+    uint8_t *ffn_ws = ws + c.off;
+    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
+    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
+    // ids >= n_expert match no expert's list: those slots stay empty
+    LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)L->n_expert, tpe, ids_map, s));
+    bool sorted = false, sh_sorted = false;
+    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x, (int)top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s, spos,
+                                 rscale, &sorted, x_f16, masked);
+    if (st) return st;
+    const float *shared = nullptr;
+    if (add_shared && L->sh_gate) {
+        iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64));
+        LMOE_LAUNCH_CHECK("iota_list_kernel");
+        // the shared expert's rows take the same form as the routed ones, so one kernel sums both
+        st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
+                         nullptr, ysh, ffn_ws, flag, s, sorted ? sh_spos : nullptr, sorted ? sh_scale : nullptr, &sh_sorted,
+                         x_f16);
+        if (st) return st;
+        shared = ysh;
+    }
+    const int64_t n = t * (H / 4);
+    if (sorted && (!shared || sh_sorted))
+        sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, rscale, spos, shared, sh_scale, sh_spos, t,
+                                                                      (int)top_k, (int)(H / 4), out);
+    else
+        sum_slots_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, shared, t, (int)top_k, (int)(H / 4), out);
+    LMOE_LAUNCH_CHECK("sum_slots_kernel");
+    return LMOE_OK;
+}
+
+size_t prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
+    if (t < 1) t = 1;
+    const int64_t rows = t * L->top_k;
+    size_t o = 65536;
+    o += lmoe_align_up((size_t)t * L->n_expert * 4, 256);            // logits
+    o += 2 * lmoe_align_up((size_t)rows * 4, 256);                   // ids, weights
+    o += experts_ws_bytes(L, t, L->top_k);
     return o;
 }
 
@@ -325,46 +379,32 @@ lmoe_status launch_moe_prefill(const lmoe_layer *L, const float *x, int64_t t, f
     float *logits = c.take<float>((size_t)t * L->n_expert);
     uint32_t *ids = c.take<uint32_t>((size_t)rows);
     float *w = c.take<float>((size_t)rows);
-    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
-    float *y = c.take<float>((size_t)rows * H);
-    float *ysh = c.take<float>((size_t)t * H);
-    uint32_t *sh_list = c.take<uint32_t>((size_t)t + 64);
-    int32_t *spos = c.take<int32_t>((size_t)rows);
-    float *rscale = c.take<float>((size_t)rows);
-    int32_t *sh_spos = c.take<int32_t>((size_t)t);
-    float *sh_scale = c.take<float>((size_t)t);
-    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
+    uint8_t *ex_ws = static_cast<uint8_t *>(workspace) + c.off;
 
     LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s)); // a fresh device flag: the workspace needs no initialisation
     LMOE_CUDA(launch_route_logits(L->router, x, (int)t, (int)H, (int)L->n_expert, logits, s));
     LMOE_CUDA(launch_route_select(logits, L->bias, (int)t, (int)L->n_expert, (int)L->top_k, L->scale, L->norm, ids, w, s));
-    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
-    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
-    LMOE_CUDA(launch_map0(ids, (int)t, (int)L->top_k, (int)L->n_expert, tpe, ids_map, s));
-    bool sorted = false, sh_sorted = false;
-    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x, (int)L->top_k, t, tpe, ids_map, t, w, y, ffn_ws, flag, s, spos,
-                                 rscale, &sorted);
+    lmoe_status st = experts_prefill(L, x, 0, ids, w, t, L->top_k, 0, 1, out, ex_ws, flag, s);
     if (st) return st;
-    const float *shared = nullptr;
-    if (L->sh_gate) {
-        iota_list_kernel<<<(unsigned)((t + 255) / 256), 256, 0, s>>>(t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64));
-        LMOE_LAUNCH_CHECK("iota_list_kernel");
-        // the shared expert's rows take the same form as the routed ones, so one kernel sums both
-        st = ffn_grouped(L->sh_gate, L->sh_up, L->sh_down, x, 1, t, sh_list, reinterpret_cast<int32_t *>(sh_list + 64), t,
-                         nullptr, ysh, ffn_ws, flag, s, sorted ? sh_spos : nullptr, sorted ? sh_scale : nullptr, &sh_sorted);
-        if (st) return st;
-        shared = ysh;
-    }
-    const int64_t n = t * (H / 4);
-    if (sorted && (!shared || sh_sorted))
-        sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, rscale, spos, shared, sh_scale, sh_spos, t,
-                                                                      (int)L->top_k, (int)(H / 4), out);
-    else
-        sum_slots_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, shared, t, (int)L->top_k, (int)(H / 4), out);
-    LMOE_LAUNCH_CHECK("sum_slots_kernel");
     if (ids_out) LMOE_CUDA(cudaMemcpyAsync(ids_out, ids, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
     if (w_out) LMOE_CUDA(cudaMemcpyAsync(w_out, w, (size_t)rows * 4, cudaMemcpyDeviceToDevice, s));
     return LMOE_OK;
+}
+
+// `ExpertFfn::forward` on the grouped-GEMM path (see lmoe_experts_forward): the caller's routing decision.
+size_t experts_prefill_workspace_bytes(const lmoe_layer *L, int64_t t) {
+    return 65536 + experts_ws_bytes(L, t < 1 ? 1 : t, L->top_k);
+}
+lmoe_status launch_experts_prefill(const lmoe_layer *L, const float *x, const uint32_t *ids, const float *w, int64_t t,
+                                   int add_shared, float *out, void *workspace, size_t workspace_bytes, cudaStream_t s) {
+    if (!layer_mm_ok(L)) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "no grouped-GEMM kernel for this layer's shapes / dtypes");
+    if (!workspace || workspace_bytes < experts_prefill_workspace_bytes(L, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", experts_prefill_workspace_bytes(L, t),
+                         workspace_bytes);
+    if (t * L->top_k > INT32_MAX / 2) return lmoe_fail(LMOE_ERR_INVALID, "too many routed rows");
+    uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
+    LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
+    return experts_prefill(L, x, 0, ids, w, t, L->top_k, 1, add_shared, out, static_cast<uint8_t *>(workspace) + 65536, flag, s);
 }
 
 // ---- op-level entry points ------------------------------------------------------------
@@ -481,9 +521,7 @@ extern "C" lmoe_status lmoe_experts_forward_rows_f16(const lmoe_layer *L, const 
 
 // Token-level form for the expert-parallel exchange: one activation row per token, up to top_k experts each.
 static size_t tokens_ws_bytes(const lmoe_layer *L, int64_t t, int64_t top_k) {
-    const int64_t rows = t * top_k;
-    return 65536 + lmoe_map0_scratch_bytes(L->n_expert, t) + lmoe_align_up((size_t)rows * L->hidden * 4, 256) +
-           2 * lmoe_align_up((size_t)rows * 4, 256) + ffn_bytes(rows, L->hidden, L->expert_ff, L->n_expert);
+    return 65536 + experts_ws_bytes(L, t, top_k);
 }
 
 extern "C" size_t lmoe_tokens_workspace_bytes(const lmoe_layer *L, int64_t t, int64_t top_k) {
@@ -503,28 +541,9 @@ extern "C" lmoe_status lmoe_experts_forward_tokens_f16(const lmoe_layer *L, cons
     if (!workspace || workspace_bytes < tokens_ws_bytes(L, t, top_k))
         return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", tokens_ws_bytes(L, t, top_k), workspace_bytes);
     cudaStream_t s = (cudaStream_t)stream;
-    const int64_t rows = t * top_k, H = L->hidden;
-    Carver c{static_cast<uint8_t *>(workspace), 65536};
     uint32_t *flag = reinterpret_cast<uint32_t *>(workspace);
-    uint8_t *map0 = c.take<uint8_t>(lmoe_map0_scratch_bytes(L->n_expert, t));
-    float *y = c.take<float>((size_t)rows * H);
-    int32_t *spos = c.take<int32_t>((size_t)rows);
-    float *rscale = c.take<float>((size_t)rows);
-    uint8_t *ffn_ws = static_cast<uint8_t *>(workspace) + c.off;
-    uint32_t *tpe = reinterpret_cast<uint32_t *>(map0);
-    int32_t *ids_map = reinterpret_cast<int32_t *>(map0 + L->n_expert * 4);
     LMOE_CUDA(cudaMemsetAsync(flag, 0, 16, s));
-    // ids >= n_expert match no expert's list: those slots stay empty
-    LMOE_CUDA(launch_map0(ids, (int)t, (int)top_k, (int)L->n_expert, tpe, ids_map, s));
-    bool sorted = false;
-    lmoe_status st = ffn_grouped(L->gate, L->up, L->down, x_f16, (int)top_k, t, tpe, ids_map, t, weights, y, ffn_ws, flag, s,
-                                 spos, rscale, &sorted, 1, 1);
-    if (st) return st;
-    const int64_t n = t * (H / 4);
-    sum_sorted_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, rscale, spos, nullptr, nullptr, nullptr, t, (int)top_k,
-                                                                  (int)(H / 4), out);
-    LMOE_LAUNCH_CHECK("sum_sorted_kernel");
-    return LMOE_OK;
+    return experts_prefill(L, x_f16, 1, ids, weights, t, top_k, 1, 0, out, static_cast<uint8_t *>(workspace) + 65536, flag, s);
 }
 
 extern "C" lmoe_status lmoe_shared_forward(const lmoe_layer *L, const float *x, int64_t t, float *out, void *workspace,

@@ -166,6 +166,13 @@ public:
         return Result::from(lmoe_moe_forward_decode(h_, x_normed, seq, out, ids_out, weights_out, workspace, workspace_bytes,
                                                     stream));
     }
+    // `ExpertFfn::forward` (src/moe.rs:19-21): the routed experts on the caller's routing decision.
+    size_t experts_workspace_bytes(int64_t max_tokens) const { return lmoe_experts_workspace_bytes(h_, max_tokens); }
+    Result experts_forward(const float *x, const uint32_t *ids, const float *weights, int64_t seq, float *out, void *workspace,
+                           size_t workspace_bytes, void *stream, bool add_shared = false) const {
+        return Result::from(lmoe_experts_forward(h_, x, ids, weights, seq, add_shared ? 1 : 0, out, workspace, workspace_bytes,
+                                                 stream));
+    }
     // The FFN half of a layer (src/model.rs:340-350): out = ffn_inp + forward(ffn_norm(ffn_inp)).
     size_t layer_workspace_bytes(int64_t max_tokens) const { return lmoe_moe_layer_workspace_bytes(h_, max_tokens); }
     Result layer_forward(const float *ffn_inp, const float *ffn_norm_weight, float rms_eps, int64_t seq, float *out,

@@ -192,6 +192,25 @@ class MoeBlock:
                  None if w is None else w.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr()))
         return (out, ids, w) if return_routing else out
 
+    def experts_forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, add_shared: bool = False):
+        """`ExpertFfn::forward`, src/moe.rs:19-21, through the fused kernels (`lmoe_experts_forward`): the
+        routing decision is the caller's; ids >= n_expert are empty slots."""
+        x = x.to(torch.float32).contiguous()
+        seq = x.shape[0]
+        if x.dim() != 2 or x.shape[1] != self.hidden:
+            raise LmoeError(-1, f"x must be [seq, {self.hidden}], got {tuple(x.shape)}")
+        if tuple(ids.shape) != (seq, self.n_expert_used) or tuple(weights.shape) != (seq, self.n_expert_used):
+            raise LmoeError(-1, f"ids / weights must be [{seq}, {self.n_expert_used}]")
+        ids = ids.contiguous()
+        weights = weights.to(torch.float32).contiguous()
+        out = torch.empty(seq, self.hidden, dtype=torch.float32, device=x.device)
+        n = lib().lmoe_experts_workspace_bytes(self._h, seq)
+        if getattr(self, "_ews", None) is None or self._ews.numel() < n:
+            self._ews = torch.empty(n, dtype=torch.uint8, device=x.device)
+        check(lib().lmoe_experts_forward(self._h, x.data_ptr(), ids.data_ptr(), weights.data_ptr(), seq, int(add_shared),
+                                         out.data_ptr(), self._ews.data_ptr(), self._ews.numel(), stream_ptr()))
+        return out
+
     def layer_forward(self, ffn_inp: torch.Tensor, norm_weight: torch.Tensor, eps: float = 1e-6,
                       return_routing: bool = False):
         """`lmoe_moe_layer_forward`: ``ffn_inp + MoeBlock::forward(ffn_norm(ffn_inp))``, src/model.rs:340-350."""

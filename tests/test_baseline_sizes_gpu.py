@@ -144,7 +144,7 @@ def test_prefill_entries_clear_the_device_flag(dev, entry):
     from maxuna_b200.gguf import stream_ptr
     from maxuna_b200.moe import MoeBlock
 
-    blk = MoeBlock.random(256, 256, 8, 3, seed=95, device=dev, weight_std=0.25)
+    blk = MoeBlock.random(256, 512, 8, 3, seed=95, device=dev, weight_std=0.25)
     t = 70
     x = torch.randn(t, 256, device=dev)
     out = torch.empty(t, 256, device=dev)
