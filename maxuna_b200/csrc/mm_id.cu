@@ -26,7 +26,7 @@
 namespace {
 
 constexpr int MM_M = 128;      // weight rows per tile
-constexpr int MM_N = 256;      // routed rows per tile
+constexpr int MM_N = LMOE_MM_N; // routed rows per tile (192)
 constexpr int MM_K = 64;       // k per pipeline stage (one 128-byte swizzle row of f16)
 constexpr int MM_THREADS = 16 * 32;
 constexpr int A_STAGE_BYTES = MM_M * MM_K * 2; // 16 KB
@@ -103,6 +103,25 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc),
         "r"(accum) : "memory");
+}
+// The same with the A operand in tensor memory: 128 lanes (weight rows) x 8 columns (K = 16 as f16 pairs).
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc),
+        "r"(accum) : "memory");
+}
+// 32 registers of every lane -> 32 columns of the warp's 32 tensor-memory lanes, then wait for the store.
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -241,12 +260,12 @@ __global__ void __launch_bounds__(512) build_tiles_kernel(const uint32_t *__rest
     if (e == 0) *n_tiles = min(pre[512], max_tiles);
 }
 
-// Routed rows -> the f16 B operand in TILE ORDER.  Row tile `slot` (256 routed rows of one expert)
-// and k-stage ks (64 values) form one contiguous 32 KB block that is the exact shared-memory image
+// Routed rows -> the f16 B operand in TILE ORDER.  Row tile `slot` (MM_N routed rows of one expert)
+// and k-stage ks (64 values) form one contiguous 24 KB block that is the exact shared-memory image
 // of a B stage: row rr at rr*128 B, its 16-byte chunk c at position c ^ (rr & 7) (the 128-byte
 // swizzle of the tensor core's K-major layout), 8 values per chunk in the order [0 2 1 3 4 6 5 7]
 // (the order in which the dequantiser emits a chunk of weights).  A B stage is then ONE bulk copy.
-// pos[flat id] = slot*256 + rr lets later kernels (SwiGLU) write rows in the same order.
+// pos[flat id] = slot*MM_N + rr lets later kernels (SwiGLU) write rows in the same order.
 __device__ __forceinline__ size_t tiled_off(int slot, int k_stages, int ks, int rr, int c) {
     return (((size_t)slot * k_stages + ks) * MM_N + rr) * 128 + ((size_t)(c ^ (rr & 7)) << 4);
 }
@@ -538,17 +557,24 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mm_id_kernel(const __grid_const
 
 // ================= gate + up in one pass, SwiGLU in the epilogue =========================
 // Same tile list as above, but a CTA multiplies one block of routed rows by 128 gate rows AND the
-// matching 128 up rows (two accumulators of 256 TMEM columns), so every activation stage is
-// loaded once for both projections.  The quantized rows are read straight from global memory
-// by the dequantising threads (one thread per weight row, two stages prefetched in registers):
-// no staging ring for raw blocks.  Epilogue: act = silu(gate) * up, f32, one row per routed row.
+// matching 128 up rows (two accumulators of MM_N tensor-memory columns), so every activation stage is
+// loaded once for both projections.  The quantized rows are staged by TMA tile loads; the dequantising
+// threads (one per weight row and projection) write their f16 values straight into TENSOR MEMORY
+// (tcgen05.st: lane = weight row, 32 columns = the 64 values of a k-stage) and the tensor core takes its
+// A operand from there, so the dequantised tile never passes through shared memory: per k-stage that
+// removes a 32 KB write and a 32 KB read from the shared-memory traffic that bounded the loop.
+// Tensor-memory columns: [0, MM_N) gate accumulator, [MM_N, 2 MM_N) up accumulator,
+// [2 MM_N, 2 MM_N + 128) the A operand: 2 stages x 2 projections x 32 columns.
+// Epilogue: act = silu(gate) * up, f32, one row per routed row.
 //   warps 0-7   dequant (thread = (projection, weight row))     warp 8   B loader (bulk copy)
-//   warp 9      MMA issuer                                        warps 10-13  epilogue
+//   warp 9      MMA issuer     warps 10-13  epilogue     warp 14  loader of the quantized columns
 constexpr int GU_THREADS = 15 * 32;
-constexpr int GU_A_STAGE = 2 * A_STAGE_BYTES;
 constexpr int GU_NS = 2;
 constexpr int GU_RAW_SLOT = MM_M * Q4K_BYTES; // one super-block column of 128 rows of one projection
 constexpr int GU_RAW_SLOTS = 4;               // (column parity, projection)
+constexpr int GU_ACC_UP = MM_N;               // first tensor-memory column of the up accumulator
+constexpr int GU_A_COL0 = 2 * MM_N;           // first column of the A operand stages
+static_assert(GU_A_COL0 + GU_NS * 2 * 32 <= 512, "tensor memory: two accumulators and the operand stages must fit 512 columns");
 
 struct GuParams {
     // 2-D views of the gate / up stacks as bytes: [n_expert * n_out rows][row_bytes], box = 144 bytes x 128 rows
@@ -565,8 +591,9 @@ struct GuParams {
     uint32_t *flag;
 };
 
-// 64 weights (sub-block pair j) of one Q4_K row from registers -> 8 swizzled chunks
-__device__ __forceinline__ void dequant_q4k_regs(const uint4 hdr, const uint4 qa, const uint4 qb, int j, uint8_t *a_stage, int r) {
+// 64 weights (sub-block pair j) of one Q4_K row -> the 32 words of the row's k-stage, in the order the
+// activation rows are stored (8-value chunks as [0 2 1 3 4 6 5 7]): word 4c + i = chunk c, pair i.
+__device__ __forceinline__ void dequant_q4k_regs(const uint4 hdr, const uint4 qa, const uint4 qb, int j, uint32_t (&o)[32]) {
     const float d = lmoe_h2f((uint16_t)(hdr.x & 0xffff)), dmin = lmoe_h2f((uint16_t)(hdr.x >> 16));
     uint32_t sc[2], mn[2];
     q4k_unpack_scales(hdr.y, hdr.z, hdr.w, sc[0], sc[1], mn[0], mn[1]);
@@ -576,24 +603,22 @@ __device__ __forceinline__ void dequant_q4k_regs(const uint4 hdr, const uint4 qa
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-        uint32_t lo[4], hi[4];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint32_t v = w[2 * c + h], v8 = v >> 8;
-            lo[2 * h] = h2_sub_fma((v & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
-            lo[2 * h + 1] = h2_sub_fma((v8 & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
-            hi[2 * h] = h2_sub_fma((v & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
-            hi[2 * h + 1] = h2_sub_fma((v8 & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+            // low nibbles (sub-block 2j): chunks 0-3; high nibbles (sub-block 2j+1): chunks 4-7
+            o[4 * c + 2 * h] = h2_sub_fma((v & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            o[4 * c + 2 * h + 1] = h2_sub_fma((v8 & 0x000F000Fu) | 0x64006400u, 0x64006400u, s_lo, m_lo);
+            o[16 + 4 * c + 2 * h] = h2_sub_fma((v & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
+            o[16 + 4 * c + 2 * h + 1] = h2_sub_fma((v8 & 0x00F000F0u) | 0x54005400u, 0x54005400u, s_hi, m_hi);
         }
-        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(a_stage + swz_off(r, c + 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     }
 }
 
 __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_constant__ GuParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_st = smem, *b_st = smem + GU_NS * GU_A_STAGE;
+    uint8_t *b_st = smem;
     uint8_t *raw = b_st + GU_NS * B_STAGE_BYTES; // quantized super-block columns, TMA-staged
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw + GU_RAW_SLOTS * GU_RAW_SLOT);
     // full[s]: eight dequant warps + the B loader's expect_tx arrival; empty[s]: one tcgen05.commit;
@@ -648,14 +673,17 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 for (int j = 0; j < 4; j++, g++) {
                     const int s = g % GU_NS;
                     ok = ok && mb_wait(&empty[s], ((g / GU_NS) & 1) ^ 1, P.flag, 3);
-                    uint8_t *ast = a_st + (size_t)s * GU_A_STAGE + sub * A_STAGE_BYTES;
+                    uint32_t o[32];
                     if (rvalid) {
-                        dequant_q4k_regs(hdr, blk[1 + 2 * j], blk[2 + 2 * j], j, ast, r);
+                        dequant_q4k_regs(hdr, blk[1 + 2 * j], blk[2 + 2 * j], j, o);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(ast + swz_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = 0; c < 32; c++) o[c] = 0u;
                     }
-                    fence_async_smem();
+                    // lane = weight row of this warp's quadrant; the stage's 32 columns of this projection
+                    tc_fence_after();
+                    tc_st32(tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + GU_A_COL0 + (uint32_t)(s * 2 + sub) * 32u, o);
+                    tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mb_arrive(&full[s]);
                 }
@@ -716,13 +744,9 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
         if (lane == 0) {
             // The issuing thread runs a dependent chain of scalar instructions, so everything it can
             // know ahead is precomputed: operand descriptors per ring slot, slot and phase as counters.
-            uint64_t ad0[GU_NS], ad1[GU_NS], bd[GU_NS];
+            uint64_t bd[GU_NS];
 #pragma unroll
-            for (int s = 0; s < GU_NS; s++) {
-                ad0[s] = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
-                ad1[s] = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
-                bd[s] = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
-            }
+            for (int s = 0; s < GU_NS; s++) bd[s] = umma_desc(s32(b_st + (size_t)s * B_STAGE_BYTES));
             uint32_t it = 0, ph = 0;
             int s = 0;
             bool ok = true;
@@ -736,13 +760,13 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                     ok = mb_wait(&full[s], ph, P.flag, 6);
                     tc_fence_after();
                     // slot-indexed descriptors without dynamic register indexing
-                    const uint64_t a0 = s == 0 ? ad0[0] : ad0[GU_NS - 1];
-                    const uint64_t a1 = s == 0 ? ad1[0] : ad1[GU_NS - 1];
                     const uint64_t b0 = s == 0 ? bd[0] : bd[GU_NS - 1];
+                    // A operand: 8 tensor-memory columns per K = 16 step of the stage's gate / up block
+                    const uint32_t a0 = tmem_base + GU_A_COL0 + (uint32_t)s * 64u, a1 = a0 + 32u;
 #pragma unroll
                     for (int kk = 0; kk < MM_K / 16; kk++) {
-                        tc_mma_f16(tmem_base, a0 + 2 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                        tc_mma_f16(tmem_base + 256, a1 + 2 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16_ts(tmem_base, a0 + 8 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        tc_mma_f16_ts(tmem_base + GU_ACC_UP, a1 + 8 * kk, b0 + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     tc_commit(&empty[s]);
                     if (++s == GU_NS) { s = 0; ph ^= 1; }
@@ -776,7 +800,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 if (cb >= nv) break;
                 uint32_t vg[32], vu[32];
                 tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + cb, vg);
-                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + 256 + cb, vu);
+                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + GU_ACC_UP + cb, vu);
                 const int myfid = fids[c];
                 if (P.sorted) {
                     // rows in expert-sorted order: consecutive tile columns are consecutive rows
@@ -817,6 +841,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 constexpr int DN_DQ_WARPS = 16;                       // dequant warps
 constexpr int DN_THREADS = (DN_DQ_WARPS + 6) * 32;    // + B loader, MMA issuer, four epilogue warps
 constexpr int DN_NSA = 3, DN_NSB = 2;
+constexpr int GU_A_STAGE = 2 * A_STAGE_BYTES;    // two 128-row A tiles of one k-stage
 
 struct DnParams {
     const uint8_t *w; // down stack (Q6_K)
@@ -1278,7 +1303,7 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     P.wg = gate->blocks(); P.wu = up->blocks(); P.expert_bytes = gate->expert_bytes();
     P.n_out = (int)gate->n_out; P.k = (int)gate->k; P.xt = static_cast<const uint8_t *>(xt);
     P.ids_map = ids_map; P.map_stride = (int)map_stride; P.tiles = tiles; P.n_tiles = n_tiles; P.act = act; P.sorted = sorted; P.flag = flag;
-    const int smem = GU_NS * (GU_A_STAGE + B_STAGE_BYTES) + GU_RAW_SLOTS * GU_RAW_SLOT + 256 + 1024;
+    const int smem = GU_NS * B_STAGE_BYTES + GU_RAW_SLOTS * GU_RAW_SLOT + 256 + 1024;
     static thread_local int c_dev = -1, c_sms = 0;
     int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));

@@ -26,7 +26,7 @@ namespace {
 
 // One warp per row: act = silu(g) * u; l2 = clamp(||act||, 1e-8, 1e30); the f16 operand of the
 // down projection is act * 32768 / l2 (src/moe.rs:292-302), written in the grouped GEMM's tile
-// order (row tile pos>>8, row pos&255, 128-byte swizzle, groups of 8 as [0 2 1 3 4 6 5 7]);
+// order (row tile pos / LMOE_MM_N, row pos % LMOE_MM_N, 128-byte swizzle, groups of 8 as [0 2 1 3 4 6 5 7]);
 // scale[row] = l2 * 2^-15 * weight[row] undoes it in the down epilogue together with the
 // routing weight (src/ops/combine.metal:102-133).
 __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restrict__ g, const float *__restrict__ u,
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restric
         __align__(16) __half2 h[4] = {__floats2half2_rn(a[0], a[2]), __floats2half2_rn(a[1], a[3]),
                                       __floats2half2_rn(a[4], a[6]), __floats2half2_rn(a[5], a[7])};
         const int ci = i >> 3;
-        const size_t off = (((size_t)(p >> 8) * (ff / 64) + (ci >> 3)) * 256 + (p & 255)) * 128 +
+        const size_t off = (((size_t)(p / LMOE_MM_N) * (ff / 64) + (ci >> 3)) * LMOE_MM_N + (p % LMOE_MM_N)) * 128 +
                            ((size_t)((ci & 7) ^ (p & 7)) << 4);
         *reinterpret_cast<uint4 *>(act + off) = *reinterpret_cast<const uint4 *>(h);
     }
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) rescale_rows_kernel(const float *__restri
         __align__(16) __half2 h[4] = {__floats2half2_rn(a0.x * k, a0.z * k), __floats2half2_rn(a0.y * k, a0.w * k),
                                       __floats2half2_rn(a1.x * k, a1.z * k), __floats2half2_rn(a1.y * k, a1.w * k)};
         const int ci = i >> 3;
-        const size_t off = (((size_t)(p >> 8) * (ff / 64) + (ci >> 3)) * 256 + (p & 255)) * 128 +
+        const size_t off = (((size_t)(p / LMOE_MM_N) * (ff / 64) + (ci >> 3)) * LMOE_MM_N + (p % LMOE_MM_N)) * 128 +
                            ((size_t)((ci & 7) ^ (p & 7)) << 4);
         *reinterpret_cast<uint4 *>(act + off) = *reinterpret_cast<const uint4 *>(h);
     }
