@@ -832,16 +832,25 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 }
 
 
-// ================= down projection (Q6_K), 256 weight rows per CTA ===========================
-// Two 128-row sub-tiles of the same stack share every activation stage (two accumulators of
-// 256 TMEM columns).  The quantized rows are read from global memory one super-block column at a
-// time, in 16-byte pieces of the aligned window around each 210-byte block, staged in shared memory
-// and converted by one thread per (row, 16-wide l range); see the helpers below.
-//   warps 0-15 dequant    warp 16 B loader    warp 17 MMA issuer    warps 18-21 epilogue
-constexpr int DN_DQ_WARPS = 16;                       // dequant warps
-constexpr int DN_THREADS = (DN_DQ_WARPS + 6) * 32;    // + B loader, MMA issuer, four epilogue warps
-constexpr int DN_NSA = 3, DN_NSB = 2;
-constexpr int GU_A_STAGE = 2 * A_STAGE_BYTES;    // two 128-row A tiles of one k-stage
+// ================= down projection (Q6_K), 128 weight rows per CTA tile ===========================
+// A tile's quantized rows are four contiguous runs of 32 rows (one per tensor-memory lane quadrant); each run
+// is ONE bulk copy into a ring of shared-memory slots, so no load/store unit moves weight bytes.  Sixteen
+// dequantising warps (quadrant x 16-wide l range x nibble half) read their row's block out of shared memory
+// - at whatever 2-byte alignment the 210-byte blocks fall, re-aligned with funnel shifts - convert 32 weights
+// each with one scale per 16 and store them straight into TENSOR MEMORY (tcgen05.st), from where the tensor
+// core takes its A operand (TS-form tcgen05.mma).  Two accumulator buffers let the epilogue of a tile overlap
+// the multiplies of the next.
+// Tensor-memory columns: [0, MM_N) and [MM_N, 2 MM_N) accumulator buffers, [2 MM_N, 2 MM_N + 128) four A stages.
+//   warps 0-15 dequant (quadrant = warp & 3, l half = (warp >> 2) & 1, nibble half = warp >> 3)
+//   warp 16 loader of the quantized runs    warp 17 B loader    warp 18 MMA issuer    warps 19-22 epilogue
+constexpr int DN_DQ_WARPS = 16;
+constexpr int DN_THREADS = (DN_DQ_WARPS + 7) * 32;
+constexpr int DN_NSA = 4, DN_NSB = 2;
+constexpr int DN_RUN_ROWS = 32;                 // rows of one bulk-copied run (= one lane quadrant)
+constexpr int DN_RAW_SLOTS = 6;                 // ring of runs: the four of the current tile and two ahead
+constexpr int DN_MAX_NB = 4;                    // super-blocks per row this kernel stages (k <= 1024)
+constexpr int DN_A_COL0 = 2 * MM_N;
+static_assert(DN_A_COL0 + DN_NSA * 32 <= 512, "tensor memory: two accumulators and four operand stages must fit 512 columns");
 
 struct DnParams {
     const uint8_t *w; // down stack (Q6_K)
@@ -855,62 +864,12 @@ struct DnParams {
     float *out; // [rows, n_out]
     int sorted; // rows of `out` in expert-sorted order, unscaled, instead of scaled rows by flat id
     uint32_t *flag;
+    int raw_slot_bytes; // 32 rows of quantized blocks + slack for re-aligning reads
 };
 
-// Predicated 16-byte global load that leaves zeros when off (no select after the load, so nothing waits
-// for the data until it is really used).
-__device__ __forceinline__ uint4 ldg128_if(const void *p, bool on) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t@q ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
-                 : "l"(p), "r"((uint32_t)on));
-    return v;
-}
-
-// Down-projection dequant, one super-block column b of the tile's 256 rows at a time:
-//   load   the 210 bytes of (row, b) lie inside a 16-byte aligned window of 224 bytes; 14 lanes read one
-//          window with 16-byte loads (two rows per warp instruction: whole cache lines per request);
-//   stage  the windows go to shared memory, one row of 228 bytes per weight row (an odd number of words,
-//          so the per-row reads below spread over the banks);
-//   row    for each 128-weight half, one thread per (row, 16-wide l range) picks its ql / qh / scale
-//          bytes out of the window - at the byte offset the block has inside it, re-aligned with funnel
-//          shifts - and converts 64 weights with one scale each.
-constexpr int DN_WIN = 224;                         // window bytes per (row, super-block)
-constexpr int DN_RAWP = DN_WIN + 4;                 // shared-memory pitch of a staged window
-constexpr int DN_RAW_BYTES = 2 * MM_M * DN_RAWP + 64; // + slack: a re-aligning read may touch 16 bytes past a window
-constexpr int DN_LPT = 2 * MM_M / (DN_DQ_WARPS * 2); // window loads per thread (two rows per warp instruction)
-
-struct DnWin {
-    uint4 v[DN_LPT];
-};
-
-// (issued in two halves, PART = 0 / 1, so that the requests of a column do not all queue at once)
-template <int PART>
-__device__ __forceinline__ void dn_load(DnWin &R, const uint8_t *tile_w, int row_bytes, int rows_valid, int b, int warp, int lane) {
-    const int sub = lane / 14, piece = lane - 14 * sub; // lanes 28-31 idle
-#pragma unroll
-    for (int i = PART * (DN_LPT / 2); i < (PART + 1) * (DN_LPT / 2); i++) {
-        const int row = 2 * warp + sub + 2 * DN_DQ_WARPS * i;
-        const bool on = lane < 28 && row < rows_valid;
-        const uintptr_t blk = reinterpret_cast<uintptr_t>(tile_w) + (size_t)(on ? row : 0) * row_bytes + (size_t)b * Q6K_BYTES;
-        R.v[i] = ldg128_if(reinterpret_cast<const void *>((blk & ~(uintptr_t)15) + 16 * piece), on);
-    }
-}
-
-__device__ __forceinline__ void dn_stage(const DnWin &R, uint8_t *raw, int warp, int lane) {
-    const int sub = lane / 14, piece = lane - 14 * sub;
-    if (lane >= 28) return;
-#pragma unroll
-    for (int i = 0; i < DN_LPT; i++) {
-        const int row = 2 * warp + sub + 2 * DN_DQ_WARPS * i;
-        uint32_t *dst = reinterpret_cast<uint32_t *>(raw + row * DN_RAWP + 16 * piece);
-        dst[0] = R.v[i].x; dst[1] = R.v[i].y; dst[2] = R.v[i].z; dst[3] = R.v[i].w;
-    }
-}
-
-// 16 bytes at byte offset `o` (even) of a staged window, as four words
-__device__ __forceinline__ void dn_read16(const uint8_t *rowp, int o, uint32_t (&out)[4]) {
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(rowp) + (o >> 2);
+// 16 bytes at byte offset `o` (even) from a 4-byte aligned base, as four words
+__device__ __forceinline__ void dn_read16(const uint8_t *base4, int o, uint32_t (&out)[4]) {
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(base4) + (o >> 2);
     const uint32_t sh = (uint32_t)(o & 3) * 8u;
     const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
     out[0] = __funnelshift_r(w0, w1, sh);
@@ -919,18 +878,20 @@ __device__ __forceinline__ void dn_read16(const uint8_t *rowp, int o, uint32_t (
     out[3] = __funnelshift_r(w3, w4, sh);
 }
 
-// The fields of (row, half n, l range lh) out of the staged window whose block starts at byte `sh`.
+// The fields of (row, half n, l range lh) of the Q6_K block that starts `sh` bytes (even) after the 4-byte
+// aligned address base4: 16 bytes of ql for groups {0,2} and for groups {1,3}, 16 bytes of qh, the eight
+// scales of the half, d.
 struct DnFields {
     uint32_t qa[4], qb[4], qh[4], s0, s1;
     float d;
 };
-__device__ __forceinline__ void dn_fields(const uint8_t *rowp, int sh, int n, int lh, DnFields &F) {
-    dn_read16(rowp, sh + 64 * n + 16 * lh, F.qa);
-    dn_read16(rowp, sh + 64 * n + 32 + 16 * lh, F.qb);
-    dn_read16(rowp, sh + 128 + 32 * n + 16 * lh, F.qh);
+__device__ __forceinline__ void dn_fields(const uint8_t *base4, int sh, int n, int lh, DnFields &F) {
+    dn_read16(base4, sh + 64 * n + 16 * lh, F.qa);
+    dn_read16(base4, sh + 64 * n + 32 + 16 * lh, F.qb);
+    dn_read16(base4, sh + 128 + 32 * n + 16 * lh, F.qh);
     {
         const int o = sh + 192 + 8 * n;
-        const uint32_t *w = reinterpret_cast<const uint32_t *>(rowp) + (o >> 2);
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(base4) + (o >> 2);
         const uint32_t s = (uint32_t)(o & 3) * 8u;
         const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
         F.s0 = __funnelshift_r(w0, w1, s);
@@ -938,52 +899,55 @@ __device__ __forceinline__ void dn_fields(const uint8_t *rowp, int sh, int n, in
     }
     {
         const int o = sh + 208;
-        const uint32_t w = reinterpret_cast<const uint32_t *>(rowp)[o >> 2];
+        const uint32_t w = reinterpret_cast<const uint32_t *>(base4)[o >> 2];
         F.d = lmoe_h2f((uint16_t)((w >> ((o & 2) * 8)) & 0xffffu));
     }
 }
 
-// Groups 2*hn and 2*hn+1 (low nibbles: hn = 0, the even k-stage; high nibbles: hn = 1, the odd one) of
-// one (row, l range): 32 weights -> four 16-byte chunks of the stage.
-__device__ __forceinline__ void dn_dequant_stage(const DnFields &F, int hn, uint8_t *stage, int row, int lh) {
-    uint8_t *base = stage + (row >> 7) * A_STAGE_BYTES;
-    const int r = row & 127;
+// Groups 2*hn and 2*hn+1 (low nibbles: hn = 0, the even k-stage of the half; high nibbles: hn = 1, the odd
+// one) of one (row, l range): 32 weights -> o[0..7] = the 16 values of group 2*hn (stage chunks 2*lh,
+// 2*lh + 1), o[8..15] = the 16 of group 2*hn + 1 (chunks 4 + 2*lh, 5 + 2*lh); 8-value chunks as [0 2 1 3 4 6 5 7].
+__device__ __forceinline__ void dn_dequant32(const DnFields &F, int hn, int lh, uint32_t (&o)[16]) {
     const uint32_t ml = hn ? 0x00F000F0u : 0x000F000Fu, mh = hn ? 0x03000300u : 0x00300030u;
-    const uint32_t off = hn ? 0x66006600u : 0x64206420u;
+    const uint32_t off = hn ? 0x66006600u : 0x64206420u; // 1024 + 16*32 | 1024 + 32
     const uint32_t scw = hn ? F.s1 : F.s0;
 #pragma unroll
-    for (int g1 = 0; g1 < 2; g1++) { // gi = 2*hn + g1
-        // scale 2*gi + lh of this half: byte 2*g1 + lh of the word
+    for (int g1 = 0; g1 < 2; g1++) { // group 2*hn + g1
+        // scale 2*(2*hn + g1) + lh of this half: byte 2*g1 + lh of the word
         const int sb = (int)(int8_t)((scw >> (8 * (2 * g1 + lh))) & 0xff);
         const __half2 sc = __float2half2_rn(F.d * (float)sb * (hn ? 0.0625f : 1.0f));
 #pragma unroll
-        for (int m = 0; m < 2; m++) {
-            uint32_t o[4];
-#pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
-                const int j = 2 * m + jj;
-                const uint32_t q = g1 ? F.qb[j] : F.qa[j], hh = F.qh[j];
-                const uint32_t h02 = g1 ? (hh << 2) : (hh << 4), h13 = g1 ? (hh >> 6) : (hh >> 4);
-                const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
-                const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
-                const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
-                const __half2 d13 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v13), *reinterpret_cast<const __half2 *>(&off)), sc);
-                o[2 * jj] = *reinterpret_cast<const uint32_t *>(&d02);
-                o[2 * jj + 1] = *reinterpret_cast<const uint32_t *>(&d13);
-            }
-            *reinterpret_cast<uint4 *>(base + swz_off(r, 4 * g1 + 2 * lh + m)) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int j = 0; j < 4; j++) {
+            const uint32_t q = g1 ? F.qb[j] : F.qa[j], hh = F.qh[j];
+            // the two qh bits of group 2*hn + g1 sit four positions higher for hn = 1, and so does the place they go
+            // to (next to a nibble that stays in the high half of its byte): the shifts are the same, the mask differs
+            const uint32_t h02 = g1 ? (hh << 2) : (hh << 4), h13 = g1 ? (hh >> 6) : (hh >> 4);
+            const uint32_t v02 = (q & ml) | (h02 & mh) | 0x64006400u;
+            const uint32_t v13 = ((q >> 8) & ml) | (h13 & mh) | 0x64006400u;
+            const __half2 d02 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v02), *reinterpret_cast<const __half2 *>(&off)), sc);
+            const __half2 d13 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v13), *reinterpret_cast<const __half2 *>(&off)), sc);
+            o[8 * g1 + 2 * j] = *reinterpret_cast<const uint32_t *>(&d02);
+            o[8 * g1 + 2 * j + 1] = *reinterpret_cast<const uint32_t *>(&d13);
         }
     }
+}
+
+// 8 registers of every lane -> 8 columns of the warp's 32 tensor-memory lanes
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t *r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
 
 __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_constant__ DnParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *a_st = smem, *b_st = smem + DN_NSA * GU_A_STAGE;
+    uint8_t *b_st = smem;
     uint8_t *raw = b_st + DN_NSB * B_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + DN_RAW_BYTES);
-    uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 10, *acc_full = bars + 12, *acc_empty = bars + 13;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw + DN_RAW_SLOTS * P.raw_slot_bytes);
+    uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 10, *raw_full = bars + 12,
+             *raw_empty = bars + 18, *acc_full = bars + 24, *acc_empty = bars + 26;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_tiles = *P.n_tiles;
@@ -992,18 +956,24 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
 
     if (tid == 0) {
         for (int s = 0; s < DN_NSA; s++) {
-            mb_init(&a_full[s], DN_DQ_WARPS);
+            mb_init(&a_full[s], DN_DQ_WARPS / 2); // the eight warps of the stage's nibble half
             mb_init(&a_empty[s], 1);
         }
         for (int s = 0; s < DN_NSB; s++) {
             mb_init(&b_full[s], 1);
             mb_init(&b_empty[s], 1);
         }
-        mb_init(acc_full, 1);
-        mb_init(acc_empty, 4);
+        for (int s = 0; s < DN_RAW_SLOTS; s++) {
+            mb_init(&raw_full[s], 1);
+            mb_init(&raw_empty[s], 4); // the four dequant warps of the run's quadrant
+        }
+        for (int s = 0; s < 2; s++) {
+            mb_init(&acc_full[s], 1);
+            mb_init(&acc_empty[s], 4);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == DN_DQ_WARPS + 1) {
+    if (warp == DN_DQ_WARPS + 2) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -1013,49 +983,76 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < DN_DQ_WARPS) {
-        // ---------------- dequant ----------------
-        const int drow = tid & (2 * MM_M - 1), dlh = tid / (2 * MM_M); // convert step: (row, l half)
-        uint32_t g = 0;
+        // ---------------- dequant: thread = (weight row, 16-wide l range, nibble half) ----------------
+        const int q = warp & 3, lh = (warp >> 2) & 1, hn = warp >> 3;
+        const int r = 32 * q + lane; // row of the tile = tensor-memory lane
+        uint32_t it = 0;
         bool ok = true;
-        // (after a wait timed out the loops still run to their end, without waiting: every warp must
-        // keep meeting the others at the staging barriers)
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
-            const int rows_valid = min(2 * MM_M, P.n_out - m0);
-            const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
-            const uint8_t *rowp = raw + drow * DN_RAWP;
-            DnWin R;
-            dn_load<0>(R, tw, row_bytes, rows_valid, 0, warp, lane);
-            dn_load<1>(R, tw, row_bytes, rows_valid, 0, warp, lane);
-            for (int b = 0; b < n_blk; b++) {
-                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory"); // the previous column's windows are consumed
-                dn_stage(R, raw, warp, lane);
-                // the next column is requested now (first half) and between the two conversions (second half),
-                // and only touched after this one is converted
-                if (b + 1 < n_blk) dn_load<0>(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
-                asm volatile("bar.sync 1, %0;" ::"n"(DN_DQ_WARPS * 32) : "memory");
-                // byte offset of this row's block inside its window
-                const int sh = (int)((reinterpret_cast<uintptr_t>(tw) + (size_t)drow * row_bytes + (size_t)b * Q6K_BYTES) & 15u);
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+            const int m0 = P.tiles[8 * tile + 3];
+            const bool rvalid = m0 + r < P.n_out;
+            const uint32_t c = it * 4u + (uint32_t)q; // sequence number of this quadrant's run
+            const int slot = (int)(c % DN_RAW_SLOTS);
+            ok = mb_wait(&raw_full[slot], (c / DN_RAW_SLOTS) & 1, P.flag, 2);
+            // the row's blocks: 4-byte aligned address below the block start, plus the offset inside it
+            const uint8_t *rowp = raw + (size_t)slot * P.raw_slot_bytes + (size_t)lane * row_bytes;
+            const uint32_t g0 = it * (uint32_t)k_stages; // first k-stage of the tile in the kernel-wide count
+            for (int b = 0; b < n_blk && ok; b++) {
+                const uint8_t *blk = rowp + b * Q6K_BYTES;
+                const uint8_t *base4 = reinterpret_cast<const uint8_t *>(reinterpret_cast<uintptr_t>(blk) & ~(uintptr_t)3);
+                const int sh = (int)(reinterpret_cast<uintptr_t>(blk) & 3u);
 #pragma unroll 1
-                for (int n = 0; n < 2; n++, g += 2) {
-                    DnFields F;
-                    dn_fields(rowp, sh, n, dlh, F);
-                    const int s0 = g % DN_NSA, s1 = (g + 1) % DN_NSA;
-                    ok = ok && mb_wait(&a_empty[s0], ((g / DN_NSA) & 1) ^ 1, P.flag, 3);
-                    dn_dequant_stage(F, 0, a_st + (size_t)s0 * GU_A_STAGE, drow, dlh);
-                    ok = ok && mb_wait(&a_empty[s1], (((g + 1) / DN_NSA) & 1) ^ 1, P.flag, 3);
-                    dn_dequant_stage(F, 1, a_st + (size_t)s1 * GU_A_STAGE, drow, dlh);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mb_arrive(&a_full[s0]);
-                        mb_arrive(&a_full[s1]);
+                for (int n = 0; n < 2; n++) {
+                    uint32_t o[16];
+                    if (rvalid) {
+                        DnFields F;
+                        dn_fields(base4, sh, n, lh, F);
+                        dn_dequant32(F, hn, lh, o);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) o[i] = 0u;
                     }
-                    if (n == 0 && b + 1 < n_blk) dn_load<1>(R, tw, row_bytes, rows_valid, b + 1, warp, lane);
+                    const uint32_t g = g0 + (uint32_t)(4 * b + 2 * n + hn); // this thread's k-stage of the pair
+                    const int sa = (int)(g % DN_NSA);
+                    ok = ok && mb_wait(&a_empty[sa], ((g / DN_NSA) & 1) ^ 1, P.flag, 3);
+                    tc_fence_after();
+                    const uint32_t ta = tmem_base + ((uint32_t)(32 * q) << 16) + DN_A_COL0 + (uint32_t)sa * 32u;
+                    tc_st8(ta + 8u * lh, o);            // group 2*hn: chunks 2*lh, 2*lh + 1
+                    tc_st8(ta + 16u + 8u * lh, o + 8);  // group 2*hn + 1: chunks 4 + 2*lh, 5 + 2*lh
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mb_arrive(&a_full[sa]);
+                }
+            }
+            // the run is consumed: hand its slot back to the loader
+            __syncwarp();
+            if (lane == 0) mb_arrive(&raw_empty[slot]);
+        }
+    } else if (warp == DN_DQ_WARPS) {
+        // ---------------- loader of the quantized runs: one bulk copy per (tile, quadrant) ----------------
+        if (lane == 0) {
+            uint32_t c = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int e = P.tiles[8 * tile], m0 = P.tiles[8 * tile + 3];
+                const uint8_t *tw = P.w + (size_t)e * P.expert_bytes + (size_t)m0 * row_bytes;
+                for (int q = 0; q < 4 && ok; q++, c++) {
+                    const int slot = (int)(c % DN_RAW_SLOTS);
+                    ok = mb_wait(&raw_empty[slot], ((c / DN_RAW_SLOTS) & 1) ^ 1, P.flag, 1);
+                    int rows = P.n_out - m0 - DN_RUN_ROWS * q;
+                    rows = rows < 0 ? 0 : (rows > DN_RUN_ROWS ? DN_RUN_ROWS : rows);
+                    const uint32_t bytes = (uint32_t)(rows * row_bytes); // even row count: a multiple of 16 bytes
+                    if (bytes) {
+                        mb_expect_tx(&raw_full[slot], bytes);
+                        bulk_g2s(raw + (size_t)slot * P.raw_slot_bytes, tw + (size_t)q * DN_RUN_ROWS * row_bytes, bytes, &raw_full[slot]);
+                    } else {
+                        mb_arrive(&raw_full[slot]);
+                    }
                 }
             }
         }
-    } else if (warp == DN_DQ_WARPS) {
+    } else if (warp == DN_DQ_WARPS + 1) {
         // ---------------- B loader ----------------
         if (lane == 0) {
             uint32_t g = 0;
@@ -1063,16 +1060,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int nv = P.tiles[8 * tile + 2], slot = P.tiles[8 * tile + 4];
                 const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
-                {
-                    // the quantized rows of this CTA's next tile are one contiguous range: have L2 fetch it
-                    // now, so the dequant warps' small loads find it there
-                    const int nt = tile + gridDim.x;
-                    if (nt < n_tiles) {
-                        const int ne = P.tiles[8 * nt], nm0 = P.tiles[8 * nt + 3];
-                        const int nrows = min(2 * MM_M, P.n_out - nm0);
-                        bulk_prefetch_l2(P.w + (size_t)ne * P.expert_bytes + (size_t)nm0 * row_bytes, (uint32_t)(nrows * row_bytes) & ~15u);
-                    }
-                }
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % DN_NSB;
                     ok = mb_wait(&b_empty[s], ((g / DN_NSB) & 1) ^ 1, P.flag, 4);
@@ -1081,7 +1068,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp == DN_DQ_WARPS + 1) {
+    } else if (warp == DN_DQ_WARPS + 2) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t g = 0, it = 0;
@@ -1090,84 +1077,70 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 const int nv = P.tiles[8 * tile + 2];
                 const int npad = (nv + 15) & ~15;
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(npad >> 3) << 17) | ((uint32_t)(MM_M >> 4) << 24);
-                ok = mb_wait(acc_empty, (it & 1) ^ 1, P.flag, 5);
+                const uint32_t buf = it & 1;
+                ok = mb_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, P.flag, 5);
                 tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * MM_N;
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                    const int s = g % DN_NSA, sb = g % DN_NSB;
-                    ok = mb_wait(&a_full[s], (g / DN_NSA) & 1, P.flag, 6);
+                    const int sa = g % DN_NSA, sb = g % DN_NSB;
+                    ok = mb_wait(&a_full[sa], (g / DN_NSA) & 1, P.flag, 6);
                     ok = ok && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
                     tc_fence_after();
-                    const uint64_t ad0 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE));
-                    const uint64_t ad1 = umma_desc(s32(a_st + (size_t)s * GU_A_STAGE + A_STAGE_BYTES));
+                    const uint32_t a_tmem = tmem_base + DN_A_COL0 + (uint32_t)sa * 32u;
                     const uint64_t bd = umma_desc(s32(b_st + (size_t)sb * B_STAGE_BYTES));
 #pragma unroll
-                    for (int kk = 0; kk < MM_K / 16; kk++) {
-                        tc_mma_f16(tmem_base, ad0 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                        tc_mma_f16(tmem_base + 256, ad1 + 2 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                    }
-                    tc_commit(&a_empty[s]);
+                    for (int kk = 0; kk < MM_K / 16; kk++)
+                        tc_mma_f16_ts(d_tmem, a_tmem + 8 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                    tc_commit(&a_empty[sa]); // frees both stages when these MMAs have read them
                     tc_commit(&b_empty[sb]);
                 }
-                tc_commit(acc_full);
+                tc_commit(&acc_full[buf]);
             }
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: scaled rows ----------------
-        const int q = warp & 3;
+        // ---------------- epilogue: rows of one accumulator buffer ----------------
+        const int q = warp & 3; // tensor-memory lane quadrant this warp may read
         const int m = 32 * q + lane;
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
             const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
             const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
-            // destination rows and their scales are fetched while the tile is still being multiplied
-            int fids[MM_N / 32];
-            float scs[MM_N / 32];
-#pragma unroll
-            for (int c = 0; c < MM_N / 32; c++) {
-                const int my = 32 * c + lane;
-                fids[c] = my < nv ? list[my] : 0;
-            }
-#pragma unroll
-            for (int c = 0; c < MM_N / 32; c++) scs[c] = (P.row_scale && 32 * c + lane < nv) ? P.row_scale[fids[c]] : 1.0f;
-            ok = mb_wait(acc_full, it & 1, P.flag, 8);
+            const uint32_t buf = it & 1;
+            const int mrow = m0 + m;
+            const bool mvalid = mrow < P.n_out;
+            ok = mb_wait(&acc_full[buf], (it >> 1) & 1, P.flag, 8);
             tc_fence_after();
-            for (int sub = 0; sub < 2; sub++) {
-                const int mrow = m0 + sub * MM_M + m;
-                const bool mvalid = mrow < P.n_out;
+            for (int cb = 0; cb < nv; cb += 32) {
+                uint32_t v[32];
+                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + buf * MM_N + cb, v);
+                if (P.sorted) {
+                    // rows in expert-sorted order, unscaled: consecutive tile columns are consecutive rows
+                    float *dst = P.out + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + mrow;
 #pragma unroll
-                for (int c = 0; c < MM_N / 32; c++) {
-                    const int cb = 32 * c;
-                    if (cb >= nv) break;
-                    uint32_t v[32];
-                    tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + sub * 256 + cb, v);
-                    const int myfid = fids[c];
-                    const float mysc = scs[c];
-                    if (P.sorted) {
-                        // rows in expert-sorted order, unscaled: consecutive tile columns are consecutive rows
-                        float *dst = P.out + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + mrow;
+                    for (int j = 0; j < 32; j++)
+                        if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = __uint_as_float(v[j]);
+                } else {
+                    const int my = cb + lane;
+                    const int myfid = my < nv ? list[my] : 0;
+                    const float mysc = (P.row_scale && my < nv) ? P.row_scale[myfid] : 1.0f;
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = __uint_as_float(v[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int fid = __shfl_sync(0xffffffffu, myfid, j);
-                            const float sc = __shfl_sync(0xffffffffu, mysc, j);
-                            if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + mrow] = __uint_as_float(v[j]) * sc;
-                        }
+                    for (int j = 0; j < 32; j++) {
+                        const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                        const float sc = __shfl_sync(0xffffffffu, mysc, j);
+                        if (cb + j < nv && mvalid) P.out[(size_t)fid * P.n_out + mrow] = __uint_as_float(v[j]) * sc;
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mb_arrive(acc_empty);
+            if (lane == 0) mb_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == DN_DQ_WARPS + 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (warp == DN_DQ_WARPS + 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
 } // namespace
@@ -1317,30 +1290,38 @@ lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_st
     return LMOE_OK;
 }
 
-// The down projection: 256 Q6_K weight rows per CTA, optional per-row scale in the epilogue.
+// The down projection: Q6_K stacks with at most DN_MAX_NB super-blocks per row and an even row count
+// (run copies are multiples of 16 bytes); optional per-row scale in the epilogue.
+bool mm_down_available(const lmoe_expert_stack *down) {
+    return down->dtype == LMOE_Q6_K && down->k / QK_K <= DN_MAX_NB && (down->n_out & 1) == 0 && down->n_expert <= 512;
+}
+
 lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
                            int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, int sorted,
                            void *tiles_ws, uint32_t *flag, cudaStream_t stream) {
-    if (down->dtype != LMOE_Q6_K || (down->k / QK_K) % 2 != 0 || (down->n_out & 1))
-        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the 256-row down kernel needs a Q6_K stack with k %% 512 == 0 and even n_out");
-    if (down->n_expert > 512) return lmoe_fail(LMOE_ERR_UNSUPPORTED, "grouped GEMM supports at most 512 experts");
+    if (!mm_down_available(down))
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the down kernel needs a Q6_K stack with k <= %d, even n_out and at most 512 experts",
+                         DN_MAX_NB * QK_K);
     const int64_t max_tiles = mm_max_tiles(list_rows, down->n_expert, down->n_out);
     int32_t *tiles = static_cast<int32_t *>(tiles_ws);
     int32_t *n_tiles = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(tiles_ws) + lmoe_align_up((size_t)max_tiles * 32, 256));
-    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)down->n_expert, (int)down->n_out, tiles, n_tiles, (int)max_tiles, 2 * MM_M);
+    build_tiles_kernel<<<1, 512, 0, stream>>>(tpe, (int)down->n_expert, (int)down->n_out, tiles, n_tiles, (int)max_tiles, MM_M);
     LMOE_LAUNCH_CHECK("build_tiles_kernel");
     DnParams P;
     P.w = down->blocks(); P.expert_bytes = down->expert_bytes(); P.n_out = (int)down->n_out; P.k = (int)down->k;
     P.xt = static_cast<const uint8_t *>(xt); P.ids_map = ids_map; P.map_stride = (int)map_stride;
     P.tiles = tiles; P.n_tiles = n_tiles; P.row_scale = row_scale; P.out = out; P.sorted = sorted; P.flag = flag;
-    const int smem = DN_NSA * GU_A_STAGE + DN_NSB * B_STAGE_BYTES + DN_RAW_BYTES + 256 + 1024;
-    static thread_local int c_dev = -1, c_sms = 0;
+    // a slot holds 32 rows; re-aligning reads may touch up to 20 bytes past the last block
+    P.raw_slot_bytes = (int)lmoe_align_up((size_t)DN_RUN_ROWS * down->row_bytes() + 32, 128);
+    const int smem = DN_NSB * B_STAGE_BYTES + DN_RAW_SLOTS * P.raw_slot_bytes + 512 + 1024;
+    static thread_local int c_dev = -1, c_sms = 0, c_smem = 0;
     int dev = 0;
     LMOE_CUDA(cudaGetDevice(&dev));
-    if (dev != c_dev) {
+    if (dev != c_dev || smem > c_smem) {
         LMOE_CUDA(cudaDeviceGetAttribute(&c_sms, cudaDevAttrMultiProcessorCount, dev));
         LMOE_CUDA(cudaFuncSetAttribute(mm_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         c_dev = dev;
+        c_smem = smem;
     }
     mm_down_kernel<<<c_sms, DN_THREADS, smem, stream>>>(P);
     LMOE_LAUNCH_CHECK("mm_down_kernel");

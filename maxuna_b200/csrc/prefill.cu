@@ -15,6 +15,7 @@ cudaError_t launch_gather_tiles(const void *x, int x_f16, int x_per_row, int top
 lmoe_status launch_mm_gateup(const lmoe_expert_stack *gate, const lmoe_expert_stack *up, const void *xt,
                              const uint32_t *tpe, const int32_t *ids_map, int64_t map_stride, int64_t list_rows,
                              float *act, int sorted, void *tiles_ws, uint32_t *flag, cudaStream_t stream);
+bool mm_down_available(const lmoe_expert_stack *down);
 lmoe_status launch_mm_down(const lmoe_expert_stack *down, const void *xt, const uint32_t *tpe, const int32_t *ids_map,
                            int64_t map_stride, int64_t list_rows, const float *row_scale, float *out, int sorted,
                            void *tiles_ws, uint32_t *flag, cudaStream_t stream);
@@ -258,7 +259,7 @@ lmoe_status ffn_grouped(const lmoe_expert_stack *gate, const lmoe_expert_stack *
     void *tiles = ws + c.off;
     lmoe_status st;
     const bool fused_gu = gate->dtype == LMOE_Q4_K && up->dtype == LMOE_Q4_K;
-    const bool fused_dn = down->dtype == LMOE_Q6_K && (down->k / 256) % 2 == 0 && (down->n_out & 1) == 0;
+    const bool fused_dn = mm_down_available(down);
     const bool sorted = spos && scale_out && fused_gu && fused_dn;
     if (sorted_used) *sorted_used = sorted;
     if (masked) {
