@@ -257,6 +257,15 @@ lmoe_status lmoe_experts_forward(const lmoe_layer *layer, const float *x, const 
                                  int64_t t, int32_t add_shared, float *out, void *workspace, size_t workspace_bytes,
                                  void *stream);
 
+/* The same for one rank of an expert-parallel decode step (no counterpart in the single-GPU reference): x / ids
+ * / weights cover ALL tokens of the batch, with the slots of experts that live on other ranks set empty; the
+ * replicated shared expert is added only for the tokens [shared_first, shared_first + shared_count), this
+ * rank's own.  out [t, hidden] holds this rank's partial rows; the ranks' rows of a token are summed by its
+ * owner.  A partial shared range needs t < lmoe_mm_id_min_seq(). */
+lmoe_status lmoe_experts_forward_ep(const lmoe_layer *layer, const float *x, const uint32_t *ids, const float *weights,
+                                    int64_t t, int64_t shared_first, int64_t shared_count, float *out, void *workspace,
+                                    size_t workspace_bytes, void *stream);
+
 /* `MoeBlock::forward` on the prefill path (the mm_id branch of src/moe.rs:236-323):
  * route, sort token-slots by expert, grouped GEMM on tensor cores with f16
  * operand tiles dequantized in shared memory and f32 accumulation, SwiGLU in
@@ -324,6 +333,9 @@ lmoe_status lmoe_ep_pack(const float *x, const uint32_t *ids, const float *weigh
                          int64_t top_k, int64_t n_expert, int64_t world, void *rows_f16, uint32_t *local_ids,
                          float *row_weights, int32_t *row_pos, int64_t *send_counts, void *workspace,
                          size_t workspace_bytes, void *stream);
+/* Expert ids of the whole block -> ids relative to the experts [first, first + count) of one rank; every other
+ * id becomes the empty-slot id `count` (what lmoe_experts_forward{,_ep,_tokens_f16} skip).  n = number of ids. */
+lmoe_status lmoe_ep_localize_ids(const uint32_t *ids, int64_t n, int64_t first, int64_t count, uint32_t *out, void *stream);
 /* The return leg: out [t, hidden] = sum over slots, in slot order, of rows[row_pos[token * top_k + slot]]
  * (the weighted expert outputs, back in the order they were sent), then + shared [t, hidden] when non-NULL.
  * A negative row_pos entry is skipped (with the token-level dispatch: top_k = ranks, one slot per rank). */

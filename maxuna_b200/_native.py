@@ -49,11 +49,13 @@ PROTOTYPES = {
     "lmoe_moe_forward_decode": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_workspace_bytes": (c_sz, [c_vp, c_i64]),
     "lmoe_experts_forward": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_experts_forward_ep": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_prefill": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_host": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_forward_rows": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_ep_pack_workspace_bytes": (c_sz, [c_i64, c_i64]),
     "lmoe_ep_pack": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_ep_localize_ids": (c_i32, [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "lmoe_ep_combine": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "lmoe_experts_forward_rows_f16": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_rows_workspace_bytes": (c_sz, [c_vp, c_i64]),

@@ -85,6 +85,8 @@ cudaError_t launch_silu_mul(const float *g, const float *u, int64_t n, float *ou
 cudaError_t launch_combine(const float *down, const float *col_l2, const float *w, int seq, int top_k,
                            int n_out, float *out, cudaStream_t s);
 cudaError_t launch_add_inplace(float *out, const float *b, int64_t n, cudaStream_t s);
+cudaError_t launch_ep_localize_ids(const uint32_t *ids, int64_t n, uint32_t first, uint32_t count, uint32_t *out,
+                                   cudaStream_t s);
 cudaError_t launch_rms_norm(const float *x, const float *w, float eps, int64_t t, int hidden, float *out, cudaStream_t s);
 cudaError_t launch_map0(const uint32_t *ids, int t, int top_k, int n_expert, uint32_t *tpe, int32_t *ids_map,
                         cudaStream_t s);

@@ -89,6 +89,7 @@ struct DecodeParams {
     int t, hidden, ff, n_expert, top_k;
     float scale;
     int norm, has_shared;
+    int sh_t0, sh_nt; // the shared expert serves tokens [sh_t0, sh_t0 + sh_nt) (all of them unless the caller narrows it)
     uint32_t *ctrl;   // workspace: [0..3] device flag (zeroed by the launch with first_launch set)
     uint32_t *sync;   // owned by the layer, zero between launches: [0] grid barrier, [1] exit count, [32..] per-pass counts
     int first_launch;
@@ -261,12 +262,12 @@ __device__ __forceinline__ int find_active(const uint16_t *ppre, int n_active, i
 
 // The tokens pass `q` serves (shared expert: tokens q*NTOK ...; routed: a slice of one expert's list).
 template <int NTOK>
-__device__ __forceinline__ void make_pass(Pass &U, int t, int top_k, const Tables &T, int shared, int q) {
+__device__ __forceinline__ void make_pass(Pass &U, int sh_t0, int sh_nt, int top_k, const Tables &T, int shared, int q) {
     if (shared) {
-        U.n_tok = min(NTOK, t - q * NTOK);
+        U.n_tok = min(NTOK, sh_nt - q * NTOK);
 #pragma unroll
         for (int i = 0; i < NTOK; i++) {
-            U.tok[i] = min(q * NTOK + i, t - 1);
+            U.tok[i] = sh_t0 + min(q * NTOK + i, sh_nt - 1);
             U.pair[i] = U.tok[i] * (top_k + 1) + top_k;
         }
     } else {
@@ -613,7 +614,7 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
     const int nb4 = P.hidden / QK_K, nb6 = P.ff / QK_K;
     const int row4 = nb4 * Q4K_BYTES, row6 = nb6 * Q6K_BYTES;
     const int tiles1 = P.ff / 8, tiles2 = P.hidden / DOWN_ROWS;
-    const int shared_passes = P.has_shared ? (P.t + NTOK - 1) / NTOK : 0;
+    const int shared_passes = P.has_shared ? (P.sh_nt + NTOK - 1) / NTOK : 0;
     const size_t gexp = (size_t)P.ff * row4, dexp = (size_t)P.hidden * row6;
     // Between phases 1 and 2: per-pass completion counters up to 16 tokens (no grid barrier, early passes start
     // early: a few per cent at 4 and 8 tokens), a grid barrier for larger batches.
@@ -718,7 +719,7 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
                 if (u0 >= u1) continue;
                 int q = u0 / tiles, tile = u0 - q * tiles;
                 Pass U;
-                make_pass<NTOK>(U, P.t, K, T, shared, q);
+                make_pass<NTOK>(U, P.sh_t0, P.sh_nt, K, T, shared, q);
                 // Phase 2 of a pass may start, on any CTA, once all its phase-1 units are done: this CTA adds
                 // the number it finished to the pass's counter whenever it leaves a pass.
                 int done_in_pass = 0;
@@ -773,7 +774,7 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
                     if (++tile == tiles && u + 1 < u1) {
                         tile = 0;
                         publish(q);
-                        make_pass<NTOK>(U, P.t, K, T, shared, ++q);
+                        make_pass<NTOK>(U, P.sh_t0, P.sh_nt, K, T, shared, ++q);
                     }
                 }
                 publish(q);
@@ -1097,7 +1098,7 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
             for (int q = u0 / tiles; q * tiles < u1; q++) {
                 const int a = max(u0, q * tiles), b = min(u1, (q + 1) * tiles);
                 Pass U;
-                make_pass<NTOK>(U, P.t, K, T, shared, q);
+                make_pass<NTOK>(U, P.sh_t0, P.sh_nt, K, T, shared, q);
                 // what the cache holds is identified by the rows staged into it
                 unsigned long long key = ((unsigned long long)phase << 60) | ((unsigned long long)U.n_tok << 56);
 #pragma unroll
@@ -1146,10 +1147,10 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
     // ---- phase 3: out[t, :] = sum over slots (then the shared expert) of the weighted partial rows,
     //      in slot order (`combine`, src/ops/combine.metal:70-97, plus `routed + shared`, src/moe.rs:77) ----
     {
-        const int nslot = K + P.has_shared;
         const int h4 = P.hidden / 4;
         for (int i = blockIdx.x * CONS_THREADS + tid; i < P.t * h4; i += G * CONS_THREADS) {
             const int tok = i / h4, c = i - tok * h4;
+            const int nslot = K + (P.has_shared && tok >= P.sh_t0 && tok < P.sh_t0 + P.sh_nt ? 1 : 0);
             const float4 *yp = reinterpret_cast<const float4 *>(P.ypart + (size_t)tok * (K + 1) * P.hidden) + c;
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int sl = 0; sl < nslot; sl++) {
@@ -1211,11 +1212,11 @@ DecVariant make_variant() {
 }
 } // namespace
 
-// ext_ids / ext_w: NULL = route inside the kernel; otherwise the caller's decision [t, top_k] (`with_shared`
-// then says whether the shared expert is added).
+// ext_ids / ext_w: NULL = route inside the kernel; otherwise the caller's decision [t, top_k].  The shared expert is
+// added for the tokens [shared_first, shared_first + shared_count) of this launch (count 0: for none).
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
-                              float *w_out, const uint32_t *ext_ids, const float *ext_w, int with_shared, void *workspace,
-                              size_t workspace_bytes, int first_launch, cudaStream_t stream) {
+                              float *w_out, const uint32_t *ext_ids, const float *ext_w, int shared_first, int shared_count,
+                              void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream) {
     const int H = (int)Ly->hidden, F = (int)Ly->expert_ff, E = (int)Ly->n_expert, K = (int)Ly->top_k;
     if (Ly->gate->dtype != LMOE_Q4_K || Ly->down->dtype != LMOE_Q6_K)
         return lmoe_fail(LMOE_ERR_UNSUPPORTED, "the fused decode kernel is built for Q4_K gate/up and Q6_K down stacks");
@@ -1260,7 +1261,12 @@ lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float
     P.router = Ly->router; P.bias = Ly->bias;
     P.ext_ids = ext_ids; P.ext_w = ext_w;
     P.gate = Ly->gate->blocks(); P.up = Ly->up->blocks(); P.down = Ly->down->blocks();
-    P.has_shared = Ly->sh_gate != nullptr && with_shared;
+    if (shared_first < 0 || shared_count < 0 || shared_first + shared_count > t)
+        return lmoe_fail(LMOE_ERR_INVALID, "shared-expert token range [%d, %d) lies outside the launch's %d tokens", shared_first,
+                         shared_first + shared_count, t);
+    P.has_shared = Ly->sh_gate != nullptr && shared_count > 0;
+    P.sh_t0 = P.has_shared ? shared_first : 0;
+    P.sh_nt = P.has_shared ? shared_count : 0;
     P.sh_gate = P.has_shared ? Ly->sh_gate->blocks() : nullptr;
     P.sh_up = P.has_shared ? Ly->sh_up->blocks() : nullptr;
     P.sh_down = P.has_shared ? Ly->sh_down->blocks() : nullptr;

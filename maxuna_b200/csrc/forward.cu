@@ -7,8 +7,8 @@
 size_t decode_workspace_bytes(int t, int hidden, int ff, int n_expert, int top_k);
 int decode_max_tokens();
 lmoe_status launch_moe_decode(const lmoe_layer *Ly, const float *x, int t, float *out, uint32_t *ids_out,
-                              float *w_out, const uint32_t *ext_ids, const float *ext_w, int with_shared, void *workspace,
-                              size_t workspace_bytes, int first_launch, cudaStream_t stream);
+                              float *w_out, const uint32_t *ext_ids, const float *ext_w, int shared_first, int shared_count,
+                              void *workspace, size_t workspace_bytes, int first_launch, cudaStream_t stream);
 // prefill.cu
 size_t prefill_workspace_bytes(const lmoe_layer *Ly, int64_t t);
 lmoe_status launch_moe_prefill(const lmoe_layer *Ly, const float *x, int64_t t, float *out, uint32_t *ids_out,
@@ -58,8 +58,9 @@ static lmoe_status forward_check(const lmoe_layer *layer, const float *x, int64_
 
 // The mat-vec kernel over any token count, 64 tokens per launch, with the one-call-per-handle guard.
 // ext_ids / ext_w: NULL = route inside the kernel, else the caller's decision [t, top_k].
+// The shared expert is added for tokens [sh_first, sh_first + sh_count) of the call.
 static lmoe_status decode_run(const lmoe_layer *layer, const float *x, int64_t t, float *out, uint32_t *ids_out,
-                              float *weights_out, const uint32_t *ext_ids, const float *ext_w, int with_shared,
+                              float *weights_out, const uint32_t *ext_ids, const float *ext_w, int64_t sh_first, int64_t sh_count,
                               void *workspace, size_t workspace_bytes, cudaStream_t s) {
     // The kernel's CTAs meet through words owned by the layer: a second call may only start once the
     // previous one has finished.  Calls on one stream are ordered; a call on another stream is refused
@@ -78,10 +79,12 @@ static lmoe_status decode_run(const lmoe_layer *layer, const float *x, int64_t t
     const int64_t K = layer->top_k;
     for (int64_t t0 = 0; t0 < t; t0 += step) {
         const int n = (int)(t - t0 < step ? t - t0 : step);
+        // the part of the shared-expert range that falls into this launch
+        const int64_t a = sh_first > t0 ? sh_first : t0, b = sh_first + sh_count < t0 + n ? sh_first + sh_count : t0 + n;
         lmoe_status st = launch_moe_decode(layer, x + t0 * layer->hidden, n, out + t0 * layer->hidden,
                                            ids_out ? ids_out + t0 * K : nullptr, weights_out ? weights_out + t0 * K : nullptr,
-                                           ext_ids ? ext_ids + t0 * K : nullptr, ext_w ? ext_w + t0 * K : nullptr, with_shared,
-                                           workspace, workspace_bytes, t0 == 0, s);
+                                           ext_ids ? ext_ids + t0 * K : nullptr, ext_w ? ext_w + t0 * K : nullptr,
+                                           b > a ? (int)(a - t0) : 0, b > a ? (int)(b - a) : 0, workspace, workspace_bytes, t0 == 0, s);
         if (st) return st;
     }
     if (cudaEventRecord(layer->dec_event, s) == cudaSuccess) {
@@ -100,7 +103,7 @@ extern "C" lmoe_status lmoe_moe_forward_decode(const lmoe_layer *layer, const fl
     lmoe_status st = forward_check(layer, x, t, out);
     if (st) return st;
     if (t == 0) return LMOE_OK;
-    return decode_run(layer, x, t, out, ids_out, weights_out, nullptr, nullptr, 1, workspace, workspace_bytes,
+    return decode_run(layer, x, t, out, ids_out, weights_out, nullptr, nullptr, 0, t, workspace, workspace_bytes,
                       (cudaStream_t)stream);
 }
 
@@ -127,7 +130,33 @@ extern "C" lmoe_status lmoe_experts_forward(const lmoe_layer *layer, const float
                          lmoe_experts_workspace_bytes(layer, t), (long long)t, workspace_bytes);
     if (t >= lmoe_mm_id_min_seq())
         return launch_experts_prefill(layer, x, ids, weights, t, add_shared, out, workspace, workspace_bytes, (cudaStream_t)stream);
-    return decode_run(layer, x, t, out, nullptr, nullptr, ids, weights, add_shared, workspace, workspace_bytes,
+    return decode_run(layer, x, t, out, nullptr, nullptr, ids, weights, 0, add_shared ? t : 0, workspace, workspace_bytes,
+                      (cudaStream_t)stream);
+}
+
+// The expert-parallel decode step of one rank: the routed experts resident here for ALL tokens of the batch
+// (slots of other ranks' experts arrive as empty), the replicated shared expert only for this rank's own tokens.
+extern "C" lmoe_status lmoe_experts_forward_ep(const lmoe_layer *layer, const float *x, const uint32_t *ids,
+                                               const float *weights, int64_t t, int64_t shared_first, int64_t shared_count,
+                                               float *out, void *workspace, size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_check(layer, x, t, out);
+    if (st) return st;
+    if (!ids || !weights) return lmoe_fail(LMOE_ERR_INVALID, "ids/weights is NULL");
+    if (shared_first < 0 || shared_count < 0 || shared_first + shared_count > t)
+        return lmoe_fail(LMOE_ERR_INVALID, "shared-expert token range [%lld, %lld) lies outside the %lld tokens", (long long)shared_first,
+                         (long long)(shared_first + shared_count), (long long)t);
+    if (t == 0) return LMOE_OK;
+    if (t >= lmoe_mm_id_min_seq() && shared_count != 0 && shared_count != t)
+        return lmoe_fail(LMOE_ERR_UNSUPPORTED, "a partial shared-expert range needs the mat-vec path (fewer than %lld tokens)",
+                         (long long)lmoe_mm_id_min_seq());
+    if (!workspace || workspace_bytes < lmoe_experts_workspace_bytes(layer, t))
+        return lmoe_fail(LMOE_ERR_WORKSPACE, "workspace needs %zu bytes for %lld tokens, got %zu",
+                         lmoe_experts_workspace_bytes(layer, t), (long long)t, workspace_bytes);
+    if (t >= lmoe_mm_id_min_seq())
+        return launch_experts_prefill(layer, x, ids, weights, t, shared_count == t, out, workspace, workspace_bytes,
+                                      (cudaStream_t)stream);
+    return decode_run(layer, x, t, out, nullptr, nullptr, ids, weights, shared_first, shared_count, workspace, workspace_bytes,
                       (cudaStream_t)stream);
 }
 

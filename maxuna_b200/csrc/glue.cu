@@ -164,3 +164,20 @@ cudaError_t launch_map0(const uint32_t *ids, int t, int top_k, int n_expert, uin
     map0_kernel<<<n_expert, 256, 0, s>>>(ids, t, top_k, n_expert, tpe, ids_map);
     return cudaGetLastError();
 }
+
+// Expert ids of the whole block -> ids relative to the experts [first, first + count) resident on one rank;
+// every other id (other ranks' experts, or already-empty slots) becomes the empty-slot id `count`.
+__global__ void ep_localize_ids_kernel(const uint32_t *__restrict__ ids, int64_t n, uint32_t first, uint32_t count,
+                                       uint32_t *__restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t e = ids[i] - first; // wraps for ids below `first`
+    out[i] = e < count ? e : count;
+}
+
+cudaError_t launch_ep_localize_ids(const uint32_t *ids, int64_t n, uint32_t first, uint32_t count, uint32_t *out,
+                                   cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    ep_localize_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ids, n, first, count, out);
+    return cudaGetLastError();
+}

@@ -607,6 +607,16 @@ extern "C" lmoe_status lmoe_ep_pack(const float *x, const uint32_t *ids, const f
     return LMOE_OK;
 }
 
+extern "C" lmoe_status lmoe_ep_localize_ids(const uint32_t *ids, int64_t n, int64_t first, int64_t count, uint32_t *out,
+                                            void *stream) {
+    lmoe_clear_error();
+    if (!ids || !out) return lmoe_fail(LMOE_ERR_INVALID, "ep_localize_ids: ids/out is NULL");
+    if (n < 0 || first < 0 || count < 1 || first + count > (int64_t)UINT32_MAX)
+        return lmoe_fail(LMOE_ERR_INVALID, "ep_localize_ids: n >= 0, first >= 0, count >= 1 required");
+    LMOE_CUDA(launch_ep_localize_ids(ids, n, (uint32_t)first, (uint32_t)count, out, (cudaStream_t)stream));
+    return LMOE_OK;
+}
+
 extern "C" lmoe_status lmoe_ep_combine(const float *rows, const int32_t *row_pos, const float *shared, int64_t t,
                                        int64_t top_k, int64_t hidden, float *out, void *stream) {
     lmoe_clear_error();

@@ -243,3 +243,99 @@ def make_gpu_ep_block(full_router, bias, local_block, n_expert, top_k, scale=2.5
                              combine_rows_fn=combine_rows_fn,
                              tokens_fn=local_block.experts_forward_tokens if token_level else None,
                              sum_ranks_fn=sum_ranks_fn if token_level else None)
+
+
+class ExpertParallelDecode:
+    """Expert-parallel batched decode of one MoE layer (BASELINE config 5: 64 sequences over the ranks).
+
+    Rank r owns the routed experts ``[r*E/G, (r+1)*E/G)`` and ``t_loc`` of the ``T = G*t_loc`` tokens; router,
+    bias and shared expert are replicated.  The step is latency-bound, so it uses two fixed-size collectives and
+    no host round trip:
+      1. all-gather of the normed hidden states: every rank sees all T rows;
+      2. every rank routes all T tokens itself (the router is replicated, so the decision is identical on all
+         ranks and bit-identical to the single-GPU one) and keeps the slots of its own experts;
+      3. one launch of the fused mat-vec kernel streams each local expert that any token selected ONCE, for all
+         T tokens, and the shared expert for the rank's own tokens;
+      4. all-to-all of the partial rows ([G, t_loc, H]: chunk s goes to the owner of tokens s); the owner adds
+         the G partial rows of a token in rank order, then the residual.
+    The expert math comes in as callables so that the host logic runs on CPU ranks in the tests:
+      norm_fn(x[t_loc,H]) -> [t_loc,H];  route_fn(x[T,H]) -> (ids[T,K] int32, w[T,K] f32);
+      localize_fn(ids, first, count) -> local ids (empty slot = count);
+      experts_fn(x[T,H], ids_local, w, shared_first, shared_count) -> partial rows [T,H] f32;
+      sum_fn(parts[G*t_loc,H], residual[t_loc,H]) -> [t_loc,H] (rank-order sum + residual).
+    """
+
+    def __init__(self, norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert: int, group=None):
+        self.norm_fn, self.route_fn, self.localize_fn = norm_fn, route_fn, localize_fn
+        self.experts_fn, self.sum_fn = experts_fn, sum_fn
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if n_expert % self.world:
+            raise ValueError(f"n_expert ({n_expert}) must divide over {self.world} ranks")
+        self.e_local = n_expert // self.world
+
+    def forward(self, ffn_inp: torch.Tensor) -> torch.Tensor:
+        """ffn_inp [t_loc, H] (this rank's tokens; t_loc equal on all ranks) -> ffn_inp + block(norm(ffn_inp))."""
+        t_loc, h = ffn_inp.shape
+        g = self.world
+        normed = self.norm_fn(ffn_inp)
+        x_all = torch.empty(g * t_loc, h, dtype=normed.dtype, device=normed.device)
+        dist.all_gather_into_tensor(x_all, normed.contiguous(), group=self.group)
+        ids, w = self.route_fn(x_all)
+        ids_local = self.localize_fn(ids, self.rank * self.e_local, self.e_local)
+        part = self.experts_fn(x_all, ids_local, w, self.rank * t_loc, t_loc)
+        recv = torch.empty_like(part)
+        dist.all_to_all_single(recv, part.contiguous(), group=self.group)
+        return self.sum_fn(recv, ffn_inp)
+
+
+def make_gpu_ep_decode(router, bias, norm_weight, local_block, n_expert, top_k, scale=2.5, norm=True, eps=1e-6,
+                       group=None):
+    """Bind `ExpertParallelDecode` to the CUDA entry points of a local `MoeBlock` shard (`MoeBlock.shard`):
+    `lmoe_rms_norm`, `lmoe_route` on the full replicated router, `lmoe_ep_localize_ids`,
+    `lmoe_experts_forward_ep`, `lmoe_ep_combine`."""
+    from . import ops
+    from ._native import check, lib
+    from .gguf import stream_ptr
+
+    world = dist.get_world_size(group)
+    state = {}
+
+    def norm_fn(x):
+        out = torch.empty_like(x)
+        check(lib().lmoe_rms_norm(x.data_ptr(), norm_weight.data_ptr(), eps, x.shape[0], x.shape[1], out.data_ptr(), stream_ptr()))
+        return out
+
+    def route_fn(x_all):
+        return ops.route(router, bias, x_all, top_k, scale, norm)
+
+    def localize_fn(ids, first, count):
+        out = torch.empty_like(ids)
+        check(lib().lmoe_ep_localize_ids(ids.data_ptr(), ids.numel(), first, count, out.data_ptr(), stream_ptr()))
+        return out
+
+    def experts_fn(x_all, ids_local, w, sh_first, sh_count):
+        t = x_all.shape[0]
+        out = torch.empty(t, x_all.shape[1], dtype=torch.float32, device=x_all.device)
+        n = lib().lmoe_experts_workspace_bytes(local_block.handle, t)
+        if state.get("ws") is None or state["ws"].numel() < n:
+            state["ws"] = torch.empty(n, dtype=torch.uint8, device=x_all.device)
+        check(lib().lmoe_experts_forward_ep(local_block.handle, x_all.data_ptr(), ids_local.data_ptr(), w.data_ptr(), t,
+                                            sh_first, sh_count, out.data_ptr(), state["ws"].data_ptr(), state["ws"].numel(),
+                                            stream_ptr()))
+        return out
+
+    def sum_fn(parts, residual):
+        t_loc, h = residual.shape
+        key = (t_loc, str(parts.device))
+        if state.get("pos_key") != key:
+            # row of rank s's partial for token i inside the received buffer: s * t_loc + i
+            state["pos"] = (torch.arange(world, dtype=torch.int32, device=parts.device)[None, :] * t_loc +
+                            torch.arange(t_loc, dtype=torch.int32, device=parts.device)[:, None]).contiguous()
+            state["pos_key"] = key
+        out = torch.empty(t_loc, h, dtype=torch.float32, device=parts.device)
+        check(lib().lmoe_ep_combine(parts.data_ptr(), state["pos"].data_ptr(), residual.data_ptr(), t_loc, world, h,
+                                    out.data_ptr(), stream_ptr()))
+        return out
+
+    return ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert, group)

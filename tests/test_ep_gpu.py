@@ -10,6 +10,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    return torch.device("cuda:0")
+
+
 def test_rows_entry_points_single_gpu(orc):
     from maxuna_b200.moe import MoeBlock
 
@@ -182,3 +188,114 @@ def test_expert_parallel_two_gpus(token_level):
     for rank, err, stats, pairs in res:
         assert err < 1e-5, (rank, err)  # same f16 operands; the token-level sum is grouped by rank (f32 rounding)
         assert stats["rows_sent"] == (pairs if token_level else 96 * 3)
+
+
+# ---- expert-parallel batched decode (BASELINE config 5) ------------------------------------------------------
+@pytest.mark.parametrize("world,t_loc", [(2, 8), (4, 4), (8, 8)])
+def test_ep_decode_ranks_emulated_on_one_gpu(orc, dev, world, t_loc):
+    """The per-rank pieces of the expert-parallel decode step, with the ranks run one after the other on one
+    GPU (no collective: the gathered batch and the returned partial rows are plain slices): routing of all
+    tokens, id localisation, `lmoe_experts_forward_ep` on every shard with the shared expert for the shard's
+    own tokens, rank-order sum + residual.  Against the oracle on the whole batch; ids bit for bit."""
+    from maxuna_b200 import ops
+    from maxuna_b200._native import check, lib
+    from maxuna_b200.gguf import stream_ptr
+    from maxuna_b200.moe import MoeBlock
+
+    hidden, ne, k = 512, 32, 4      # every shard keeps at least top_k experts, so its handle has the block's top_k
+    full = MoeBlock.random(hidden, 512, ne, k, seed=71, device=dev, weight_std=0.2)
+    host = full.host_layer(orc)
+    t = world * t_loc
+    rng = np.random.default_rng(72)
+    ffn_inp = (rng.standard_normal((t, hidden)) * 2).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, hidden).astype(np.float32)
+    inp = torch.from_numpy(ffn_inp).to(dev)
+    gw = torch.from_numpy(g).to(dev)
+    normed = torch.empty_like(inp)
+    check(lib().lmoe_rms_norm(inp.data_ptr(), gw.data_ptr(), 1e-6, t, hidden, normed.data_ptr(), stream_ptr()))
+    ids, w = ops.route(full.router, full.exp_probs_b, normed, k, 2.5, True)
+    e_local = ne // world
+    parts = []
+    for r in range(world):
+        shard = full.shard(r, world)
+        lids = torch.empty_like(ids)
+        check(lib().lmoe_ep_localize_ids(ids.data_ptr(), ids.numel(), r * e_local, e_local, lids.data_ptr(), stream_ptr()))
+        want_l = torch.where((ids // e_local) == r, ids - r * e_local, e_local)
+        assert torch.equal(lids, want_l.to(torch.int32))
+        part = torch.empty(t, hidden, device=dev)
+        n = lib().lmoe_experts_workspace_bytes(shard.handle, t)
+        ws = torch.full((n,), 0xFF, dtype=torch.uint8, device=dev)
+        check(lib().lmoe_experts_forward_ep(shard.handle, normed.data_ptr(), lids.data_ptr(), w.data_ptr(), t, r * t_loc, t_loc,
+                                            part.data_ptr(), ws.data_ptr(), n, stream_ptr()))
+        torch.cuda.synchronize()
+        check(lib().lmoe_check_device_flag(ws.data_ptr(), stream_ptr()))
+        parts.append(part)
+    out = torch.empty(t, hidden, device=dev)
+    pos = (torch.arange(world, dtype=torch.int32, device=dev)[None, :] * t_loc +
+           torch.arange(t_loc, dtype=torch.int32, device=dev)[:, None]).contiguous()
+    for s_ in range(world):       # what rank s receives: chunk s of every rank's partial rows
+        recv = torch.cat([p[s_ * t_loc:(s_ + 1) * t_loc] for p in parts]).contiguous()
+        res = inp[s_ * t_loc:(s_ + 1) * t_loc].contiguous()
+        o = torch.empty(t_loc, hidden, device=dev)
+        check(lib().lmoe_ep_combine(recv.data_ptr(), pos.data_ptr(), res.data_ptr(), t_loc, world, hidden, o.data_ptr(), stream_ptr()))
+        out[s_ * t_loc:(s_ + 1) * t_loc] = o
+    torch.cuda.synchronize()
+    ffn_out, ids_o, _ = host.forward(orc.rms_norm(ffn_inp, g, 1e-6))
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
+    assert orc.rel_l2(out.cpu().numpy(), ffn_inp + ffn_out) < 2e-3
+    # and against the single-GPU layer entry: the same kernels, sums grouped by rank instead of by slot
+    single = full.layer_forward(inp, gw, 1e-6)
+    torch.cuda.synchronize()
+    assert float((out - single).norm() / single.norm()) < 1e-5
+
+
+def _ep_decode_worker(rank, world, port, q):
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+
+    from maxuna_b200.ep import make_gpu_ep_decode
+    from maxuna_b200.moe import MoeBlock
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    n_layers, t_loc, hidden = 3, 32, 512
+    fulls = [MoeBlock.random(hidden, 512, 16, 4, seed=81 + i, device=dev, weight_std=0.2) for i in range(n_layers)]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    norms = [0.5 + torch.rand(hidden, generator=gen, device=dev) for _ in fulls]
+    steps = [make_gpu_ep_decode(f.router, f.exp_probs_b, nw, f.shard(rank, world), 16, 4) for f, nw in zip(fulls, norms)]
+    x_all = torch.randn(world * t_loc, hidden, generator=gen, device=dev)
+    x = x_all[rank * t_loc:(rank + 1) * t_loc].contiguous()
+    ref = x.clone()
+    for step, f, nw in zip(steps, fulls, norms):
+        x = step.forward(x)
+        ref = f.layer_forward(ref, nw, 1e-6)
+    torch.cuda.synchronize()
+    q.put((rank, float((x - ref).norm() / ref.norm())))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_decode_two_gpus():
+    """A three-layer residual stack, 64 sequences over two ranks, against the single-GPU layer entry."""
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ep_decode_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err in res:
+        assert err < 1e-5, (rank, err)
