@@ -248,7 +248,7 @@ def prefill_parity(blk, x, out, ids, n_sample, seed):
             "near_ties_lt_1e-6": int(np.count_nonzero(part[:, K - 1] - part[:, K] < 1e-6)), "of_tokens": int(t)}
 
 
-def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=True):
+def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=True, ep_mode="dense", ep_waves=0):
     """Prefill of one MoE layer: N=1 -> config 3 (4096 tokens, Zipf-skewed routing, one GPU), plus the
     16384-token single-GPU run that anchors the expert-parallel scaling curve; N>1 -> config 4 (16384 tokens
     split over the ranks, experts sharded 256/N per GPU, all-to-all dispatch / combine), uniform and Zipf.
@@ -257,7 +257,7 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=Tru
     import torch.distributed as dist
 
     from maxuna_b200 import _native
-    from maxuna_b200.ep import make_gpu_ep_block
+    from maxuna_b200.ep import make_gpu_ep_block, make_gpu_ep_prefill
     from maxuna_b200.moe import MoeBlock
 
     lib = _native.lib()
@@ -287,11 +287,16 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=Tru
             ep = None
             entry["path"] = "lmoe_moe_forward_prefill: router, expert-sorted gather, tcgen05 grouped GEMMs, slot-order sum"
         else:
-            ep = make_gpu_ep_block(blk.router, blk.exp_probs_b, blk.shard(rank, world), E, K)
+            if ep_mode == "tokens":
+                ep = make_gpu_ep_block(blk.router, blk.exp_probs_b, blk.shard(rank, world), E, K)
+                entry["path"] = "expert parallel, compacted token-level exchange (ExpertParallelMoe: counts on the host)"
+            else:
+                ep = make_gpu_ep_prefill(blk.router, blk.exp_probs_b, blk.shard(rank, world), E, K, waves=ep_waves)
+                entry["path"] = ("expert parallel, fixed-size exchange (ExpertParallelPrefill: all-gather of f16 rows, "
+                                 "all-to-all of f32 partial rows, waves overlapped with the grouped GEMMs)")
 
             def run():
                 out.copy_(ep.forward(x))
-            entry["path"] = "expert parallel, token-level exchange (maxuna_b200/ep.py)"
         ms = _time_gpu(run, steps, warmup, world, dev)
         flops = t_case * (K + 1) * 18874368
         entry.update({"ms": ms, "tflops": flops / ms / 1e9, "tok_per_s": t_case / ms * 1e3})
@@ -351,60 +356,128 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=Tru
     return res
 
 
-def measure_stack(dev, n_layers, steps=3, warmup=3):
-    """The expert portion of a Laguna-shaped model on ONE GPU (config 5 is quoted on 8 GPUs; 48 layers are
-    75.5 GB and fit one B200): a residual stack of `n_layers` MoE layers, x <- x + block_l(rms_norm_l(x)),
-    through `lmoe_moe_layer_forward`.  Batched decode of 64 sequences (one token each) and a 2048-token
-    prefill; for the 64-token step the grouped-GEMM path (what the reference's `seq >= 32` rule would pick) is
-    timed beside the mat-vec kernel that the layer entry uses up to 64 tokens."""
+def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
+    """The expert portion of a Laguna-shaped model (BASELINE config 5): a residual stack of `n_layers` MoE
+    layers, x <- x + block_l(rms_norm_l(x)); batched decode of 64 sequences (one token each) and a 2048-token
+    prefill.
+    One GPU: every layer whole on the device (48 layers are 75.5 GB and fit one B200), through
+    `lmoe_moe_layer_forward`; for the 64-token step the grouped-GEMM path (what the reference's `seq >= 32` rule
+    would pick) is timed beside the mat-vec kernel.
+    N GPUs: expert parallel - rank r holds experts [r*256/N, (r+1)*256/N) of every layer (router, bias, norm and
+    shared expert replicated) and 64/N sequences / 2048/N prefill tokens; decode through
+    `ExpertParallelDecode` (all-gather, one fused mat-vec launch per layer, all-to-all of the partial rows),
+    prefill through `ExpertParallelPrefill` (the same exchange around the grouped GEMMs).  A two-layer copy of the stack that every
+    rank also holds whole gives the parity figure (expert-parallel result against the single-GPU layer entry)."""
     import torch
+    import torch.distributed as dist
 
     from maxuna_b200 import _native
+    from maxuna_b200.ep import make_gpu_ep_decode, make_gpu_ep_prefill
+    from maxuna_b200.gguf import Q4_K, Q6_K, ExpertStack
     from maxuna_b200.moe import MoeBlock
 
     lib = _native.lib()
-    layers = [MoeBlock.random(H, F, E, K, seed=7000 + i, device=dev) for i in range(n_layers)]
     gen = torch.Generator(device=dev)
     gen.manual_seed(5)
-    norms = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in layers]
-    need = max(lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 2048), lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 64))
-    ws = torch.zeros(need, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    res = {"layers": n_layers, "weights_gb": n_layers * ((E + 1) * EXPERT_BYTES + ROUTER_BYTES) / 1e9}
+    res = {"layers": n_layers, "n_gpus": world,
+           "weights_gb_per_gpu": n_layers * ((E // world + 1) * EXPERT_BYTES + ROUTER_BYTES) / 1e9}
 
-    def layer_path(x, bufs):
-        for i, ly in enumerate(layers):
-            a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
-            src = x if i == 0 else a
-            _native.check(lib.lmoe_moe_layer_forward(ly.handle, src.data_ptr(), norms[i].data_ptr(), 1e-6, x.shape[0],
-                                                     b.data_ptr(), None, None, ws.data_ptr(), ws.numel(), stream))
+    def timed(fn, tokens):
+        ms = _time_gpu(fn, steps, warmup, world, dev)
+        return {"tokens": tokens, "ms_per_pass": ms, "tok_per_s": tokens / ms * 1e3, "us_per_layer": ms * 1e3 / n_layers}
 
-    def gemm_path(x, bufs, normed):
-        t = x.shape[0]
-        for i, ly in enumerate(layers):
-            a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
-            src = x if i == 0 else a
-            _native.check(lib.lmoe_rms_norm(src.data_ptr(), norms[i].data_ptr(), 1e-6, t, H, normed.data_ptr(), stream))
-            _native.check(lib.lmoe_moe_forward_prefill(ly.handle, normed.data_ptr(), t, b.data_ptr(), None, None,
-                                                      ws.data_ptr(), ws.numel(), stream))
-            b.add_(src)
+    if world == 1:
+        layers = [MoeBlock.random(H, F, E, K, seed=7000 + i, device=dev) for i in range(n_layers)]
+        norms = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in layers]
+        need = max(lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 2048), lib.lmoe_moe_layer_workspace_bytes(layers[0].handle, 64))
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)
 
-    for name, t, fn in (("decode64", 64, layer_path), ("decode64_grouped_gemm", 64, gemm_path),
-                        ("prefill2048", 2048, layer_path)):
-        x = torch.randn(t, H, generator=gen, device=dev)
-        bufs = [torch.empty(t, H, device=dev), torch.empty(t, H, device=dev)]
-        extra = (torch.empty(t, H, device=dev),) if fn is gemm_path else ()
-        for _ in range(warmup):
-            fn(x, bufs, *extra)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn(x, bufs, *extra)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        res[name] = {"tokens": t, "ms_per_pass": ms, "tok_per_s": t / ms * 1e3, "us_per_layer": ms * 1e3 / n_layers}
+        def layer_path(x, bufs):
+            for i, ly in enumerate(layers):
+                a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
+                src = x if i == 0 else a
+                _native.check(lib.lmoe_moe_layer_forward(ly.handle, src.data_ptr(), norms[i].data_ptr(), 1e-6, x.shape[0],
+                                                         b.data_ptr(), None, None, ws.data_ptr(), ws.numel(), stream))
+
+        def gemm_path(x, bufs, normed):
+            t = x.shape[0]
+            for i, ly in enumerate(layers):
+                a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
+                src = x if i == 0 else a
+                _native.check(lib.lmoe_rms_norm(src.data_ptr(), norms[i].data_ptr(), 1e-6, t, H, normed.data_ptr(), stream))
+                _native.check(lib.lmoe_moe_forward_prefill(ly.handle, normed.data_ptr(), t, b.data_ptr(), None, None,
+                                                          ws.data_ptr(), ws.numel(), stream))
+                b.add_(src)
+
+        for name, t, fn in (("decode64", 64, layer_path), ("decode64_grouped_gemm", 64, gemm_path),
+                            ("prefill2048", 2048, layer_path)):
+            x = torch.randn(t, H, generator=gen, device=dev)
+            bufs = [torch.empty(t, H, device=dev), torch.empty(t, H, device=dev)]
+            extra = (torch.empty(t, H, device=dev),) if fn is gemm_path else ()
+            res[name] = timed(lambda: fn(x, bufs, *extra), t)
+        return res
+
+    # ---- expert parallel ----
+    n_loc = E // world
+
+    def shard_layer(i):
+        """This rank's part of layer i: replicated router / bias / shared expert (same seed on every rank), own experts."""
+        g = torch.Generator(device=dev)
+        g.manual_seed(7000 + i)
+        router = torch.randn(E, H, generator=g, device=dev) * 0.02
+        bias = torch.rand(E, generator=g, device=dev) * 0.2 - 0.1
+        mk = lambda dt, ne, no, k, sd: ExpertStack.random(dt, ne, no, k, std=0.02, seed=sd, device=dev)
+        base = (7000 + i) * 100
+        blk = MoeBlock(router[rank * n_loc:(rank + 1) * n_loc], None, mk(Q4_K, n_loc, F, H, base + 10 * rank + 1),
+                       mk(Q4_K, n_loc, F, H, base + 10 * rank + 2), mk(Q6_K, n_loc, H, F, base + 10 * rank + 3),
+                       mk(Q4_K, 1, F, H, base + 94), mk(Q4_K, 1, F, H, base + 95), mk(Q6_K, 1, H, F, base + 96), K)
+        return router, bias, blk
+
+    parts = [shard_layer(i) for i in range(n_layers)]
+    norms = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in parts]
+    dec = [make_gpu_ep_decode(r, b, nw, blk, E, K) for (r, b, blk), nw in zip(parts, norms)]
+    pre = [make_gpu_ep_prefill(r, b, blk, E, K) for (r, b, blk) in parts]
+
+    t_loc = 64 // world
+    xg = torch.Generator(device=dev)
+    xg.manual_seed(50 + rank)
+    x64 = torch.randn(t_loc, H, generator=xg, device=dev)
+
+    def decode_pass():
+        x = x64
+        for step in dec:
+            x = step.forward(x)
+        return x
+
+    res["decode64"] = timed(decode_pass, 64)
+    p_loc = 2048 // world
+    x2k = torch.randn(p_loc, H, generator=xg, device=dev)
+    normed = torch.empty_like(x2k)
+
+    def prefill_pass():
+        x = x2k
+        for ep, nw in zip(pre, norms):
+            _native.check(lib.lmoe_rms_norm(x.data_ptr(), nw.data_ptr(), 1e-6, p_loc, H, normed.data_ptr(), stream))
+            x = ep.forward(normed) + x
+        return x
+
+    res["prefill2048"] = timed(prefill_pass, 2048)
+    del parts, dec, pre
+    torch.cuda.empty_cache()
+    # ---- parity: two layers that every rank also holds whole ----
+    fulls = [MoeBlock.random(H, F, E, K, seed=7100 + i, device=dev) for i in range(2)]
+    pn = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in fulls]
+    steps_p = [make_gpu_ep_decode(f.router, f.exp_probs_b, nw, f.shard(rank, world), E, K) for f, nw in zip(fulls, pn)]
+    x, ref = x64, x64
+    for step, f, nw in zip(steps_p, fulls, pn):
+        x = step.forward(x)
+        ref = f.layer_forward(ref, nw, 1e-6)
+    torch.cuda.synchronize()
+    tt = torch.tensor([float((x - ref).norm() / ref.norm())], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    res["parity"] = {"tokens": 64, "layers": 2, "rel_l2": float(tt[0]),
+                     "against": "the single-GPU layer entry on the same tokens and weights, max over ranks"}
     return res
 
 
@@ -420,7 +493,12 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="profiling aid: run only the prefill measurement and print it")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="profiling aid: token count of the prefill measurement")
     ap.add_argument("--stack-layers", type=int, default=0,
-                    help="run only the residual stack of this many MoE layers on one GPU (48 = the model's expert portion) and print it")
+                    help="run only the residual stack of this many MoE layers (48 = the model's expert portion; expert "
+                         "parallel under torchrun) and print it")
+    ap.add_argument("--ep-mode", default="dense", choices=["dense", "tokens"],
+                    help="expert-parallel prefill exchange: fixed-size (all-gather / all-to-all) or compacted token lists")
+    ap.add_argument("--ep-waves", type=int, default=0, help="waves of the fixed-size exchange (0 = by size)")
+    ap.add_argument("--no-stack", action="store_true", help="skip the config-5 stack measurement of the default run")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -448,14 +526,15 @@ def main():
 
     _native.lib()
     if args.stack_layers > 0:
+        st = measure_stack(dev, rank, world, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 3))
         if rank == 0:
-            print(json.dumps({"stack": measure_stack(dev, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=args.warmup)}))
+            print(json.dumps({"stack": st}))
         if world > 1:
             dist.destroy_process_group()
         return
     if args.prefill_only:
         res = measure_prefill(dev, rank, world, steps=max(1, min(args.steps, 8)), warmup=args.warmup,
-                              tokens=args.prefill_tokens or None)
+                              tokens=args.prefill_tokens or None, ep_mode=args.ep_mode, ep_waves=args.ep_waves)
         if rank == 0:
             print(json.dumps({"prefill_only": res}))
         if world > 1:
@@ -608,13 +687,21 @@ def main():
     if not args.no_prefill:
         del layers, ws
         torch.cuda.empty_cache()
-        prefill = measure_prefill(dev, rank, world, tokens=args.prefill_tokens or None)
+        prefill = measure_prefill(dev, rank, world, tokens=args.prefill_tokens or None, ep_mode=args.ep_mode, ep_waves=args.ep_waves)
+
+    stack = None
+    if not args.no_stack:
+        # config 5: all 48 layers; expert parallel under torchrun, whole on the device on one GPU (75.5 GB)
+        if prefill is None:
+            del layers, ws
+        torch.cuda.empty_cache()
+        stack = measure_stack(dev, rank, world, 48, steps=3, warmup=3)
 
     if rank == 0:
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K x s8 digits (3 per activation, 21 bits) -> s32 -> f32",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "q4_K/q6_K (u8 fields) x s8 activation digits (3 digits = 21 bits up to 8 tokens, 2 digits = 15 bits beyond) -> s32 -> f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "hidden": H, "expert_ff": F, "n_expert": E, "top_k": K, "shared_expert": True,
@@ -651,6 +738,11 @@ def main():
                 "peak_tflops": peaks.get("bf16_tflops"), "results": prefill,
                 "frac_of_peak": {k: v["tflops"] / (peaks.get("bf16_tflops") * world) for k, v in prefill.items()},
             }
+        if stack is not None:
+            stack["workload"] = ("config5: residual stack of MoE layers, 64-sequence batched decode and 2048-token prefill" +
+                                 (f", expert parallel over {world} GPUs" if world > 1 else
+                                  ", one GPU (all 48 layers resident: 75.5 GB)"))
+            line["stack"] = stack
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -339,3 +339,122 @@ def make_gpu_ep_decode(router, bias, norm_weight, local_block, n_expert, top_k, 
         return out
 
     return ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert, group)
+
+
+class ExpertParallelPrefill:
+    """Expert-parallel prefill of one MoE layer without any host round trip (BASELINE config 4).
+
+    Rank r owns experts ``[r*E/G, (r+1)*E/G)`` and ``t_loc`` tokens (the same count on every rank).  Instead of
+    compacting per-destination token lists - which needs the counts on the host before the payload exchange can
+    be sized - every rank receives every token: fixed-size collectives, sized by the shapes alone.
+      1. route the rank's own tokens (replicated router: ids identical to the single-GPU result);
+      2. all-gather of the f16 activations and of the (id, weight) words, in `waves` slices of the local tokens;
+      3. per wave: localise the ids (other ranks' experts -> empty slot) and run the token-level grouped GEMMs
+         over all G*n tokens of the wave: a token without a local expert costs nothing but a zero output row;
+      4. per wave: all-to-all of the partial rows ([G, n, H] f32: chunk s belongs to rank s's tokens);
+      5. the owner adds the G partial rows of a token in rank order, then the shared expert, which ran on a side
+         stream meanwhile.
+    The collectives of wave i+1 (gather) and i-1 (return) run on the communicator's stream while wave i
+    multiplies.  Callables as in `ExpertParallelMoe` / `ExpertParallelDecode`:
+      route_fn(x) -> (ids, w);  localize_fn(ids, first, count);  tokens_fn(x16[N,H], ids_local[N,K], w[N,K]) -> [N,H] f32;
+      shared_fn(x) -> [t_loc,H] or None;  sum_fn(parts[G*n,H], shared_or_None[n,H]) -> [n,H].
+    """
+
+    def __init__(self, route_fn, localize_fn, tokens_fn, shared_fn, sum_fn, n_expert: int, top_k: int, group=None,
+                 payload_dtype=torch.float16, waves: int = 0):
+        self.route_fn, self.localize_fn, self.tokens_fn = route_fn, localize_fn, tokens_fn
+        self.shared_fn, self.sum_fn = shared_fn, sum_fn
+        self.n_expert, self.top_k, self.group = n_expert, top_k, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if n_expert % self.world:
+            raise ValueError(f"n_expert ({n_expert}) must divide over {self.world} ranks")
+        self.e_local = n_expert // self.world
+        self.payload_dtype = payload_dtype
+        self.waves = waves
+        self._side = None
+        self.last_stats = {}
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        t_loc, h = x.shape
+        g, k, dev = self.world, self.top_k, x.device
+        # by default: one wave for small inputs, else as many as ranks up to four (with few ranks the local
+        # experts' weights are large, and every wave streams them again)
+        n_waves = self.waves if self.waves > 0 else (1 if t_loc < 2048 else min(4, g))
+        n_waves = max(1, min(n_waves, t_loc))
+        ids, w = self.route_fn(x)
+        shared = None
+        if self.shared_fn is not None:
+            if x.is_cuda:
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=dev)
+                self._side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(self._side):
+                    shared = self.shared_fn(x)
+            else:
+                shared = self.shared_fn(x)
+        x16 = x.to(self.payload_dtype)
+        meta = torch.cat([ids.view(torch.int32), w.contiguous().view(torch.int32)], dim=1).contiguous()  # [t_loc, 2K] words
+        bounds = [(t_loc * i // n_waves, t_loc * (i + 1) // n_waves) for i in range(n_waves)]
+        gathers = []
+        for a, b in bounds:                                # all gathers are queued at once: they run back to back
+            n = b - a
+            xa = torch.empty(g * n, h, dtype=x16.dtype, device=dev)
+            ma = torch.empty(g * n, 2 * k, dtype=torch.int32, device=dev)
+            h1 = dist.all_gather_into_tensor(xa, x16[a:b].contiguous(), group=self.group, async_op=True)
+            h2 = dist.all_gather_into_tensor(ma, meta[a:b].contiguous(), group=self.group, async_op=True)
+            gathers.append((xa, ma, h1, h2))
+        returns = []
+        for (a, b), (xa, ma, h1, h2) in zip(bounds, gathers):
+            h1.wait()
+            h2.wait()
+            ids_all = ma[:, :k].contiguous()
+            w_all = ma[:, k:].contiguous().view(torch.float32)
+            part = self.tokens_fn(xa, self.localize_fn(ids_all, self.rank * self.e_local, self.e_local), w_all)
+            recv = torch.empty_like(part)
+            hr = dist.all_to_all_single(recv, part, group=self.group, async_op=True)
+            returns.append((recv, hr, part))
+        if shared is not None and x.is_cuda:
+            torch.cuda.current_stream(dev).wait_stream(self._side)
+        out = torch.empty(t_loc, h, dtype=torch.float32, device=dev)
+        for (a, b), (recv, hr, _) in zip(bounds, returns):
+            hr.wait()
+            out[a:b] = self.sum_fn(recv, None if shared is None else shared[a:b])
+        self.last_stats = {"waves": n_waves, "tokens_gathered": g * t_loc, "rows_returned": (g - 1) * t_loc}
+        return out
+
+
+def make_gpu_ep_prefill(full_router, bias, local_block, n_expert, top_k, scale=2.5, norm=True, group=None, waves=0):
+    """Bind `ExpertParallelPrefill` to the CUDA entry points of a local `MoeBlock` shard: `lmoe_route`,
+    `lmoe_ep_localize_ids`, `lmoe_experts_forward_tokens_f16`, `lmoe_shared_forward`, `lmoe_ep_combine`."""
+    from . import ops
+    from ._native import check, lib
+    from .gguf import stream_ptr
+
+    world = dist.get_world_size(group)
+    state = {}
+
+    def route_fn(x):
+        return ops.route(full_router, bias, x, top_k, scale, norm)
+
+    def localize_fn(ids, first, count):
+        out = torch.empty_like(ids)
+        check(lib().lmoe_ep_localize_ids(ids.data_ptr(), ids.numel(), first, count, out.data_ptr(), stream_ptr()))
+        return out
+
+    def sum_fn(parts, shared):
+        n = parts.shape[0] // world
+        hdim = parts.shape[1]
+        key = (n, str(parts.device))
+        if state.get("pos_key") != key:
+            state["pos"] = (torch.arange(world, dtype=torch.int32, device=parts.device)[None, :] * n +
+                            torch.arange(n, dtype=torch.int32, device=parts.device)[:, None]).contiguous()
+            state["pos_key"] = key
+        out = torch.empty(n, hdim, dtype=torch.float32, device=parts.device)
+        sh = None if shared is None else shared.contiguous()
+        check(lib().lmoe_ep_combine(parts.data_ptr(), state["pos"].data_ptr(), None if sh is None else sh.data_ptr(), n, world,
+                                    hdim, out.data_ptr(), stream_ptr()))
+        return out
+
+    return ExpertParallelPrefill(route_fn, localize_fn, local_block.experts_forward_tokens,
+                                 local_block.shared_forward if local_block.shared is not None else None, sum_fn,
+                                 n_expert, top_k, group, waves=waves)

@@ -114,3 +114,72 @@ def test_expert_parallel_cpu_ranks(orc, token_level, world):
         assert err < 1e-5, (rank, err)
         assert ok_sorted
         assert stats["rows_sent"] == (n_pairs if token_level else (5 + 3 * rank) * 3)
+
+
+def _prefill_worker(rank, world, port, q, waves):
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from maxuna_b200.ep import ExpertParallelPrefill
+    from oracle import oracle as orc
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    L = _layer(orc)
+    ne_local = L.n_expert // world
+    gexp, dexp = L.gate.size // L.n_expert, L.down.size // L.n_expert
+    lo, hi = rank * ne_local, (rank + 1) * ne_local
+    shard = orc.HostLayer(L.hidden, L.expert_ff, ne_local, L.top_k, L.router[lo:hi], None, L.gate[lo * gexp:hi * gexp],
+                          L.up[lo * gexp:hi * gexp], L.down[lo * dexp:hi * dexp])
+    shared_only = orc.HostLayer(L.hidden, L.expert_ff, 1, 1, L.router[:1], None, L.sh_gate, L.sh_up, L.sh_down)
+
+    def route_fn(x):
+        ids, w = orc.route(L.router, L.bias, x.numpy(), L.top_k, L.scale, L.norm)
+        return torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(w)
+
+    def localize_fn(ids, first, count):
+        e = ids.to(torch.int64) - first
+        return torch.where((e >= 0) & (e < count), e, torch.full_like(e, count)).to(torch.int32)
+
+    def tokens_fn(x, ids_local, w):
+        return torch.from_numpy(shard.experts_forward(x.numpy(), ids_local.numpy().astype(np.uint32), w.numpy()))
+
+    def shared_fn(x):
+        n = x.shape[0]
+        return torch.from_numpy(shared_only.experts_forward(x.numpy(), np.zeros((n, 1), np.uint32), np.ones((n, 1), np.float32)))
+
+    def sum_fn(parts, shared):
+        n = parts.shape[0] // world
+        out = torch.zeros(n, parts.shape[1])
+        for s_ in range(world):
+            out += parts[s_ * n:(s_ + 1) * n]
+        return out if shared is None else out + shared
+
+    ep = ExpertParallelPrefill(route_fn, localize_fn, tokens_fn, shared_fn, sum_fn, L.n_expert, L.top_k,
+                               payload_dtype=torch.float32, waves=waves)
+    t_loc = 11                                            # the same count on every rank; not a multiple of the waves
+    x = np.random.default_rng(300 + rank).standard_normal((t_loc, L.hidden)).astype(np.float32)
+    out = ep.forward(torch.from_numpy(x)).numpy()
+    want, _, _ = L.forward(x)
+    q.put((rank, orc.rel_l2(out, want), ep.last_stats))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,waves", [(2, 1), (2, 3), (4, 2)])
+def test_expert_parallel_prefill_fixed_size_exchange(orc, world, waves):
+    """`ExpertParallelPrefill`: every rank receives every token (all-gather), keeps the slots of its own experts,
+    returns one partial row per token (all-to-all); no counts travel and nothing is read back on the host."""
+    orc.build()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_prefill_worker, args=(r, world, port, q, waves)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, stats in res:
+        assert err < 1e-5, (rank, err)
+        assert stats["waves"] == waves and stats["tokens_gathered"] == world * 11
