@@ -474,9 +474,9 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
         x = step.forward(x)
         ref = f.layer_forward(ref, nw, 1e-6)
     torch.cuda.synchronize()
-    tt = torch.tensor([float((x - ref).norm() / ref.norm())], device=dev, dtype=torch.float64)
+    tt = torch.tensor([float((x - ref).norm() / ref.norm()), float((x - ref).abs().max())], device=dev, dtype=torch.float64)
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    res["parity"] = {"tokens": 64, "layers": 2, "rel_l2": float(tt[0]),
+    res["parity"] = {"tokens": 64, "layers": 2, "rel_l2": float(tt[0]), "max_abs_diff": float(tt[1]),
                      "against": "the single-GPU layer entry on the same tokens and weights, max over ranks"}
     return res
 

@@ -278,8 +278,9 @@ def _ep_decode_worker(rank, world, port, q):
         if err0 is None:          # first layer: identical inputs on both paths
             torch.cuda.synchronize()
             err0 = float((x - ref).norm() / ref.norm())
+            moved = float((x - x_all[rank * t_loc:(rank + 1) * t_loc]).norm() / x.norm())   # the block's share of the output
     torch.cuda.synchronize()
-    q.put((rank, err0, float((x - ref).norm() / ref.norm())))
+    q.put((rank, err0, float((x - ref).norm() / ref.norm()), moved))
     dist.destroy_process_group()
 
 
@@ -301,7 +302,8 @@ def test_expert_parallel_decode_two_gpus():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, err0, err in res:
+    for rank, err0, err, moved in res:
+        assert moved > 1e-2, (rank, moved)  # the block's output is a visible part of what is compared
         assert err0 < 1e-5, (rank, err0)   # same kernels on the same inputs; the sum is grouped by rank: f32 rounding
         assert err < 2e-3, (rank, err)     # later layers see inputs that differ in the last bits (a near-tie may re-route)
 
