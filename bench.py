@@ -356,6 +356,46 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=Tru
     return res
 
 
+def measure_lm_head(dev, steps=20, warmup=5):
+    """The plain quantized mat-vec at the model's lm_head shape (`ops::mul_mv`, src/ops/mv_id.rs:54-56 of the
+    reference, called from src/model.rs:388-403): Q6_K [100352 x 3072], 253 MB per token, one token.  Timed with
+    CUDA events over weights that do not fit L2; a sample of rows is checked against the CPU oracle."""
+    import torch
+
+    from maxuna_b200 import _native
+    from maxuna_b200.gguf import Q6_K, ExpertStack, stream_ptr
+    from oracle import oracle as orc
+
+    lib = _native.lib()
+    n_out, k = 100352, H
+    copies = 2                                                       # 2 x 253 MB rotated: nothing stays in L2
+    stacks = [ExpertStack.random(Q6_K, 1, n_out, k, std=0.02, seed=900 + i, device=dev, chunk_experts=1) for i in range(copies)]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    x = torch.randn(1, k, generator=gen, device=dev)
+    out = torch.empty(1, n_out, device=dev)
+
+    def run(i=[0]):
+        st = stacks[i[0] % copies]
+        i[0] += 1
+        _native.check(lib.lmoe_mul_mv(st.buffer.data_ptr() + st.base_off, Q6_K, n_out, k, x.data_ptr(), 1, out.data_ptr(), stream_ptr()))
+
+    ms = _time_gpu(run, steps, warmup, 1, dev)
+    nbytes = n_out * (k // 256) * 210
+    # parity: the last launch used stack (steps + warmup - 1) % copies; check 64 sampled rows of it
+    st = stacks[(steps + warmup - 1) % copies]
+    rows = np.sort(np.random.default_rng(5).choice(n_out, 64, replace=False))
+    rb = (k // 256) * 210
+    raw = st.buffer[st.base_off:st.base_off + st.nbytes].view(n_out, rb)[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    want = orc.mul_mv(Q6_K, raw, 64, k, x.cpu().numpy())[0]
+    got = out[0, torch.from_numpy(rows).to(dev)].cpu().numpy()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+    return {"workload": "lm_head-shaped plain mat-vec: Q6_K [100352 x 3072], one token", "us": ms * 1e3,
+            "gb_per_s": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak, "bytes": nbytes,
+            "parity": {"rows": 64, "rel_l2": orc.rel_l2(got, want), "against": "CPU oracle (dequantize -> f32 dot)"}}
+
+
 def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
     """The expert portion of a Laguna-shaped model (BASELINE config 5): a residual stack of `n_layers` MoE
     layers, x <- x + block_l(rms_norm_l(x)); batched decode of 64 sequences (one token each) and a 2048-token
@@ -498,7 +538,8 @@ def main():
     ap.add_argument("--ep-mode", default="dense", choices=["dense", "tokens"],
                     help="expert-parallel prefill exchange: fixed-size (all-gather / all-to-all) or compacted token lists")
     ap.add_argument("--ep-waves", type=int, default=0, help="waves of the fixed-size exchange (0 = by size)")
-    ap.add_argument("--no-stack", action="store_true", help="skip the config-5 stack measurement of the default run")
+    ap.add_argument("--no-stack", action="store_true", help="skip the config-5 stack and the lm_head measurements of the default run")
+    ap.add_argument("--lm-head-only", action="store_true", help="profiling aid: run only the lm_head-shaped mat-vec and print it")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -529,6 +570,12 @@ def main():
         st = measure_stack(dev, rank, world, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 3))
         if rank == 0:
             print(json.dumps({"stack": st}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.lm_head_only:
+        if rank == 0:
+            print(json.dumps({"lm_head": measure_lm_head(dev, steps=max(3, min(args.steps, 50)), warmup=args.warmup)}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -697,6 +744,8 @@ def main():
         torch.cuda.empty_cache()
         stack = measure_stack(dev, rank, world, 48, steps=3, warmup=3)
 
+    lm_head = measure_lm_head(dev) if (rank == 0 and world == 1 and not args.no_stack) else None
+
     if rank == 0:
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
@@ -738,6 +787,8 @@ def main():
                 "peak_tflops": peaks.get("bf16_tflops"), "results": prefill,
                 "frac_of_peak": {k: v["tflops"] / (peaks.get("bf16_tflops") * world) for k, v in prefill.items()},
             }
+        if lm_head is not None:
+            line["lm_head"] = lm_head
         if stack is not None:
             stack["workload"] = ("config5: residual stack of MoE layers, 64-sequence batched decode and 2048-token prefill" +
                                  (f", expert parallel over {world} GPUs" if world > 1 else

@@ -226,7 +226,20 @@ extern "C" lmoe_status lmoe_mul_mv(const void *weight, int32_t dtype, int64_t n_
     REQUIRE(n_out >= 1 && n_out <= INT32_MAX && t >= 0 && t <= INT32_MAX, "n_out/t out of range");
     REQUIRE(k > 0 && k % QK_K == 0 && k <= INT32_MAX, "k (%lld) is not a positive multiple of %d", (long long)k, QK_K);
     REQUIRE(aligned16(weight) && aligned16(x), "weight and x must be 16-byte aligned");
-    LMOE_CUDA(launch_mul_mv_id(dtype, static_cast<const uint8_t *>(weight), n_out * (k / QK_K) * ts, 1, (int)n_out,
+    const uint8_t *wb = static_cast<const uint8_t *>(weight);
+    if (dtype == LMOE_Q6_K && t >= 1 && t <= 4 && n_out >= 4096 && mv_q6k_stream_available(n_out, k)) {
+        // the vocabulary projection of a decode step: every weight byte is read once per token, through the
+        // streamed kernel; the rows past the last whole 16-row chunk go to the row-per-warp kernel below
+        const int64_t body = n_out / 16 * 16, row_bytes = (k / QK_K) * ts;
+        for (int64_t i = 0; i < t; i++) {
+            LMOE_CUDA(launch_mv_q6k_stream(wb, (int)n_out, (int)k, x + i * k, out + i * n_out, (cudaStream_t)stream));
+            if (body < n_out)
+                LMOE_CUDA(launch_mul_mv_id(dtype, wb + body * row_bytes, (n_out - body) * row_bytes, 1, (int)(n_out - body),
+                                           (int)k, x + i * k, 1, 1, nullptr, 1, out + i * n_out + body, (cudaStream_t)stream));
+        }
+        return LMOE_OK;
+    }
+    LMOE_CUDA(launch_mul_mv_id(dtype, wb, n_out * (k / QK_K) * ts, 1, (int)n_out,
                                (int)k, x, (int)t, 1, nullptr, 1, out, (cudaStream_t)stream));
     return LMOE_OK;
 }

@@ -77,6 +77,9 @@ cudaError_t launch_route_logits(const float *router, const float *x, int t, int 
 cudaError_t launch_route_select(const float *logits, const float *bias, int t, int n_expert, int top_k,
                                 float scale, int norm, uint32_t *ids, float *weights, cudaStream_t s);
 // mv_id.cu
+// Streamed Q6_K mat-vec (mv_stream.cu): rows [0, n_out - n_out % 16) of one activation row.
+bool mv_q6k_stream_available(int64_t n_out, int64_t k);
+cudaError_t launch_mv_q6k_stream(const uint8_t *w, int n_out, int k, const float *x, float *out, cudaStream_t s);
 cudaError_t launch_mul_mv_id(int dtype, const uint8_t *w, int64_t expert_bytes, int n_expert, int n_out, int k,
                              const float *x, int t, int x_per_row, const uint32_t *ids, int top_k, float *out,
                              cudaStream_t s);

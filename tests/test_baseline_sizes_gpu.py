@@ -215,3 +215,28 @@ def test_decode_entry_takes_more_than_64_tokens(orc, dev):
     want, ids_o, _ = host.forward(x)
     assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ids_o)
     assert orc.rel_l2(out.cpu().numpy(), want) < 2e-3
+
+
+def test_lm_head_shape_plain_mv(orc, dev):
+    """`ops::mul_mv` at the shape the model calls it on, once per decoded token (src/model.rs:388-403):
+    Q6_K [100352 x 3072].  256 sampled rows against the oracle, the first and the last chunk among them, and
+    every row finite; a second activation row checks the per-token loop."""
+    from maxuna_b200 import ops
+    from maxuna_b200.gguf import Q6_K, ExpertStack
+
+    n_out, k = 100352, 3072
+    st = ExpertStack.random(Q6_K, 1, n_out, k, std=0.02, seed=4242, device=dev, chunk_experts=1)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    x = torch.randn(2, k, generator=gen, device=dev)
+    x[0, 100] = 40.0  # an outlier channel, as the hidden state has them
+    w = st.buffer[st.base_off:st.base_off + st.nbytes]
+    got = ops.mul_mv(w, Q6_K, n_out, k, x)
+    assert bool(torch.isfinite(got).all())
+    rows = np.unique(np.concatenate([np.arange(16), np.arange(n_out - 16, n_out),
+                                     np.random.default_rng(3).choice(n_out, 224, replace=False)]))
+    rb = (k // 256) * 210
+    raw = w.view(n_out, rb)[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    want = orc.mul_mv(Q6_K, raw, len(rows), k, x.cpu().numpy())
+    sub = got[:, torch.from_numpy(rows).to(dev)].cpu().numpy()
+    assert orc.rel_l2(sub, want) < 1e-5

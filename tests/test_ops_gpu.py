@@ -112,6 +112,26 @@ def test_plain_mv(orc, dev, dt, name):
     assert orc.rel_l2(got, orc.mul_mv(dt, raw, n_out, k, x)) < 1e-3
 
 
+@pytest.mark.parametrize("n_out,k,t", [(4096, 256, 1), (4104, 512, 3), (4112, 768, 2), (4096 + 16 * 150, 3072, 1)])
+def test_plain_mv_q6k_streamed(orc, dev, n_out, k, t):
+    """The streamed Q6_K kernel behind `lmoe_mul_mv` (rows in 16-row chunks through shared memory, integer tensor
+    cores): odd and even super-block counts per row (the 210-byte blocks change word alignment), a row count
+    with a tail, more than one chunk per CTA, several tokens, and an outlier channel.  Same oracle and a tighter
+    bound than the reference's 1e-3 (src/ops/mv_id.rs:300-330): the activations carry 21 bits."""
+    from maxuna_b200 import ops
+
+    raw = orc.quantize(14, orc.pseudo_random(n_out * k, 70 + k, -1.0, 1.0))
+    x = orc.pseudo_random(t * k, 8, -1.0, 1.0).reshape(t, k)
+    x[0, 5] = 300.0
+    buf = torch.zeros(raw.size + 128, dtype=torch.uint8, device=dev)
+    buf[: raw.size] = torch.from_numpy(raw).to(dev)
+    got = ops.mul_mv(buf, 14, n_out, k, torch.from_numpy(x).to(dev)).cpu().numpy()
+    want = orc.mul_mv(14, raw, n_out, k, x)
+    assert np.isfinite(got).all()
+    assert orc.rel_l2(got, want) < 1e-5
+    assert np.abs(got - want).max() < 1e-5 * np.abs(want).max() * 10
+
+
 @pytest.mark.parametrize("dt,name", DTYPES)
 def test_device_codec_matches_oracle(orc, dev, dt, name):
     from maxuna_b200.gguf import ExpertStack
