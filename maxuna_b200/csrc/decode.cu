@@ -154,7 +154,7 @@ __device__ __noinline__ void dec_bad_index(uint32_t *ctrl, uint32_t code, uint32
 // CTA arrives).  `target` = arrivals expected so far in this launch.
 __device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t *sync, uint32_t target, int tid, int cons_threads,
                                              int first_id, int first_count) {
-    __threadfence();
+    // the CTA barrier orders every thread's stores before thread 0's fence, which is cumulative: one fence per CTA
     bar_sync(first_id, first_count); // phases 1/2: the epilogue warp arrives here once its stores are fenced
     if (tid == 0) {
         __threadfence();
@@ -170,7 +170,6 @@ __device__ __forceinline__ void grid_barrier(uint32_t *ctrl, uint32_t *sync, uin
                 break;
             }
         }
-        __threadfence();
     }
     bar_sync(1, cons_threads);
 }
@@ -386,8 +385,10 @@ __device__ __forceinline__ void unit_q4k(const uint8_t *stage, int row_bytes, in
 __device__ __forceinline__ void unit_q6k(const uint8_t *stage, int row_bytes, int nb, int wq, int g, int t,
                                          const int8_t *xcol, const __half *scol, const float *sxs, float r0, float r1,
                                          float (&acc)[4]) {
-    const uint8_t *rg = stage + ((wq & 1) * 16 + g) * row_bytes;
-    const uint8_t *rG = rg + 8 * row_bytes;
+    // lane group g works on rows 2g and 2g+1 of the tile: with 840-byte rows the eight rows of one load sit in
+    // disjoint shared-memory banks (rows g and g+8 would share two)
+    const uint8_t *rg = stage + ((wq & 1) * 16 + 2 * g) * row_bytes;
+    const uint8_t *rG = rg + row_bytes;
     for (int b = wq >> 1; b < nb; b += CW / 2) {
         const uint8_t *bg = rg + b * Q6K_BYTES, *bG = rG + b * Q6K_BYTES;
         if (row_bytes & 2) q6k_block<2>(bg, bG, b, t, xcol, scol, sxs, r0, r1, acc); // odd block count: rows alternate too
@@ -963,9 +964,11 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
                     mbar_wait(&red_free[buf], ((n / NRED) & 1) ^ 1, P.ctrl, 0x28 + phase);
                     float *rb = red + buf * (CW * 16 * NCOL);
                     if (2 * t4 < NCOL) {
-                        float *r0 = rb + (wq * 16 + g) * NCOL + 2 * t4;
+                        // accumulator rows: g and g+8 of the 16 (phase 1), 2g and 2g+1 (phase 2, see unit_q6k)
+                        float *r0 = rb + (wq * 16 + (phase == 1 ? g : 2 * g)) * NCOL + 2 * t4;
+                        const int second = phase == 1 ? 8 * NCOL : NCOL;
                         r0[0] = acc[0]; r0[1] = acc[1];
-                        r0[8 * NCOL] = acc[2]; r0[8 * NCOL + 1] = acc[3];
+                        r0[second] = acc[2]; r0[second + 1] = acc[3];
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&red_full[buf]);
@@ -986,14 +989,27 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
             const int nslot = K + (P.has_shared && tok >= P.sh_t0 && tok < P.sh_t0 + P.sh_nt ? 1 : 0);
             const float4 *yp = reinterpret_cast<const float4 *>(P.ypart + (size_t)tok * (K + 1) * P.hidden) + c;
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int sl = 0; sl < nslot; sl++) {
-                // a slot the caller left empty has no partial row
-                if (P.ext_ids != nullptr && sl < K && __ldg(P.ext_ids + tok * K + sl) >= (uint32_t)E) continue;
-                const float4 v = __ldcg(yp + (size_t)sl * h4);
-                sum.x = __fadd_rn(sum.x, v.x);
-                sum.y = __fadd_rn(sum.y, v.y);
-                sum.z = __fadd_rn(sum.z, v.z);
-                sum.w = __fadd_rn(sum.w, v.w);
+            // twelve slots' loads are in flight at once (the rows come from L2: one round trip, not one per slot)
+            for (int s0 = 0; s0 < nslot; s0 += 12) {
+                float4 v[12];
+                uint32_t present = 0u;
+#pragma unroll
+                for (int j = 0; j < 12; j++) {
+                    const int sl = s0 + j;
+                    // a slot the caller left empty has no partial row
+                    const bool ok = sl < nslot && !(P.ext_ids != nullptr && sl < K && __ldg(P.ext_ids + tok * K + sl) >= (uint32_t)E);
+                    v[j] = ok ? __ldcg(yp + (size_t)sl * h4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    present |= (uint32_t)ok << j;
+                }
+#pragma unroll
+                for (int j = 0; j < 12; j++) {
+                    if (present & (1u << j)) {
+                        sum.x = __fadd_rn(sum.x, v[j].x);
+                        sum.y = __fadd_rn(sum.y, v[j].y);
+                        sum.z = __fadd_rn(sum.z, v[j].z);
+                        sum.w = __fadd_rn(sum.w, v[j].w);
+                    }
+                }
             }
             reinterpret_cast<float4 *>(P.out + (size_t)tok * P.hidden)[c] = sum;
         }

@@ -117,7 +117,7 @@ __device__ __forceinline__ uint32_t sc_pair_half2(const int8_t *p) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// One Q6_K super-block of rows g (bg) and g+8 (bG), which have the same alignment.  The six-bit value of a
+// One Q6_K super-block of two rows (bg -> accumulators 0/1, bG -> 2/3) that have the same alignment.  The six-bit value of a
 // weight (low nibble | two high bits << 4, 0..63) is one byte of a k = 16 integer MMA: one MMA per 16-wide
 // sub-block, whose signed scale multiplies the exact integer sum.
 template <int MIS>
