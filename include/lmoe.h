@@ -278,7 +278,8 @@ lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const float *x, in
 /* `MoeBlock::forward` with HOST buffers: copies x to the device, runs the decode
  * or prefill path (t >= lmoe_mm_id_min_seq() -> prefill; the reference's own switch, src/moe.rs:236-240, is at 32),
  * copies the result back and synchronises the stream. `x_host` / `out_host`
- * should be pinned for full copy bandwidth. */
+ * should be pinned for full copy bandwidth; on the decode path a pinned, device-mapped `out_host` is written by
+ * the kernel itself (no device-to-host copy), pageable memory goes through a copy. */
 lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
                                   uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                   size_t workspace_bytes, void *stream);

@@ -170,6 +170,19 @@ extern "C" lmoe_status lmoe_moe_forward_prefill(const lmoe_layer *layer, const f
     return launch_moe_prefill(layer, x, t, out, ids_out, weights_out, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+// The device-side address of a page-locked, device-mapped host buffer; NULL for pageable or unknown memory
+// (those go through a copy).
+static float *host_buffer_device_alias(float *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (a.type != cudaMemoryTypeHost || a.devicePointer == nullptr) return nullptr;
+    if ((reinterpret_cast<uintptr_t>(a.devicePointer) & 15u) != 0) return nullptr; // the kernel stores 16-byte vectors
+    return static_cast<float *>(a.devicePointer);
+}
+
 extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
                                              uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                              size_t workspace_bytes, void *stream) {
@@ -195,14 +208,19 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     lmoe_status st;
     // the reference switches to its grouped GEMM at 32 tokens (`use_mm`, src/moe.rs:236-240); here the mat-vec
     // kernel, which streams each distinct expert once per launch, stays ahead up to 64 tokens
-    if (t >= lmoe_mm_id_min_seq())
+    const bool decode = t < lmoe_mm_id_min_seq();
+    // Decode: when the result buffer is page-locked host memory that the device can address, the kernel's last
+    // phase stores the rows there itself (a few KB of posted writes) and the device-to-host copy, whose fixed
+    // cost is a tenth of a one-token call, is not needed.
+    float *out_direct = decode ? host_buffer_device_alias(out_host) : nullptr;
+    if (!decode)
         st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
                                       workspace, kernel_ws, stream);
     else
-        st = lmoe_moe_forward_decode(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
-                                     workspace, kernel_ws, stream);
+        st = lmoe_moe_forward_decode(layer, xd, t, out_direct ? out_direct : od, ids_out_host ? idd : nullptr,
+                                     weights_out_host ? wd : nullptr, workspace, kernel_ws, stream);
     if (st) return st;
-    LMOE_CUDA(cudaMemcpyAsync(out_host, od, (size_t)t * layer->hidden * 4, cudaMemcpyDeviceToHost, s));
+    if (!out_direct) LMOE_CUDA(cudaMemcpyAsync(out_host, od, (size_t)t * layer->hidden * 4, cudaMemcpyDeviceToHost, s));
     if (ids_out_host) LMOE_CUDA(cudaMemcpyAsync(ids_out_host, idd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
     if (weights_out_host)
         LMOE_CUDA(cudaMemcpyAsync(weights_out_host, wd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));

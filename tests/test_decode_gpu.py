@@ -98,6 +98,17 @@ def test_decode_host_buffers(orc, full_block, full_host):
     assert orc.rel_l2(out.numpy(), want) < 2e-3
 
 
+def test_decode_host_buffers_pageable_and_pinned_agree(orc, full_block):
+    """A pinned result buffer is written by the kernel itself, a pageable one goes through a copy: same bits."""
+    x = np.random.default_rng(8).standard_normal((5, 3072)).astype(np.float32)
+    xh = torch.from_numpy(x).pin_memory()
+    pinned = full_block.forward_host(xh).clone()
+    pageable = torch.empty(5, 3072, dtype=torch.float32)
+    assert not pageable.is_pinned()
+    full_block.forward_host(torch.from_numpy(x.copy()), pageable)
+    assert np.array_equal(pinned.numpy().view(np.uint32), pageable.numpy().view(np.uint32))
+
+
 def test_decode_rejects_bad_shapes(full_block, dev):
     from maxuna_b200 import LmoeError
 
