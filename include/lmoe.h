@@ -284,6 +284,14 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
                                   uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                   size_t workspace_bytes, void *stream);
 
+/* The same without the final synchronisation, like every other entry of this header (the reference's ops return
+ * before the GPU has run them, src/ops/dispatch.rs `run_inner`): the copies and the kernels are enqueued on `stream`
+ * and the call returns; `out_host` holds the result once the stream has been synchronised.  Calls that share a
+ * workspace must share the stream.  Both buffers must be pinned for the copies to be asynchronous. */
+lmoe_status lmoe_moe_forward_host_async(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                  uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
 /* The FFN half of a transformer layer around the block, src/model.rs:340-350:
  *   ffn_normed = rms_norm(ffn_inp) * norm_weight;  out = ffn_inp + MoeBlock::forward(ffn_normed).
  * rms_norm is candle's `RmsNorm` (x * 1/sqrt(mean(x^2) + eps) * weight, f32); its sum of squares runs in

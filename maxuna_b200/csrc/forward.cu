@@ -183,10 +183,9 @@ static float *host_buffer_device_alias(float *p) {
     return static_cast<float *>(a.devicePointer);
 }
 
-extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
-                                             uint32_t *ids_out_host, float *weights_out_host, void *workspace,
-                                             size_t workspace_bytes, void *stream) {
-    lmoe_clear_error();
+static lmoe_status forward_host_enqueue(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                        uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                        size_t workspace_bytes, void *stream) {
     if (!layer) return lmoe_fail(LMOE_ERR_INVALID, "layer is NULL");
     if (!x_host || !out_host) return lmoe_fail(LMOE_ERR_INVALID, "x_host/out_host is NULL");
     if (t < 0 || t > (1 << 22)) return lmoe_fail(LMOE_ERR_INVALID, "t (%lld) out of range", (long long)t);
@@ -224,8 +223,26 @@ extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const floa
     if (ids_out_host) LMOE_CUDA(cudaMemcpyAsync(ids_out_host, idd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
     if (weights_out_host)
         LMOE_CUDA(cudaMemcpyAsync(weights_out_host, wd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
-    LMOE_CUDA(cudaStreamSynchronize(s));
     return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                             uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                             size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    lmoe_status st = forward_host_enqueue(layer, x_host, t, out_host, ids_out_host, weights_out_host, workspace,
+                                          workspace_bytes, stream);
+    if (st) return st;
+    LMOE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return LMOE_OK;
+}
+
+extern "C" lmoe_status lmoe_moe_forward_host_async(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
+                                                   uint32_t *ids_out_host, float *weights_out_host, void *workspace,
+                                                   size_t workspace_bytes, void *stream) {
+    lmoe_clear_error();
+    return forward_host_enqueue(layer, x_host, t, out_host, ids_out_host, weights_out_host, workspace, workspace_bytes,
+                                stream);
 }
 
 // ---- the transformer layer's FFN half around the block (src/model.rs:340-350) -------------

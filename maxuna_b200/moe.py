@@ -232,15 +232,16 @@ class MoeBlock:
                                            self._lws.data_ptr(), self._lws.numel(), stream_ptr()))
         return (out, ids, w) if return_routing else out
 
-    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor = None):
-        """Host-buffer call (x and result in pinned host memory), `lmoe_moe_forward_host`."""
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor = None, sync: bool = True):
+        """Host-buffer call (x and result in pinned host memory), `lmoe_moe_forward_host`; with ``sync=False``
+        `lmoe_moe_forward_host_async`: the result is valid once the current stream has been synchronised."""
         assert not x_host.is_cuda and x_host.dtype == torch.float32 and x_host.is_contiguous()
         seq = x_host.shape[0]
         if out_host is None:
             out_host = torch.empty(seq, self.hidden, dtype=torch.float32).pin_memory()
         ws = self.workspace(seq)
-        check(lib().lmoe_moe_forward_host(self._h, x_host.data_ptr(), seq, out_host.data_ptr(), None, None,
-                                          ws.data_ptr(), ws.numel(), stream_ptr()))
+        fn = lib().lmoe_moe_forward_host if sync else lib().lmoe_moe_forward_host_async
+        check(fn(self._h, x_host.data_ptr(), seq, out_host.data_ptr(), None, None, ws.data_ptr(), ws.numel(), stream_ptr()))
         return out_host
 
     # ---- expert-parallel pieces (rows already dispatched to this GPU) -------------------

@@ -109,6 +109,20 @@ def test_decode_host_buffers_pageable_and_pinned_agree(orc, full_block):
     assert np.array_equal(pinned.numpy().view(np.uint32), pageable.numpy().view(np.uint32))
 
 
+def test_decode_host_buffers_async_matches_sync(full_block):
+    """`lmoe_moe_forward_host_async`: several calls enqueued back to back, one synchronisation, same bits as the
+    synchronous entry."""
+    rng = np.random.default_rng(9)
+    xs = [torch.from_numpy(rng.standard_normal((b, 3072)).astype(np.float32)).pin_memory() for b in (1, 4, 2)]
+    want = [full_block.forward_host(x).clone() for x in xs]
+    outs = [torch.empty(x.shape[0], 3072).pin_memory() for x in xs]
+    for x, o in zip(xs, outs):
+        full_block.forward_host(x, o, sync=False)
+    torch.cuda.synchronize()
+    for o, w in zip(outs, want):
+        assert np.array_equal(o.numpy().view(np.uint32), w.numpy().view(np.uint32))
+
+
 def test_decode_rejects_bad_shapes(full_block, dev):
     from maxuna_b200 import LmoeError
 
