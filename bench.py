@@ -310,7 +310,9 @@ def measure_prefill(dev, rank, world, steps=8, warmup=3, tokens=None, checks=Tru
                 # of the expert-parallel result must agree to f32 rounding (the sums are grouped by rank)
                 n_s = min(256, t_loc)
                 ref, ids_ref, _ = blk.forward(x[:n_s], return_routing=True, path="prefill")
+                ep.profile = True                          # per-phase CUDA-event times of this (untimed) call
                 got = ep.forward(x)[:n_s]
+                ep.profile = False
                 torch.cuda.synchronize()
                 d = (got.double() - ref.double()).pow(2).sum().sqrt() / ref.double().pow(2).sum().sqrt()
                 tt = torch.tensor([float(d)], device=dev, dtype=torch.float64)

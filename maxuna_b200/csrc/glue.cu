@@ -51,7 +51,7 @@ __global__ void combine_kernel(const float *__restrict__ down, const float *__re
     out[i] = v[0];
 }
 
-// One block per expert: scan the tokens in chunks of blockDim.x, keep the
+// One block per expert: scan the tokens in chunks of 1024 (four consecutive tokens per thread), keep the
 // token order, write flat ids `token*top_k + slot`.
 __global__ void __launch_bounds__(256)
 map0_kernel(const uint32_t *__restrict__ ids, int t, int top_k, int n_expert, uint32_t *__restrict__ tpe,
@@ -63,19 +63,32 @@ map0_kernel(const uint32_t *__restrict__ ids, int t, int top_k, int n_expert, ui
     if (threadIdx.x == 0) base = 0;
     __syncthreads();
     int32_t *dst = ids_map + (size_t)e * t;
-    for (int t0 = 0; t0 < t; t0 += 256) {
-        const int token = t0 + threadIdx.x;
-        int slot = -1;
-        if (token < t) {
-            for (int s = 0; s < top_k; s++)
-                if (ids[(size_t)token * top_k + s] == (uint32_t)e) { slot = s; break; }
+    for (int t0 = 0; t0 < t; t0 += 1024) {
+        int slot[4], mine = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int token = t0 + 4 * (int)threadIdx.x + j;
+            slot[j] = -1;
+            if (token < t) {
+                for (int s = 0; s < top_k; s++)
+                    if (ids[(size_t)token * top_k + s] == (uint32_t)e) { slot[j] = s; break; }
+            }
+            mine += slot[j] >= 0;
         }
-        const unsigned m = __ballot_sync(0xffffffffu, slot >= 0);
-        if (lane == 0) warp_count[warp] = __popc(m);
+        // exclusive prefix of the per-thread counts inside the warp, then over the warps
+        int pre = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, pre, o);
+            if (lane >= o) pre += v;
+        }
+        if (lane == 31) warp_count[warp] = pre;
         __syncthreads();
-        int off = base;
+        int off = base + pre - mine;
         for (int wv = 0; wv < warp; wv++) off += warp_count[wv];
-        if (slot >= 0) dst[off + __popc(m & ((1u << lane) - 1))] = token * top_k + slot;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (slot[j] >= 0) dst[off++] = (t0 + 4 * (int)threadIdx.x + j) * top_k + slot[j];
         __syncthreads();
         if (threadIdx.x == 0) {
             int tot = 0;

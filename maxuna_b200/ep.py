@@ -347,15 +347,18 @@ class ExpertParallelPrefill:
     Rank r owns experts ``[r*E/G, (r+1)*E/G)`` and ``t_loc`` tokens (the same count on every rank).  Instead of
     compacting per-destination token lists - which needs the counts on the host before the payload exchange can
     be sized - every rank receives every token: fixed-size collectives, sized by the shapes alone.
-      1. route the rank's own tokens (replicated router: ids identical to the single-GPU result);
-      2. all-gather of the f16 activations and of the (id, weight) words, in `waves` slices of the local tokens;
+      1. all-gather of the f16 activations, in `waves` slices of the local tokens, queued first (they do not
+         depend on routing); route the rank's own tokens meanwhile (replicated router: ids identical to the
+         single-GPU result);
+      2. all-gather of the (id, weight) words, in the same slices;
       3. per wave: localise the ids (other ranks' experts -> empty slot) and run the token-level grouped GEMMs
          over all G*n tokens of the wave: a token without a local expert costs nothing but a zero output row;
       4. per wave: all-to-all of the partial rows ([G, n, H] f32: chunk s belongs to rank s's tokens);
-      5. the owner adds the G partial rows of a token in rank order, then the shared expert, which ran on a side
-         stream meanwhile.
+      5. the shared expert of the rank's own tokens runs while the last partial rows travel; the owner then adds
+         the G partial rows of a token in rank order and the shared expert's row.
     The collectives of wave i+1 (gather) and i-1 (return) run on the communicator's stream while wave i
-    multiplies.  Callables as in `ExpertParallelMoe` / `ExpertParallelDecode`:
+    multiplies.  (Keeping 8 or 16 SMs free of the persistent GEMM kernels for the collectives' kernels was measured
+    on 8 GPUs and did not pay: 1.92 ms with none, 1.94 / 1.97 ms with 8 / 16.)  Callables as in `ExpertParallelMoe` / `ExpertParallelDecode`:
       route_fn(x) -> (ids, w);  localize_fn(ids, first, count);  tokens_fn(x16[N,H], ids_local[N,K], w[N,K]) -> [N,H] f32;
       shared_fn(x) -> [t_loc,H] or None;  sum_fn(parts[G*n,H], shared_or_None[n,H]) -> [n,H].
     """
@@ -371,7 +374,8 @@ class ExpertParallelPrefill:
         self.e_local = n_expert // self.world
         self.payload_dtype = payload_dtype
         self.waves = waves
-        self._side = None
+        self.profile = False      # set to record per-phase CUDA-event times of the next forward in `last_phases`
+        self.last_phases = None
         self.last_stats = {}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -381,45 +385,62 @@ class ExpertParallelPrefill:
         # hide part of the exchange; four stream the local experts' weights too often to pay)
         n_waves = self.waves if self.waves > 0 else (1 if t_loc < 2048 else 2)
         n_waves = max(1, min(n_waves, t_loc))
-        ids, w = self.route_fn(x)
-        shared = None
-        if self.shared_fn is not None:
-            if x.is_cuda:
-                if self._side is None:
-                    self._side = torch.cuda.Stream(device=dev)
-                self._side.wait_stream(torch.cuda.current_stream(dev))
-                with torch.cuda.stream(self._side):
-                    shared = self.shared_fn(x)
-            else:
-                shared = self.shared_fn(x)
-        x16 = x.to(self.payload_dtype)
-        meta = torch.cat([ids.view(torch.int32), w.contiguous().view(torch.int32)], dim=1).contiguous()  # [t_loc, 2K] words
+        marks = []                                         # (name, event) on the compute stream, when profiling
+
+        def mark(name):
+            if self.profile and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         bounds = [(t_loc * i // n_waves, t_loc * (i + 1) // n_waves) for i in range(n_waves)]
+        # The activation rows do not depend on routing: the first wave's all-gather is queued before the router runs.
+        # After it the order on the communicator's stream is (id, weight) words of wave 0, rows of wave 1, words of
+        # wave 1, ...: a wave waits for nothing that belongs to a later one.
+        x16 = x.to(self.payload_dtype)
+
+        def gather_rows(a, b):
+            xa = torch.empty(g * (b - a), h, dtype=x16.dtype, device=dev)
+            return xa, dist.all_gather_into_tensor(xa, x16[a:b].contiguous(), group=self.group, async_op=True)
+
+        first = gather_rows(*bounds[0])
+        ids, w = self.route_fn(x)
+        mark("route")
+        meta = torch.cat([ids.view(torch.int32), w.contiguous().view(torch.int32)], dim=1).contiguous()  # [t_loc, 2K] words
         gathers = []
-        for a, b in bounds:                                # all gathers are queued at once: they run back to back
-            n = b - a
-            xa = torch.empty(g * n, h, dtype=x16.dtype, device=dev)
-            ma = torch.empty(g * n, 2 * k, dtype=torch.int32, device=dev)
-            h1 = dist.all_gather_into_tensor(xa, x16[a:b].contiguous(), group=self.group, async_op=True)
+        for i, (a, b) in enumerate(bounds):
+            xa, h1 = first if i == 0 else gather_rows(a, b)
+            ma = torch.empty(g * (b - a), 2 * k, dtype=torch.int32, device=dev)
             h2 = dist.all_gather_into_tensor(ma, meta[a:b].contiguous(), group=self.group, async_op=True)
             gathers.append((xa, ma, h1, h2))
         returns = []
         for (a, b), (xa, ma, h1, h2) in zip(bounds, gathers):
             h1.wait()
             h2.wait()
+            mark("gathered")
             ids_all = ma[:, :k].contiguous()
             w_all = ma[:, k:].contiguous().view(torch.float32)
             part = self.tokens_fn(xa, self.localize_fn(ids_all, self.rank * self.e_local, self.e_local), w_all)
+            mark("experts")
             recv = torch.empty_like(part)
             hr = dist.all_to_all_single(recv, part, group=self.group, async_op=True)
             returns.append((recv, hr, part))
-        if shared is not None and x.is_cuda:
-            torch.cuda.current_stream(dev).wait_stream(self._side)
+        # the shared expert of the rank's own tokens runs while the last partial rows travel
+        shared = self.shared_fn(x) if self.shared_fn is not None else None
+        mark("shared")
         out = torch.empty(t_loc, h, dtype=torch.float32, device=dev)
         for (a, b), (recv, hr, _) in zip(bounds, returns):
             hr.wait()
+            mark("returned")
             out[a:b] = self.sum_fn(recv, None if shared is None else shared[a:b])
+            mark("summed")
         self.last_stats = {"waves": n_waves, "tokens_gathered": g * t_loc, "rows_returned": (g - 1) * t_loc}
+        if marks:
+            # milliseconds on the compute stream between consecutive marks: the time a wait takes is the part of
+            # the collective that the preceding compute did not hide
+            torch.cuda.synchronize(dev)
+            self.last_phases = [(name, marks[i - 1][1].elapsed_time(ev)) for i, (name, ev) in enumerate(marks) if i > 0]
         return out
 
 
