@@ -399,7 +399,7 @@ def measure_lm_head(dev, steps=20, warmup=5):
             "parity": {"rows": 64, "rel_l2": orc.rel_l2(got, want), "against": "CPU oracle (dequantize -> f32 dot)"}}
 
 
-def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
+def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3, graph=False):
     """The expert portion of a Laguna-shaped model (BASELINE config 5): a residual stack of `n_layers` MoE
     layers, x <- x + block_l(rms_norm_l(x)); batched decode of 64 sequences (one token each) and a 2048-token
     prefill.
@@ -430,6 +430,25 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
         ms = _time_gpu(fn, steps, warmup, world, dev)
         return {"tokens": tokens, "ms_per_pass": ms, "tok_per_s": tokens / ms * 1e3, "us_per_layer": ms * 1e3 / n_layers}
 
+    def graphed(fn, tokens):
+        """The same pass recorded once as a CUDA graph and replayed (`maxuna_b200.graphs.GraphedCall`): no host work
+        per launch.  Every rank must get through the capture before any rank replays."""
+        from maxuna_b200.graphs import GraphedCall
+        try:
+            gc = GraphedCall(fn)
+            ok = 1.0
+        except Exception as e:  # noqa: BLE001 - reported in the result, the eager figure stands
+            gc, ok, err = None, 0.0, f"{type(e).__name__}: {e}"[:300]
+        if world > 1:
+            tt = torch.tensor([ok], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MIN)
+            ok = float(tt[0])
+        if ok < 1.0:
+            return {"error": err if gc is None else "capture failed on another rank"}
+        r = timed(gc.replay, tokens)
+        r["how"] = "one CUDA graph per pass, replayed"
+        return r
+
     if world == 1:
         layers = [MoeBlock.random(H, F, E, K, seed=7000 + i, device=dev) for i in range(n_layers)]
         norms = [0.5 + torch.rand(H, generator=gen, device=dev) for _ in layers]
@@ -437,6 +456,7 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
         ws = torch.zeros(need, dtype=torch.uint8, device=dev)
 
         def layer_path(x, bufs):
+            stream = torch.cuda.current_stream().cuda_stream   # the capture stream when a graph is being recorded
             for i, ly in enumerate(layers):
                 a, b = bufs[i & 1], bufs[(i & 1) ^ 1]
                 src = x if i == 0 else a
@@ -459,6 +479,8 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
             bufs = [torch.empty(t, H, device=dev), torch.empty(t, H, device=dev)]
             extra = (torch.empty(t, H, device=dev),) if fn is gemm_path else ()
             res[name] = timed(lambda: fn(x, bufs, *extra), t)
+            if graph and name == "decode64":
+                res["decode64_graph"] = graphed(lambda: fn(x, bufs), t)
         return res
 
     # ---- expert parallel ----
@@ -494,6 +516,8 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3):
         return x
 
     res["decode64"] = timed(decode_pass, 64)
+    if graph:
+        res["decode64_graph"] = graphed(decode_pass, 64)
     p_loc = 2048 // world
     x2k = torch.randn(p_loc, H, generator=xg, device=dev)
     normed = torch.empty_like(x2k)
@@ -541,6 +565,7 @@ def main():
     ap.add_argument("--ep-mode", default="dense", choices=["dense", "tokens"],
                     help="expert-parallel prefill exchange: fixed-size (all-gather / all-to-all) or compacted token lists")
     ap.add_argument("--ep-waves", type=int, default=0, help="waves of the fixed-size exchange (0 = by size)")
+    ap.add_argument("--stack-graph", action="store_true", help="with --stack-layers: also time the decode pass replayed as one CUDA graph")
     ap.add_argument("--no-stack", action="store_true", help="skip the config-5 stack and the lm_head measurements of the default run")
     ap.add_argument("--lm-head-only", action="store_true", help="profiling aid: run only the lm_head-shaped mat-vec and print it")
     args = ap.parse_args()
@@ -570,7 +595,8 @@ def main():
 
     _native.lib()
     if args.stack_layers > 0:
-        st = measure_stack(dev, rank, world, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 3))
+        st = measure_stack(dev, rank, world, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 3),
+                           graph=args.stack_graph)
         if rank == 0:
             print(json.dumps({"stack": st}))
         if world > 1:

@@ -123,6 +123,25 @@ def test_decode_host_buffers_async_matches_sync(full_block):
         assert np.array_equal(o.numpy().view(np.uint32), w.numpy().view(np.uint32))
 
 
+def test_decode_graph_replay_matches_eager(full_block, dev):
+    """`GraphedCall`: the cooperative decode launch recorded in a CUDA graph; replays on new inputs written into
+    the captured tensors give the bits of the eager call."""
+    from maxuna_b200.graphs import GraphedCall
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(21)
+    x = torch.randn(4, 3072, generator=gen, device=dev)
+    call = GraphedCall(lambda: full_block.forward(x, path="decode"))
+    for _ in range(2):
+        x.copy_(torch.randn(4, 3072, generator=gen, device=dev))
+        got = call.replay().clone()
+        torch.cuda.synchronize()
+        want = full_block.forward(x, path="decode")
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    full_block.check_device_flag()
+
+
 def test_decode_rejects_bad_shapes(full_block, dev):
     from maxuna_b200 import LmoeError
 
