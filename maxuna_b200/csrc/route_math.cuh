@@ -148,66 +148,3 @@ __device__ __forceinline__ void lmoe_warp_select_regs(LogitFn logit_of, const fl
     if (scale != 0.0f && scale != 1.0f) my_w = __fmul_rn(my_w, scale);
     if (lane < top_k) w_row[lane] = my_w;
 }
-
-// Compact variant for code that runs once per kernel (instruction fetch dominates there): scores
-// live in shared memory (probs / keys: n_expert entries each, private to the warp), every loop is
-// rolled; each lane tracks the best of its own experts, a round is two warp reductions plus a
-// rescan by the one lane that owned the winner.  Same result as lmoe_warp_select.
-static __device__ __noinline__ void lmoe_warp_select_compact(const float *__restrict__ logits_row, const float *__restrict__ bias,
-                                                      float *probs, uint32_t *keys, int n_expert, int top_k, float scale,
-                                                      int norm, uint32_t *ids_row, float *w_row, int lane) {
-    uint32_t best = 0u;
-    int best_i = 0x7fffffff;
-    for (int e0 = 0; e0 < n_expert; e0 += 256) {
-        float lg[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int e = e0 + lane + 32 * i;
-            lg[i] = e < n_expert ? __ldcg(logits_row + e) : 0.0f;
-        }
-#pragma unroll 1
-        for (int i = 0; i < 8; i++) {
-            const int e = e0 + lane + 32 * i;
-            if (e < n_expert) {
-                const float p = lmoe_sigmoid_fixed(lg[i]);
-                float sv = bias ? __fadd_rn(p, bias[e]) : p; // bias: shared or global memory
-                sv = __fadd_rn(sv, 0.0f);
-                const uint32_t u = __float_as_uint(sv);
-                uint32_t k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-                k = k == 0u ? 1u : k;
-                probs[e] = p;
-                keys[e] = k;
-                if (k > best) { best = k; best_i = e; }
-            }
-        }
-    }
-    __syncwarp();
-    float my_w = 0.0f;
-#pragma unroll 1
-    for (int k = 0; k < top_k; k++) {
-        const uint32_t m = __reduce_max_sync(0xffffffffu, best);
-        const uint32_t idx = __reduce_min_sync(0xffffffffu, best == m ? (uint32_t)best_i : 0xffffffffu);
-        if ((int)idx == best_i && best == m) { // the owning lane retires the winner and rescans its experts
-            keys[idx] = 0u;
-            best = 0u;
-            best_i = 0x7fffffff;
-#pragma unroll 1
-            for (int e = lane; e < n_expert; e += 32) {
-                const uint32_t kk = keys[e];
-                if (kk > best) { best = kk; best_i = e; }
-            }
-        }
-        const float pw = probs[idx];
-        if (lane == k) my_w = pw;
-        if (lane == 0) ids_row[k] = idx;
-    }
-    if (norm) {
-        float sum = 0.0f;
-#pragma unroll 1
-        for (int k = 0; k < top_k; k++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_w, k));
-        sum = sum < 6.103515625e-5f ? 6.103515625e-5f : sum;
-        my_w = __fdiv_rn(my_w, sum);
-    }
-    if (scale != 0.0f && scale != 1.0f) my_w = __fmul_rn(my_w, scale);
-    if (lane < top_k) w_row[lane] = my_w;
-}
