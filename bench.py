@@ -399,7 +399,7 @@ def measure_lm_head(dev, steps=20, warmup=5):
             "parity": {"rows": 64, "rel_l2": orc.rel_l2(got, want), "against": "CPU oracle (dequantize -> f32 dot)"}}
 
 
-def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3, graph=False):
+def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3, graph=False, peer=False):
     """The expert portion of a Laguna-shaped model (BASELINE config 5): a residual stack of `n_layers` MoE
     layers, x <- x + block_l(rms_norm_l(x)); batched decode of 64 sequences (one token each) and a 2048-token
     prefill.
@@ -518,6 +518,21 @@ def measure_stack(dev, rank, world, n_layers, steps=3, warmup=3, graph=False):
     res["decode64"] = timed(decode_pass, 64)
     if graph:
         res["decode64_graph"] = graphed(decode_pass, 64)
+    if peer:
+        # the two exchanges of a layer as stores into the other ranks' memory (lmoe_peer_put / lmoe_peer_wait)
+        from maxuna_b200.ep import PeerExchange
+        px = PeerExchange(t_loc, H)
+        dec_nccl = dec
+        dec = [make_gpu_ep_decode(r, b, nw, blk, E, K, exchange=px) for (r, b, blk), nw in zip(parts, norms)]
+        res["decode64_peer"] = timed(decode_pass, 64)
+        if graph:
+            res["decode64_peer_graph"] = graphed(decode_pass, 64)
+        import gc
+        gc.collect()                       # recorded graphs hold the peer pointers: drop them before unmapping
+        torch.cuda.synchronize()
+        res["decode64_peer"]["wait_timeouts"] = px.timed_out()
+        px.close()
+        dec = dec_nccl
     p_loc = 2048 // world
     x2k = torch.randn(p_loc, H, generator=xg, device=dev)
     normed = torch.empty_like(x2k)
@@ -566,6 +581,7 @@ def main():
                     help="expert-parallel prefill exchange: fixed-size (all-gather / all-to-all) or compacted token lists")
     ap.add_argument("--ep-waves", type=int, default=0, help="waves of the fixed-size exchange (0 = by size)")
     ap.add_argument("--stack-graph", action="store_true", help="with --stack-layers: also time the decode pass replayed as one CUDA graph")
+    ap.add_argument("--stack-peer", action="store_true", help="with --stack-layers under torchrun: also time the decode pass with peer-memory exchanges")
     ap.add_argument("--no-stack", action="store_true", help="skip the config-5 stack and the lm_head measurements of the default run")
     ap.add_argument("--lm-head-only", action="store_true", help="profiling aid: run only the lm_head-shaped mat-vec and print it")
     args = ap.parse_args()
@@ -596,7 +612,7 @@ def main():
     _native.lib()
     if args.stack_layers > 0:
         st = measure_stack(dev, rank, world, args.stack_layers, steps=max(1, min(args.steps, 5)), warmup=min(args.warmup, 3),
-                           graph=args.stack_graph)
+                           graph=args.stack_graph, peer=args.stack_peer)
         if rank == 0:
             print(json.dumps({"stack": st}))
         if world > 1:

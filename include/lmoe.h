@@ -361,6 +361,26 @@ lmoe_status lmoe_shared_forward(const lmoe_layer *layer, const float *x, int64_t
  * Non-zero: LMOE_ERR_DEVICE_FLAG with the cause in lmoe_last_error(). */
 lmoe_status lmoe_check_device_flag(void *workspace, void *stream);
 
+/* ---- exchanges of an expert-parallel decode step over peer memory (no counterpart in the reference: one GPU) ----
+ * One process per GPU.  Every rank allocates a receive buffer and a control block with lmoe_peer_alloc, sends the
+ * 64-byte handles to the other ranks by whatever channel the host has, and maps theirs with lmoe_peer_open.
+ * lmoe_peer_put stores this rank's rows into slot `rank` of the other ranks' buffers and raises its flag there;
+ * lmoe_peer_wait holds the stream until the flags of all ranks have arrived (bounded: a time-out sets word 40 of the
+ * control block, bit 0x2 plus one bit per missing rank, and the stream goes on).  direction 0 / 1: two independent
+ * exchanges (gather, return) share one control block.  All ranks must issue the same sequence of puts. */
+lmoe_status lmoe_peer_alloc(size_t bytes, void **ptr, void *handle64);   /* zero-filled; handle64: 64 bytes out */
+lmoe_status lmoe_peer_open(const void *handle64, void **ptr);
+lmoe_status lmoe_peer_close(void *ptr);
+lmoe_status lmoe_peer_free(void *ptr);
+size_t lmoe_peer_ctrl_bytes(void);
+/* src: `world` chunks of chunk_bytes (per_rank_src = 1: chunk s goes to rank s, an all-to-all) or one chunk that goes to
+ * every rank (per_rank_src = 0, an all-gather).  peer_bufs[s] / peer_flags[s]: rank s's receive buffer and control block
+ * as mapped in this process (entry `rank`: this rank's own).  chunk_bytes a multiple of 16. */
+lmoe_status lmoe_peer_put(const void *src, int64_t chunk_bytes, int32_t world, int32_t rank, int32_t per_rank_src,
+                          void *const *peer_bufs, void *const *peer_flags, void *local_ctrl, int32_t direction,
+                          void *stream);
+lmoe_status lmoe_peer_wait(void *local_ctrl, int32_t world, int32_t direction, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,13 @@ PROTOTYPES = {
     "lmoe_experts_forward": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_forward_ep": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_prefill": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "lmoe_peer_alloc": (c_i32, [c_sz, C.POINTER(c_vp), c_vp]),
+    "lmoe_peer_open": (c_i32, [c_vp, C.POINTER(c_vp)]),
+    "lmoe_peer_close": (c_i32, [c_vp]),
+    "lmoe_peer_free": (c_i32, [c_vp]),
+    "lmoe_peer_ctrl_bytes": (c_sz, []),
+    "lmoe_peer_put": (c_i32, [c_vp, c_i64, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_i32, c_vp]),
+    "lmoe_peer_wait": (c_i32, [c_vp, c_i32, c_i32, c_vp]),
     "lmoe_moe_forward_host": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_moe_forward_host_async": (c_i32, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "lmoe_experts_forward_rows": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),

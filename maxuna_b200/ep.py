@@ -265,10 +265,11 @@ class ExpertParallelDecode:
       sum_fn(parts[G*t_loc,H], residual[t_loc,H]) -> [t_loc,H] (rank-order sum + residual).
     """
 
-    def __init__(self, norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert: int, group=None):
+    def __init__(self, norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert: int, group=None, exchange=None):
         self.norm_fn, self.route_fn, self.localize_fn = norm_fn, route_fn, localize_fn
         self.experts_fn, self.sum_fn = experts_fn, sum_fn
         self.group = group
+        self.exchange = exchange  # a `PeerExchange`: both exchanges as stores into the peers' memory instead of NCCL
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if n_expert % self.world:
             raise ValueError(f"n_expert ({n_expert}) must divide over {self.world} ranks")
@@ -279,18 +280,24 @@ class ExpertParallelDecode:
         t_loc, h = ffn_inp.shape
         g = self.world
         normed = self.norm_fn(ffn_inp)
-        x_all = torch.empty(g * t_loc, h, dtype=normed.dtype, device=normed.device)
-        dist.all_gather_into_tensor(x_all, normed.contiguous(), group=self.group)
+        if self.exchange is not None:
+            x_all = self.exchange.gather(normed.contiguous())
+        else:
+            x_all = torch.empty(g * t_loc, h, dtype=normed.dtype, device=normed.device)
+            dist.all_gather_into_tensor(x_all, normed.contiguous(), group=self.group)
         ids, w = self.route_fn(x_all)
         ids_local = self.localize_fn(ids, self.rank * self.e_local, self.e_local)
         part = self.experts_fn(x_all, ids_local, w, self.rank * t_loc, t_loc)
-        recv = torch.empty_like(part)
-        dist.all_to_all_single(recv, part.contiguous(), group=self.group)
+        if self.exchange is not None:
+            recv = self.exchange.scatter(part.contiguous())
+        else:
+            recv = torch.empty_like(part)
+            dist.all_to_all_single(recv, part.contiguous(), group=self.group)
         return self.sum_fn(recv, ffn_inp)
 
 
 def make_gpu_ep_decode(router, bias, norm_weight, local_block, n_expert, top_k, scale=2.5, norm=True, eps=1e-6,
-                       group=None):
+                       group=None, exchange=None):
     """Bind `ExpertParallelDecode` to the CUDA entry points of a local `MoeBlock` shard (`MoeBlock.shard`):
     `lmoe_rms_norm`, `lmoe_route` on the full replicated router, `lmoe_ep_localize_ids`,
     `lmoe_experts_forward_ep`, `lmoe_ep_combine`."""
@@ -338,7 +345,7 @@ def make_gpu_ep_decode(router, bias, norm_weight, local_block, n_expert, top_k, 
                                     out.data_ptr(), stream_ptr()))
         return out
 
-    return ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert, group)
+    return ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, n_expert, group, exchange)
 
 
 class ExpertParallelPrefill:
@@ -479,3 +486,90 @@ def make_gpu_ep_prefill(full_router, bias, local_block, n_expert, top_k, scale=2
     return ExpertParallelPrefill(route_fn, localize_fn, local_block.experts_forward_tokens,
                                  local_block.shared_forward if local_block.shared is not None else None, sum_fn,
                                  n_expert, top_k, group, waves=waves)
+
+
+class _RawCuda:
+    """A device range as an object torch can wrap without copying (`__cuda_array_interface__`)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerExchange:
+    """The two exchanges of an expert-parallel decode step over peer memory instead of NCCL collectives:
+    `lmoe_peer_put` / `lmoe_peer_wait` on buffers every rank maps from every other rank (CUDA IPC).
+
+    ``gather(x)``: x [n, H] of this rank -> [G*n, H] with every rank's rows (an all-gather);
+    ``scatter(parts)``: parts [G*n, H], chunk s for rank s -> [G*n, H], chunk s from rank s (an all-to-all).
+    Both return views of the receive buffers: they are overwritten by the next call of the same kind, which is safe
+    inside a decode step (a rank sends its next rows only after it has received everybody's previous ones).
+    The only host-side collective is the exchange of the 64-byte handles at construction."""
+
+    def __init__(self, max_rows: int, hidden: int, group=None, dtype=torch.float32):
+        import ctypes as C
+
+        from ._native import check, lib
+        self._lib, self._check, self._C = lib(), check, C
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.dtype, self.hidden, self.max_rows = dtype, hidden, max_rows
+        item = torch.empty(0, dtype=dtype).element_size()
+        self.chunk_cap = max_rows * hidden * item                      # bytes one rank may send to one rank
+        sizes = {"gather": self.world * self.chunk_cap, "scatter": self.world * self.chunk_cap,
+                 "ctrl": int(self._lib.lmoe_peer_ctrl_bytes())}
+        self._own, handles = {}, {}
+        for name, nbytes in sizes.items():
+            p, h = C.c_void_p(), C.create_string_buffer(64)
+            check(self._lib.lmoe_peer_alloc(nbytes, C.byref(p), h))
+            self._own[name], handles[name] = p.value, h.raw
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, handles, group=group)
+        self._opened = []
+        self._ptrs = {name: [0] * self.world for name in sizes}
+        for s in range(self.world):
+            for name in sizes:
+                if s == self.rank:
+                    self._ptrs[name][s] = self._own[name]
+                else:
+                    p = C.c_void_p()
+                    check(self._lib.lmoe_peer_open(everyone[s][name], C.byref(p)))
+                    self._ptrs[name][s] = p.value
+                    self._opened.append(p.value)
+        arr = C.c_void_p * self.world
+        self._arr = {name: arr(*self._ptrs[name]) for name in sizes}
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._recv = {name: torch.as_tensor(_RawCuda(self._own[name], sizes[name]), device=dev) for name in ("gather", "scatter")}
+        self._ctrl = torch.as_tensor(_RawCuda(self._own["ctrl"], sizes["ctrl"]), device=dev).view(torch.int32)
+        dist.barrier(group=group)                                       # every rank has mapped every buffer
+
+    def _exchange(self, src: torch.Tensor, name: str, per_rank: int, direction: int) -> torch.Tensor:
+        from .gguf import stream_ptr
+        n = src.shape[0] // self.world if per_rank else src.shape[0]
+        chunk = n * self.hidden * src.element_size()
+        assert src.is_contiguous() and src.dtype == self.dtype and src.shape[-1] == self.hidden and chunk <= self.chunk_cap
+        st = stream_ptr()
+        self._check(self._lib.lmoe_peer_put(src.data_ptr(), chunk, self.world, self.rank, per_rank, self._arr[name],
+                                            self._arr["ctrl"], self._own["ctrl"], direction, st))
+        self._check(self._lib.lmoe_peer_wait(self._own["ctrl"], self.world, direction, st))
+        return self._recv[name][: self.world * chunk].view(self.dtype).view(self.world * n, self.hidden)
+
+    def gather(self, x: torch.Tensor) -> torch.Tensor:
+        return self._exchange(x, "gather", 0, 0)
+
+    def scatter(self, parts: torch.Tensor) -> torch.Tensor:
+        return self._exchange(parts, "scatter", 1, 1)
+
+    def timed_out(self) -> int:
+        """Word 40 of the control block: non-zero when a wait gave up (bit 0x2, plus 0x100 << rank per missing rank)."""
+        return int(self._ctrl[40].item())
+
+    def close(self):
+        dist.barrier(group=self.group)
+        torch.cuda.synchronize()
+        for p in self._opened:
+            self._lib.lmoe_peer_close(p)
+        self._opened = []
+        dist.barrier(group=self.group)
+        for p in self._own.values():
+            self._lib.lmoe_peer_free(p)
+        self._own = {}

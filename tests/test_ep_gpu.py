@@ -249,7 +249,7 @@ def test_ep_decode_ranks_emulated_on_one_gpu(orc, dev, world, t_loc):
     assert float((out - single).norm() / single.norm()) < 1e-5
 
 
-def _ep_decode_worker(rank, world, port, q):
+def _ep_decode_worker(rank, world, port, q, peer=False):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -267,7 +267,11 @@ def _ep_decode_worker(rank, world, port, q):
     gen = torch.Generator(device=dev)
     gen.manual_seed(9)
     norms = [0.5 + torch.rand(hidden, generator=gen, device=dev) for _ in fulls]
-    steps = [make_gpu_ep_decode(f.router, f.exp_probs_b, nw, f.shard(rank, world), 16, 4) for f, nw in zip(fulls, norms)]
+    px = None
+    if peer:
+        from maxuna_b200.ep import PeerExchange
+        px = PeerExchange(t_loc, hidden)
+    steps = [make_gpu_ep_decode(f.router, f.exp_probs_b, nw, f.shard(rank, world), 16, 4, exchange=px) for f, nw in zip(fulls, norms)]
     x_all = torch.randn(world * t_loc, hidden, generator=gen, device=dev)
     x = x_all[rank * t_loc:(rank + 1) * t_loc].contiguous()
     ref = x.clone()
@@ -280,13 +284,18 @@ def _ep_decode_worker(rank, world, port, q):
             err0 = float((x - ref).norm() / ref.norm())
             moved = float((x - x_all[rank * t_loc:(rank + 1) * t_loc]).norm() / x.norm())   # the block's share of the output
     torch.cuda.synchronize()
+    if px is not None:
+        assert px.timed_out() == 0
+        px.close()
     q.put((rank, err0, float((x - ref).norm() / ref.norm()), moved))
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_decode_two_gpus():
-    """A three-layer residual stack, 64 sequences over two ranks, against the single-GPU layer entry."""
+@pytest.mark.parametrize("peer", [False, True])
+def test_expert_parallel_decode_two_gpus(peer):
+    """A three-layer residual stack, 64 sequences over two ranks, against the single-GPU layer entry; with NCCL
+    collectives, and with both exchanges as stores into the other rank's memory (`PeerExchange`)."""
     import torch.multiprocessing as mp
 
     s = socket.socket()
@@ -295,7 +304,7 @@ def test_expert_parallel_decode_two_gpus():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_ep_decode_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_ep_decode_worker, args=(r, 2, port, q, peer)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
