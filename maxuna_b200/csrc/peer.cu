@@ -9,8 +9,7 @@
 //                                      buffer, then flag[rank] = epoch on rank s, released at system scope
 //   lmoe_peer_wait                   : until flag[0 .. world) have all reached the epoch
 // The epoch lives on the device (one word per direction, advanced by the put kernel), so a recorded sequence of
-// launches (a CUDA graph) can be replayed.  Only plain stores and loads touch peer memory: no bulk copy, no
-// multicast.
+// launches (a CUDA graph) can be replayed.  Only plain stores and loads touch peer memory.
 #include "common.cuh"
 #include "fused.cuh"
 
