@@ -29,7 +29,24 @@ def _layer(orc, seed, hidden=256, ff=256, ne=8, top_k=3):
                          sh_gate=q(orc.Q4_K, (ff, hidden)), sh_up=q(orc.Q4_K, (ff, hidden)), sh_down=q(orc.Q6_K, (hidden, ff)))
 
 
-def _worker(rank, world, port, q):
+class _HostExchange:
+    """What `PeerExchange` does, on the host: `gather` / `scatter` with the same shapes and slot order, over gloo."""
+
+    def __init__(self, world):
+        self.world = world
+
+    def gather(self, x):
+        out = torch.empty(self.world * x.shape[0], x.shape[1], dtype=x.dtype)
+        dist.all_gather_into_tensor(out, x.contiguous())
+        return out
+
+    def scatter(self, parts):
+        out = torch.empty_like(parts)
+        dist.all_to_all_single(out, parts.contiguous())
+        return out
+
+
+def _worker(rank, world, port, q, exchange=False):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -75,7 +92,8 @@ def _worker(rank, world, port, q):
                 out += parts[s_ * t:(s_ + 1) * t]
             return out + residual
 
-        steps.append(ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, L.n_expert))
+        steps.append(ExpertParallelDecode(norm_fn, route_fn, localize_fn, experts_fn, sum_fn, L.n_expert,
+                                          exchange=_HostExchange(world) if exchange else None))
     # all ranks draw the same batch; each keeps its slice
     x_all = np.random.default_rng(7).standard_normal((world * t_loc, hidden)).astype(np.float32)
     x = torch.from_numpy(x_all[rank * t_loc:(rank + 1) * t_loc].copy())
@@ -90,13 +108,15 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_decode_cpu_ranks(orc, world):
+@pytest.mark.parametrize("world,exchange", [(2, False), (4, False), (2, True)])
+def test_expert_parallel_decode_cpu_ranks(orc, world, exchange):
+    """The host logic of the expert-parallel decode step on gloo ranks against the single-process oracle; once with
+    the exchanges behind the `exchange` object (the seam `PeerExchange` plugs into)."""
     orc.build()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=180) for _ in procs]
