@@ -287,7 +287,10 @@ lmoe_status lmoe_moe_forward_host(const lmoe_layer *layer, const float *x_host, 
 /* The same without the final synchronisation, like every other entry of this header (the reference's ops return
  * before the GPU has run them, src/ops/dispatch.rs `run_inner`): the copies and the kernels are enqueued on `stream`
  * and the call returns; `out_host` holds the result once the stream has been synchronised.  Calls that share a
- * workspace must share the stream.  Both buffers must be pinned for the copies to be asynchronous. */
+ * workspace must share the stream.  Both buffers must be pinned for the copies to be asynchronous.  With both
+ * pinned, a decode call's input is copied on a stream of the layer's own (into staging buffers of the layer), so
+ * that the copy runs beside the previous call's kernel: x_host is read without regard to earlier work on `stream`
+ * and must be complete when the call is made.  Not for use inside a stream capture (host addresses). */
 lmoe_status lmoe_moe_forward_host_async(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
                                   uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                   size_t workspace_bytes, void *stream);

@@ -357,6 +357,12 @@ extern "C" void lmoe_layer_destroy(lmoe_layer *layer) {
     if (!layer) return;
     cudaFree(layer->sync);
     if (layer->dec_event) cudaEventDestroy(layer->dec_event);
+    for (int i = 0; i < 2; i++) {
+        if (layer->host_x[i]) cudaFree(layer->host_x[i]);
+        if (layer->host_copied[i]) cudaEventDestroy(layer->host_copied[i]);
+        if (layer->host_slot_free[i]) cudaEventDestroy(layer->host_slot_free[i]);
+    }
+    if (layer->host_copy_stream) cudaStreamDestroy(layer->host_copy_stream);
     delete layer;
 }
 

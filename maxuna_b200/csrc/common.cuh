@@ -62,6 +62,14 @@ struct lmoe_layer {
     mutable cudaEvent_t dec_event = nullptr;
     mutable cudaStream_t dec_stream = nullptr;
     mutable bool dec_pending = false;
+    // Host-buffer decode calls: two device staging rows-buffers, filled by a copy stream of the layer's own, so that
+    // the host-to-device copy of a call runs while the previous call's kernel does (created at the first such call).
+    mutable std::mutex host_mutex;
+    mutable float *host_x[2] = {nullptr, nullptr};
+    mutable cudaStream_t host_copy_stream = nullptr;
+    mutable cudaEvent_t host_copied[2] = {nullptr, nullptr}, host_slot_free[2] = {nullptr, nullptr};
+    mutable int host_slot = 0;
+    mutable bool host_failed = false;
 };
 
 static inline int lmoe_type_size(int32_t dtype) {

@@ -183,6 +183,37 @@ static float *host_buffer_device_alias(float *p) {
     return static_cast<float *>(a.devicePointer);
 }
 
+// True for page-locked host memory (a copy from it is asynchronous).
+static bool host_buffer_is_pinned(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost;
+}
+
+// The staging buffers, copy stream and events of the host-buffer decode path; false when they cannot be had
+// (the call then copies on the caller's stream).
+static bool host_staging_ready(const lmoe_layer *L) {
+    if (L->host_failed) return false;
+    if (L->host_copy_stream) return true;
+    const size_t bytes = (size_t)decode_max_tokens() * L->hidden * 4;
+    bool ok = cudaMalloc(&L->host_x[0], bytes) == cudaSuccess && cudaMalloc(&L->host_x[1], bytes) == cudaSuccess;
+    for (int i = 0; i < 2 && ok; i++)
+        ok = cudaEventCreateWithFlags(&L->host_copied[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&L->host_slot_free[i], cudaEventDisableTiming) == cudaSuccess;
+    cudaStream_t cs = nullptr;
+    ok = ok && cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        L->host_failed = true; // what was created is released with the layer
+        return false;
+    }
+    L->host_copy_stream = cs;
+    return true;
+}
+
 static lmoe_status forward_host_enqueue(const lmoe_layer *layer, const float *x_host, int64_t t, float *out_host,
                                         uint32_t *ids_out_host, float *weights_out_host, void *workspace,
                                         size_t workspace_bytes, void *stream) {
@@ -203,7 +234,6 @@ static lmoe_status forward_host_enqueue(const lmoe_layer *layer, const float *x_
     float *od = reinterpret_cast<float *>(ws + kernel_ws + xb);
     uint32_t *idd = reinterpret_cast<uint32_t *>(ws + kernel_ws + 2 * xb);
     float *wd = reinterpret_cast<float *>(ws + kernel_ws + 2 * xb + ib);
-    LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
     lmoe_status st;
     // the reference switches to its grouped GEMM at 32 tokens (`use_mm`, src/moe.rs:236-240); here the mat-vec
     // kernel, which streams each distinct expert once per launch, stays ahead up to 64 tokens
@@ -212,6 +242,34 @@ static lmoe_status forward_host_enqueue(const lmoe_layer *layer, const float *x_
     // phase stores the rows there itself (a few KB of posted writes) and the device-to-host copy, whose fixed
     // cost is a tenth of a one-token call, is not needed.
     float *out_direct = decode ? host_buffer_device_alias(out_host) : nullptr;
+    if (decode && out_direct && t <= decode_max_tokens() && host_buffer_is_pinned(x_host)) {
+        // Both buffers pinned: the input goes through one of two staging buffers of the layer on the layer's own
+        // copy stream, so this call's copy overlaps the previous call's kernel; `stream` waits for the copy, the
+        // copy waits for the kernel that last read the staging buffer.  x_host is read without regard to earlier
+        // work on `stream`: it must be complete when the call is made.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) (void)cudaGetLastError();
+        std::unique_lock<std::mutex> lock(layer->host_mutex);
+        if (cap == cudaStreamCaptureStatusNone && host_staging_ready(layer)) {
+            const int slot = layer->host_slot;
+            layer->host_slot ^= 1;
+            cudaStream_t cs = layer->host_copy_stream;
+            LMOE_CUDA(cudaStreamWaitEvent(cs, layer->host_slot_free[slot], 0));
+            LMOE_CUDA(cudaMemcpyAsync(layer->host_x[slot], x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, cs));
+            LMOE_CUDA(cudaEventRecord(layer->host_copied[slot], cs));
+            LMOE_CUDA(cudaStreamWaitEvent(s, layer->host_copied[slot], 0));
+            st = lmoe_moe_forward_decode(layer, layer->host_x[slot], t, out_direct, ids_out_host ? idd : nullptr,
+                                         weights_out_host ? wd : nullptr, workspace, kernel_ws, stream);
+            if (st) return st;
+            LMOE_CUDA(cudaEventRecord(layer->host_slot_free[slot], s));
+            lock.unlock();
+            if (ids_out_host) LMOE_CUDA(cudaMemcpyAsync(ids_out_host, idd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
+            if (weights_out_host)
+                LMOE_CUDA(cudaMemcpyAsync(weights_out_host, wd, (size_t)t * layer->top_k * 4, cudaMemcpyDeviceToHost, s));
+            return LMOE_OK;
+        }
+    }
+    LMOE_CUDA(cudaMemcpyAsync(xd, x_host, (size_t)t * layer->hidden * 4, cudaMemcpyHostToDevice, s));
     if (!decode)
         st = lmoe_moe_forward_prefill(layer, xd, t, od, ids_out_host ? idd : nullptr, weights_out_host ? wd : nullptr,
                                       workspace, kernel_ws, stream);
