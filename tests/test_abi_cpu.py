@@ -81,6 +81,29 @@ def test_expert_parallel_argument_errors_without_cuda():
     assert lib.lmoe_experts_forward_rows_f16(None, fake, fake, fake, 4, fake, fake, 1 << 20, None) == -1
 
 
+def test_peer_and_host_entry_argument_errors_without_cuda():
+    """The peer-memory exchange and the host-buffer entries check their arguments before they touch the GPU."""
+    from maxuna_b200 import _native
+
+    lib = _native.lib()
+    fake = C.c_void_p(4096)
+    arr = (C.c_void_p * 2)(4096, 8192)
+    assert lib.lmoe_peer_ctrl_bytes() >= 128 * 4
+    assert lib.lmoe_peer_alloc(0, C.byref(C.c_void_p()), C.create_string_buffer(64)) == -1
+    assert lib.lmoe_peer_open(None, C.byref(C.c_void_p())) == -1
+    assert lib.lmoe_peer_put(None, 64, 2, 0, 0, arr, arr, fake, 0, None) == -1
+    assert lib.lmoe_peer_put(fake, 64, 17, 0, 0, arr, arr, fake, 0, None) == -1          # more ranks than the kernel carries
+    assert lib.lmoe_peer_put(fake, 64, 2, 2, 0, arr, arr, fake, 0, None) == -1           # rank outside the world
+    assert lib.lmoe_peer_put(fake, 40, 2, 0, 0, arr, arr, fake, 0, None) == -1           # chunk not a multiple of 16
+    assert b"16" in lib.lmoe_last_error()
+    assert lib.lmoe_peer_put(fake, 64, 2, 0, 0, arr, arr, fake, 2, None) == -1           # direction is 0 or 1
+    assert lib.lmoe_peer_wait(None, 2, 0, None) == -1
+    assert lib.lmoe_peer_wait(fake, 0, 0, None) == -1
+    for fn in (lib.lmoe_moe_forward_host, lib.lmoe_moe_forward_host_async):
+        assert fn(None, fake, 1, fake, None, None, fake, 1 << 20, None) == -1
+        assert b"layer" in lib.lmoe_last_error()
+
+
 def test_host_mirror_rejects_cpu_tensors():
     import torch
 
