@@ -615,6 +615,48 @@ __device__ __forceinline__ void dequant_q4k_regs(const uint4 hdr, const uint4 qa
     }
 }
 
+// Epilogue of the 32-column chunks [c0, c1) of a gate/up tile for the 32 weight rows of tensor-memory quadrant q:
+// act = silu(gate) * up, one routed row per tile column.
+__device__ __forceinline__ void gu_epilogue_chunks(const GuParams &P, uint32_t tmem_base, int tile, int q, int lane, int c0, int c1) {
+    const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
+    const int m = 32 * q + lane;
+    const bool mvalid = m0 + m < P.n_out;
+    for (int c = c0; c < c1; c++) {
+        const int cb = 32 * c;
+        if (cb >= nv) break;
+        uint32_t vg[32], vu[32];
+        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + cb, vg);
+        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + GU_ACC_UP + cb, vu);
+        if (P.sorted) {
+            // rows in expert-sorted order: consecutive tile columns are consecutive rows
+            float *dst = P.act + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + m0 + m;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
+                const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = a;
+            }
+        } else {
+            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
+            const int myfid = cb + lane < nv ? list[cb + lane] : 0;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int fid = __shfl_sync(0xffffffffu, myfid, j);
+                const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
+                const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
+            }
+        }
+    }
+}
+
+// Chunks of a tile's epilogue by warp: the four epilogue warps take the first GU_EPI_OWN chunks, the dequantising
+// warps of the gate projection the next two, those of the up projection the last two.  An epilogue of 192 columns
+// by four warps alone takes as long as a fifth of the tile's multiplies, and nothing can be multiplied meanwhile
+// (there is one accumulator set); the dequantising warps have nothing to do at that moment.
+constexpr int GU_EPI_OWN = 2;
+static_assert(MM_N == 32 * (GU_EPI_OWN + 4), "the epilogue split covers six 32-column chunks");
+
 __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_constant__ GuParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -641,7 +683,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
             mb_init(&raw_empty[i], 4);
         }
         mb_init(acc_full, 1);
-        mb_init(acc_empty, 4);
+        mb_init(acc_empty, 12); // the four epilogue warps and the eight dequantising warps that share the epilogue
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -659,7 +701,7 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
         // eight consecutive rows cover all banks for 16-byte reads).
         const int sub = warp >> 2, r = tid & 127;
         const int n_blk = P.k / QK_K;
-        uint32_t g = 0, col = 0; // k-stage counter, super-block column counter of this projection
+        uint32_t g = 0, col = 0, it_e = 0; // k-stage counter, super-block column counter of this projection, tiles done
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const int m0 = P.tiles[8 * tile + 3];
@@ -691,6 +733,16 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
                 __syncwarp();
                 if (lane == 0) mb_arrive(&raw_empty[slot]);
             }
+            // this warp's share of the tile's epilogue (columns beyond the first 64, if the tile has them)
+            if (P.tiles[8 * tile + 2] > 32 * (GU_EPI_OWN + 2 * sub) && ok) {
+                ok = mb_wait(acc_full, it_e & 1, P.flag, 10);
+                tc_fence_after();
+                gu_epilogue_chunks(P, tmem_base, tile, warp & 3, lane, GU_EPI_OWN + 2 * sub, GU_EPI_OWN + 2 * sub + 2);
+                tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) mb_arrive(acc_empty);
+            it_e++;
         }
     } else if (warp == 14) {
         // ---------------- raw loader: one TMA tile load per (super-block column, projection) ----------------
@@ -776,51 +828,14 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: act = silu(gate) * up ----------------
+        // ---------------- epilogue: act = silu(gate) * up (the first chunks; see GU_EPI_OWN) ----------------
         const int q = warp & 3;
-        const int m = 32 * q + lane;
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
-            const int e = P.tiles[8 * tile], l0 = P.tiles[8 * tile + 1], nv = P.tiles[8 * tile + 2], m0 = P.tiles[8 * tile + 3];
-            const int32_t *list = P.ids_map + (size_t)e * P.map_stride + l0;
-            // destination rows are fetched while the tile is still being multiplied
-            int fids[MM_N / 32];
-#pragma unroll
-            for (int c = 0; c < MM_N / 32; c++) {
-                const int my = 32 * c + lane;
-                fids[c] = my < nv ? list[my] : 0;
-            }
             ok = mb_wait(acc_full, it & 1, P.flag, 8);
             tc_fence_after();
-            const bool mvalid = m0 + m < P.n_out;
-#pragma unroll
-            for (int c = 0; c < MM_N / 32; c++) {
-                const int cb = 32 * c;
-                if (cb >= nv) break;
-                uint32_t vg[32], vu[32];
-                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + cb, vg);
-                tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + GU_ACC_UP + cb, vu);
-                const int myfid = fids[c];
-                if (P.sorted) {
-                    // rows in expert-sorted order: consecutive tile columns are consecutive rows
-                    float *dst = P.act + (size_t)(P.tiles[8 * tile + 5] + cb) * P.n_out + m0 + m;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
-                        const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
-                        if (cb + j < nv && mvalid) dst[(size_t)j * P.n_out] = a;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int fid = __shfl_sync(0xffffffffu, myfid, j);
-                        const float gv = __uint_as_float(vg[j]), uv = __uint_as_float(vu[j]);
-                        const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
-                        if (cb + j < nv && mvalid) P.act[(size_t)fid * P.n_out + m0 + m] = a;
-                    }
-                }
-            }
+            gu_epilogue_chunks(P, tmem_base, tile, q, lane, 0, GU_EPI_OWN);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mb_arrive(acc_empty);
