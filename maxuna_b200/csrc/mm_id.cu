@@ -858,8 +858,9 @@ __global__ void __launch_bounds__(GU_THREADS, 1) mm_gateup_kernel(const __grid_c
 // Tensor-memory columns: [0, MM_N) and [MM_N, 2 MM_N) accumulator buffers, [2 MM_N, 2 MM_N + 128) four A stages.
 //   warps 0-15 dequant (quadrant = warp & 3, l half = (warp >> 2) & 1, nibble half = warp >> 3)
 //   warp 16 loader of the quantized runs    warp 17 B loader    warp 18 MMA issuer    warps 19-22 epilogue
+//   warp 23 forwarder: a B stage has landed -> the A stage's barrier (the issuer waits once per k-stage)
 constexpr int DN_DQ_WARPS = 16;
-constexpr int DN_THREADS = (DN_DQ_WARPS + 7) * 32;
+constexpr int DN_THREADS = (DN_DQ_WARPS + 8) * 32;
 constexpr int DN_NSA = 4, DN_NSB = 2;
 constexpr int DN_RUN_ROWS = 32;                 // rows of one bulk-copied run (= one lane quadrant)
 constexpr int DN_RAW_SLOTS = 6;                 // ring of runs: the four of the current tile and two ahead
@@ -960,7 +961,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
     uint8_t *b_st = smem;
     uint8_t *raw = b_st + DN_NSB * B_STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw + DN_RAW_SLOTS * P.raw_slot_bytes);
-    uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *b_empty = bars + 10, *raw_full = bars + 12,
+    uint64_t *a_full = bars, *a_empty = bars + 4, *b_full = bars + 8, *raw_full = bars + 12,
              *raw_empty = bars + 18, *acc_full = bars + 24, *acc_empty = bars + 26;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
 
@@ -970,14 +971,16 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
     const int row_bytes = n_blk * Q6K_BYTES;
 
     if (tid == 0) {
+        // The thread that issues the multiplies pays 100-300 cycles for every synchronising instruction, and its chain
+        // per k-stage was the kernel's period: it waits on ONE barrier per stage (a_full: the eight warps of the
+        // stage's nibble half + the forwarder's word that the B stage has landed) and commits to ONE (a_empty:
+        // the stage's multiplies are done), which the dequantising warps (stage g - 4), the B loader (stage g - 2)
+        // and the forwarder (stage g - 4) all wait on.
         for (int s = 0; s < DN_NSA; s++) {
-            mb_init(&a_full[s], DN_DQ_WARPS / 2); // the eight warps of the stage's nibble half
+            mb_init(&a_full[s], DN_DQ_WARPS / 2 + 1);
             mb_init(&a_empty[s], 1);
         }
-        for (int s = 0; s < DN_NSB; s++) {
-            mb_init(&b_full[s], 1);
-            mb_init(&b_empty[s], 1);
-        }
+        for (int s = 0; s < DN_NSB; s++) mb_init(&b_full[s], 1);
         for (int s = 0; s < DN_RAW_SLOTS; s++) {
             mb_init(&raw_full[s], 1);
             mb_init(&raw_empty[s], 4); // the four dequant warps of the run's quadrant
@@ -1077,9 +1080,25 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 const uint8_t *src = P.xt + (size_t)slot * k_stages * B_STAGE_BYTES;
                 for (int ks = 0; ks < k_stages && ok; ks++, g++) {
                     const int s = g % DN_NSB;
-                    ok = mb_wait(&b_empty[s], ((g / DN_NSB) & 1) ^ 1, P.flag, 4);
+                    // the B stage is free when the multiplies of stage g - DN_NSB are done
+                    if (g >= DN_NSB) ok = mb_wait(&a_empty[(g - DN_NSB) % DN_NSA], ((g - DN_NSB) / DN_NSA) & 1, P.flag, 4);
                     mb_expect_tx(&b_full[s], (uint32_t)nv * 128u);
                     bulk_g2s(b_st + (size_t)s * B_STAGE_BYTES, src + (size_t)ks * B_STAGE_BYTES, (uint32_t)nv * 128u, &b_full[s]);
+                }
+            }
+        }
+    } else if (warp == DN_DQ_WARPS + 7) {
+        // ---------------- forwarder ----------------
+        // Its word for stage g must fall into phase g / DN_NSA of a_full[g % DN_NSA]: it is given once the multiplies
+        // of stage g - DN_NSA are done (the dequantising warps wait for the same event before they store).
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
+                    ok = mb_wait(&b_full[g % DN_NSB], (g / DN_NSB) & 1, P.flag, 7);
+                    if (g >= DN_NSA) ok = ok && mb_wait(&a_empty[g % DN_NSA], ((g - DN_NSA) / DN_NSA) & 1, P.flag, 9);
+                    mb_arrive(&a_full[g % DN_NSA]);
                 }
             }
         }
@@ -1088,6 +1107,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
         if (lane == 0) {
             uint32_t g = 0, it = 0;
             bool ok = true;
+            const uint64_t bd0 = umma_desc(s32(b_st)); // B stage i: this plus i stages in the 16-byte address field
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
                 const int nv = P.tiles[8 * tile + 2];
                 const int npad = (nv + 15) & ~15;
@@ -1096,18 +1116,20 @@ __global__ void __launch_bounds__(DN_THREADS, 1) mm_down_kernel(const __grid_con
                 ok = mb_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, P.flag, 5);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * MM_N;
-                for (int ks = 0; ks < k_stages && ok; ks++, g++) {
-                    const int sa = g % DN_NSA, sb = g % DN_NSB;
-                    ok = mb_wait(&a_full[sa], (g / DN_NSA) & 1, P.flag, 6);
-                    ok = ok && mb_wait(&b_full[sb], (g / DN_NSB) & 1, P.flag, 7);
-                    tc_fence_after();
-                    const uint32_t a_tmem = tmem_base + DN_A_COL0 + (uint32_t)sa * 32u;
-                    const uint64_t bd = umma_desc(s32(b_st + (size_t)sb * B_STAGE_BYTES));
+                // a tile has a multiple of four k-stages (k is a multiple of 256): the ring slots of a stage follow from
+                // its index in the tile, and the loop is unrolled over them
+                for (int k4 = 0; k4 < k_stages / 4 && ok; k4++, g += 4) {
 #pragma unroll
-                    for (int kk = 0; kk < MM_K / 16; kk++)
-                        tc_mma_f16_ts(d_tmem, a_tmem + 8 * kk, bd + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                    tc_commit(&a_empty[sa]); // frees both stages when these MMAs have read them
-                    tc_commit(&b_empty[sb]);
+                    for (int u = 0; u < 4; u++) {
+                        ok = ok && mb_wait(&a_full[u], (g / DN_NSA) & 1, P.flag, 6);
+                        tc_fence_after();
+                        const uint32_t a_tmem = tmem_base + DN_A_COL0 + (uint32_t)u * 32u;
+                        const uint64_t bd = bd0 + (uint64_t)((u % DN_NSB) * (B_STAGE_BYTES >> 4));
+#pragma unroll
+                        for (int kk = 0; kk < MM_K / 16; kk++)
+                            tc_mma_f16_ts(d_tmem, a_tmem + 8 * kk, bd + 2 * kk, idesc, (k4 | u | kk) != 0 ? 1u : 0u);
+                        tc_commit(&a_empty[u]); // the stage's multiplies are done: its A and B stages are free
+                    }
                 }
                 tc_commit(&acc_full[buf]);
             }
