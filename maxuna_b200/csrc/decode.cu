@@ -907,6 +907,8 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
     const Tables T{off_s, plist_s, act_s, ppre_s, s_n_active, s_routed_passes, shared_passes};
 
     uint32_t n_unit = 0; // units (= ring fills) before the current section, the same sequence as the producer's
+    uint32_t probed = 0xffffffffu; // unit whose barriers have been tested ahead (see the unit loop), and the answers
+    bool probe_data = false, probe_buf = false;
     unsigned long long xkey = ~0ull;
 
     // ---- phases 1 and 2 ----
@@ -953,7 +955,12 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
                     if ((int)(n % NG) != grp) continue;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
                     const int s = n % NSTAGE; // one ring fill per unit
-                    mbar_wait(&full[s], (n / NSTAGE) & 1, P.ctrl, 0x20 + phase);
+                    // the answers about this unit's two barriers were asked for before the previous unit's arithmetic
+                    const bool have_data = probed == n && probe_data, have_buf = probed == n && probe_buf;
+                    if (!have_data) mbar_wait(&full[s], (n / NSTAGE) & 1, P.ctrl, 0x20 + phase);
+                    probed = n + 1;
+                    probe_data = mbar_test(&full[probed % NSTAGE], (probed / NSTAGE) & 1);
+                    probe_buf = mbar_test(&red_free[probed % NRED], ((probed / NRED) & 1) ^ 1);
                     const uint8_t *stage = ring + (size_t)s * L.stage_bytes;
                     if (phase == 1) unit_q4k(stage, row4, nb4, wq, g, t4, xcol, scol, sxs, r0, r1, acc);
                     else unit_q6k(stage, row6, nb6, wq, g, t4, xcol, scol, sxs, r0, r1, acc);
@@ -961,7 +968,7 @@ __global__ void __launch_bounds__(Cfg<NG>::THREADS, Cfg<NG>::MIN_CTAS) moe_decod
                     if (lane == 0) mbar_arrive(&empty[s]);
                     // K-split partials -> shared memory, handed to the epilogue warp
                     const int buf = n % NRED;
-                    mbar_wait(&red_free[buf], ((n / NRED) & 1) ^ 1, P.ctrl, 0x28 + phase);
+                    if (!have_buf) mbar_wait(&red_free[buf], ((n / NRED) & 1) ^ 1, P.ctrl, 0x28 + phase);
                     float *rb = red + buf * (CW * 16 * NCOL);
                     if (2 * t4 < NCOL) {
                         // accumulator rows: g and g+8 of the 16 (phase 1), 2g and 2g+1 (phase 2, see unit_q6k)

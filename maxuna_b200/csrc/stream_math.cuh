@@ -30,6 +30,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The non-suspending test of the same condition: answers at once.  Used to ask about the NEXT unit's barriers before
+// the current unit's arithmetic, so that the answer's latency (a few hundred cycles even for a completed phase) passes
+// under the arithmetic instead of in front of it.
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after SPIN_LIMIT polls, records the fact and carries on
 // (results are then invalid, but every loop in the kernel stays finite).
 template <int BACKOFF_NS = 0>
