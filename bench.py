@@ -49,11 +49,11 @@ EXPERT_BYTES = 2 * F * (H // 256) * 144 + H * (F // 256) * 210  # 6 119 424
 ROUTER_BYTES = E * H * 4
 WORKLOAD = "config2: single MoE layer decode sweep B=1/2/4/8/16 (31 tokens per step)"
 # DRAM traffic of one decode sweep (B = 1, 2, 4, 8, 16) from an ncu capture of the five launches
-# (dram__bytes_read.sum + dram__bytes_write.sum: 71.7 + 137.1 + 224.5 + 413.6 + 706.7 MB; the algorithmic figure is
+# (dram__bytes_read.sum + dram__bytes_write.sum: 72.3 + 136.0 + 224.6 + 412.8 + 705.8 MB; the algorithmic figure is
 # the mean over the three sweeps of that run).  The figure belongs to the kernel source it was captured on: when
 # csrc/decode.cu has changed since, the line reports null.
-NCU_TRAFFIC = {"bytes_per_sweep": 1.5537e9, "algorithmic_bytes_of_that_sweep": 1.4648e9,
-               "decode_cu_sha256_16": "a66d42906b72bf68"}
+NCU_TRAFFIC = {"bytes_per_sweep": 1.5516e9, "algorithmic_bytes_of_that_sweep": 1.4648e9,
+               "decode_cu_sha256_16": "462102bd0ae44431"}
 NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
            "clocks_event_reasons.sw_power_cap")
