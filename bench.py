@@ -12,10 +12,18 @@ weights come from HBM, not from cache.
 
   value     device-resident inputs, CUDA-event timed, whole job (all ranks)
   e2e       same sweep through the C-ABI host-buffer call (pinned host x in,
-            host result out, copies inside the timed region)
+            host result out, copies inside the timed region): the asynchronous
+            entry with one stream synchronisation per step; `sync_every_call`
+            is the synchronous entry
   roofline  decode kernel: algorithmic bytes / event-timed launch duration
   cpu_baseline  the CPU restatement of the reference's CPU path (int8-activation
             k-quant dot products), all host threads, bounded sample
+  prefill   config 3 (N = 1: 4096 tokens, with parity sample, e2e, CPU leg and a
+            16384-token anchor) or config 4 (N > 1: 16384 tokens expert parallel,
+            with parity sample and per-phase times)
+  stack     config 5: 48 layers, 64-sequence batched decode and 2048-token prefill
+            (expert parallel under torchrun)
+  lm_head   the vocabulary-projection mat-vec, Q6_K [100352 x 3072]
 
 `--impl reference` times that CPU restatement alone (the reference is Rust +
 Metal and cannot be built or run here).
